@@ -1,0 +1,195 @@
+// Host side of the C ABI: status text, pool geometry, paged-metadata validation and the
+// length-aware split-KV schedule.  Nothing here touches the device.
+#include "../../include/gaudirt_b200.h"
+
+#include <algorithm>
+#include <array>
+#include <climits>
+#include <cstdint>
+#include <numeric>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+thread_local std::string g_metadata_error;
+
+int metadata_fail(const char* message) {
+  g_metadata_error = message;
+  return GK_ERR_METADATA;
+}
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+}  // namespace
+
+namespace gk {
+extern thread_local int g_last_cuda_error;
+}
+
+extern "C" const char* gk_status_string(int status) {
+  switch (status) {
+    case GK_OK: return "ok";
+    case GK_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size, misaligned pointer or stride)";
+    case GK_ERR_UNSUPPORTED: return "unsupported geometry";
+    case GK_ERR_CUDA: return "CUDA launch failed";
+    case GK_ERR_CAPACITY: return "output array or scratch area too small";
+    case GK_ERR_METADATA: return "paged metadata rejected";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int gk_abi_version(void) { return 1; }
+extern "C" int gk_last_cuda_error(void) { return gk::g_last_cuda_error; }
+extern "C" const char* gk_metadata_error(void) { return g_metadata_error.c_str(); }
+
+extern "C" int gk_paged_kv_pool_bytes(int64_t layers, int64_t slots, int64_t kv_heads, int64_t head_dim,
+                                      uint64_t* bytes_out) {
+  if (!bytes_out) return GK_ERR_INVALID_ARGUMENT;
+  // Geometry limits of allocate_paged_kv (src/bridge/paged_kv_pool.cpp:16-20) without its
+  // 131072-slot descriptor cap; slots stay addressable by int32 slot ids.
+  if (layers <= 0 || layers > 4096 || slots <= 0 || slots > INT32_MAX || kv_heads <= 0 || kv_heads > 256 ||
+      (head_dim != 64 && head_dim != 128 && head_dim != 256))
+    return GK_ERR_UNSUPPORTED;
+  const uint64_t layer = 2ull * (uint64_t)slots * (uint64_t)kv_heads * (uint64_t)head_dim * 2ull;
+  if (layer > UINT64_MAX / (uint64_t)layers) return GK_ERR_UNSUPPORTED;
+  *bytes_out = layer * (uint64_t)layers;
+  return GK_OK;
+}
+
+extern "C" int gk_paged_metadata_validate(const int32_t* locations, const int32_t* requests, const int32_t* positions,
+                                          int64_t rows, const int32_t* mapping, int64_t n_requests, int64_t context,
+                                          int64_t slots, int32_t* seq_out, int64_t* n_seq_out,
+                                          int32_t* page_tokens_out) {
+  if (!locations || !requests || !positions || !mapping || !seq_out || !n_seq_out) return GK_ERR_INVALID_ARGUMENT;
+  if (rows <= 0 || rows > INT32_MAX || slots <= 0 || slots > INT32_MAX || n_requests <= 0 || n_requests > INT32_MAX ||
+      context <= 0 || context > INT32_MAX || n_requests * context > INT32_MAX)
+    return metadata_fail("GaudiRT: paged metadata dimensions outside supported range");
+  const int64_t cells = n_requests * context;
+  for (int64_t i = 0; i < cells; ++i)
+    if (mapping[i] < -1 || mapping[i] >= slots) return metadata_fail("GaudiRT: request-to-token slot is out of range");
+
+  std::vector<int32_t> reach(n_requests, -1);
+  std::unordered_map<int32_t, std::pair<int32_t, int32_t>> target;   // output slot -> (request, position)
+  target.reserve((size_t)rows * 2);
+  int64_t n_seq = 0;
+  for (int64_t i = 0; i < rows; ++i) {
+    const int64_t slot = locations[i], request = requests[i], position = positions[i];
+    if (slot < 0 || slot >= slots || request < 0 || request >= n_requests || position < 0 || position >= context)
+      return metadata_fail("GaudiRT: paged metadata index is out of range");
+    if (mapping[request * context + position] != slot)
+      return metadata_fail("GaudiRT: output slot does not match request-to-token mapping");
+    if (!target.emplace((int32_t)slot, std::make_pair((int32_t)request, (int32_t)position)).second)
+      return metadata_fail("GaudiRT: duplicate output KV slot");
+    const bool continues = i > 0 && requests[i - 1] == request && positions[i - 1] + 1 == position;
+    if (continues) {
+      ++seq_out[(n_seq - 1) * 4 + 1];
+    } else {
+      int32_t* s = seq_out + n_seq * 4;
+      s[0] = (int32_t)i;
+      s[1] = 1;
+      s[2] = (int32_t)position;
+      s[3] = (int32_t)request;
+      ++n_seq;
+    }
+    reach[request] = std::max(reach[request], (int32_t)position);
+  }
+  int page = 128;
+  for (int64_t request = 0; request < n_requests; ++request) {
+    const int32_t* row = mapping + request * context;
+    for (int32_t position = 0; position <= reach[request]; ++position) {
+      const int32_t slot = row[position];
+      if (slot < 0) return metadata_fail("GaudiRT: missing KV slot in a visible prefix");
+      const auto hit = target.find(slot);
+      if (hit != target.end() && (hit->second.first != request || hit->second.second != position))
+        return metadata_fail("GaudiRT: output KV slot aliases another visible prefix position");
+      // A break in slot contiguity at `position` only allows pages that end there.
+      if (position > 0 && slot != row[position - 1] + 1) page = std::min(page, position & -position);
+    }
+  }
+  *n_seq_out = n_seq;
+  if (page_tokens_out) *page_tokens_out = page;
+  return GK_OK;
+}
+
+extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_heads, int kv_heads, int head_dim,
+                                       int window, int sm_count, int split_tokens, int32_t* work_out,
+                                       int64_t work_cap, int64_t* n_work_out, int32_t* combine_out,
+                                       int64_t combine_cap, int64_t* n_combine_out, int64_t* partial_entries_out) {
+  if (!seq || n_seq <= 0 || !n_work_out || !n_combine_out || !partial_entries_out || sm_count <= 0 ||
+      split_tokens < 0 || (window != -1 && window <= 0))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (q_heads <= 0 || q_heads > 256 || kv_heads <= 0 || kv_heads > 256 || q_heads % kv_heads != 0 ||
+      (head_dim != 64 && head_dim != 128 && head_dim != 256) || q_heads / kv_heads > GK_MAX_PACKED_ROWS)
+    return GK_ERR_UNSUPPORTED;
+  const int group = q_heads / kv_heads;
+  const int block_rows = std::max(1, GK_MAX_PACKED_ROWS / group);
+
+  struct Block { int32_t first_row, n_rows, first_pos, table_row, lo, hi; };
+  std::vector<Block> blocks;
+  int64_t total_span = 0;
+  for (int64_t s = 0; s < n_seq; ++s) {
+    const int32_t* r = seq + s * 4;
+    if (r[1] <= 0 || r[2] < 0 || r[0] < 0 || r[3] < 0) return GK_ERR_INVALID_ARGUMENT;
+    for (int32_t done = 0; done < r[1]; done += block_rows) {
+      const int32_t n = std::min<int32_t>(block_rows, r[1] - done);
+      const int64_t first_pos = (int64_t)r[2] + done;
+      if (first_pos + n > INT32_MAX) return GK_ERR_UNSUPPORTED;
+      const int32_t lo = window > 0 ? (int32_t)std::max<int64_t>(0, first_pos - window + 1) : 0;
+      blocks.push_back({r[0] + done, n, (int32_t)first_pos, r[3], lo, (int32_t)(first_pos + n)});
+      total_span += blocks.back().hi - lo;
+    }
+  }
+  // Longest KV range of one work item: aim at four CTAs' worth of work per resident CTA slot
+  // (two CTAs per SM), never below 256 tokens, in multiples of the 64 tokens four warps eat.
+  int64_t chunk = split_tokens;
+  if (chunk == 0) {
+    const int64_t want = (int64_t)sm_count * 2 * 4;
+    chunk = round_up(std::max<int64_t>(256, (total_span * kv_heads + want - 1) / want), 64);
+  }
+  chunk = std::max<int64_t>(chunk, 16);
+
+  struct Item { int32_t w[GK_WORK_WORDS]; };
+  std::vector<Item> items;
+  std::vector<std::array<int32_t, GK_COMBINE_WORDS>> merges;
+  int64_t entries = 0;
+  for (const Block& b : blocks) {
+    const int64_t span = b.hi - b.lo;
+    int64_t splits = 1, per = span;
+    if (span > chunk + chunk / 4) {
+      splits = (span + chunk - 1) / chunk;
+      per = round_up((span + splits - 1) / splits, 64);
+      splits = (span + per - 1) / per;
+    }
+    int64_t base = -1;
+    if (splits > 1) {
+      base = entries;
+      entries += splits * b.n_rows * q_heads;
+      if (entries > INT32_MAX) return GK_ERR_CAPACITY;
+      merges.push_back({b.first_row, b.n_rows, (int32_t)base, (int32_t)splits});
+    }
+    for (int64_t s = 0; s < splits; ++s) {
+      Item it{};
+      it.w[0] = b.first_row;
+      it.w[1] = b.n_rows;
+      it.w[2] = b.first_pos;
+      it.w[3] = b.table_row;
+      it.w[4] = (int32_t)(b.lo + s * per);
+      it.w[5] = (int32_t)std::min<int64_t>(b.hi, b.lo + (s + 1) * per);
+      it.w[6] = base < 0 ? -1 : (int32_t)(base + s * b.n_rows * q_heads);
+      it.w[7] = (int32_t)splits;
+      items.push_back(it);
+    }
+  }
+  *n_work_out = (int64_t)items.size();
+  *n_combine_out = (int64_t)merges.size();
+  *partial_entries_out = entries;
+  if (!work_out) return GK_OK;
+  if (work_cap < (int64_t)items.size() || combine_cap < (int64_t)merges.size() || (!merges.empty() && !combine_out))
+    return GK_ERR_CAPACITY;
+  std::stable_sort(items.begin(), items.end(),
+                   [](const Item& a, const Item& b) { return a.w[5] - a.w[4] > b.w[5] - b.w[4]; });
+  for (size_t i = 0; i < items.size(); ++i) std::copy(items[i].w, items[i].w + GK_WORK_WORDS, work_out + i * GK_WORK_WORDS);
+  for (size_t i = 0; i < merges.size(); ++i)
+    std::copy(merges[i].begin(), merges[i].end(), combine_out + i * GK_COMBINE_WORDS);
+  return GK_OK;
+}

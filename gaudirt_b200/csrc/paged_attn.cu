@@ -1,0 +1,467 @@
+// Paged attention over the head-major bf16 KV pool: the decode / short-query kernel and the
+// split-KV combine.
+//
+// One CTA runs one work record (a query block of one sequence x a KV range) for one KV head.
+// All query heads of the KV head's GQA group -- times the rows of the block -- are packed into
+// the 16 rows of an m16n8k16 tile, so every K/V byte is read from HBM once per work item.
+// The KV range is cut into 16-token groups dealt round-robin to the warps; each warp owns a
+// private cp.async ring (16-byte copies, L1 bypass) and never meets a block-wide barrier until
+// the final cross-warp merge.  Slots are looked up in the kernel from the slot table, so there
+// is no gather-index buffer and no gathered K/V copy as in the reference
+// (src/bridge/attention_plan.cpp:246-255, src/bridge/paged_attention.cpp:89-100).
+#include "gk_common.cuh"
+
+#include <math_constants.h>
+
+namespace gk {
+namespace {
+
+constexpr int kGroupTokens = 16;   // tokens one warp consumes per pipeline stage
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* pool_k;
+  const __nv_bfloat16* pool_v;
+  const int32_t* table;
+  const int32_t* work;
+  __nv_bfloat16* out;
+  float* part_ml;
+  float* part_o;
+  int32_t* status;
+  int64_t q_stride, out_stride, slots, table_stride;
+  float scale, softcap;
+  int window, page_shift, q_heads, kv_heads, group;
+};
+
+template <int D, int WARPS, int STAGES>
+struct AttnConfig {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kChunks = D / 8;                         // 16-byte chunks per row
+  static constexpr int kTileBytes = kGroupTokens * kRowBytes;   // K (or V) of one group
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kWarpBytes = STAGES * kStageBytes;
+  static constexpr int kSmemBytes = WARPS * kWarpBytes;
+  static constexpr int kMergeStride = D + 8;                    // floats per merged row
+  static_assert(STAGES >= 3, "the merge buffers reuse the ring and need three stages of room");
+  static_assert(kWarpBytes >= (GK_MAX_PACKED_ROWS * kMergeStride + 2 * GK_MAX_PACKED_ROWS) * 4, "merge area");
+};
+
+template <int D, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnParams p) {
+  using C = AttnConfig<D, WARPS, STAGES>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
+
+  const int4 w0 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item);
+  const int4 w1 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item + 1);
+  const int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, table_row = w0.w;
+  const int kv_begin = w1.x, kv_end = w1.y, partial_base = w1.z;
+  const int G = p.group;
+  const int mv = n_rows * G;                                    // packed rows in use (<= 16)
+
+  // ---- Q fragments (A operand of S = Q K^T), rows g and g+8 of the packed tile ----------
+  uint32_t qf[D / 16][4];
+  int lim0 = 0x7fffffff, lim1 = 0x7fffffff;                     // last visible key per row
+  {
+    const unsigned short* q0 = nullptr;
+    const unsigned short* q1 = nullptr;
+    if (g < mv) {
+      const int r = g / G, gq = g - r * G;
+      lim0 = first_pos + r;
+      q0 = reinterpret_cast<const unsigned short*>(p.q) + (int64_t)(first_row + r) * p.q_stride +
+           (int64_t)(head * G + gq) * D;
+    }
+    if (g + 8 < mv) {
+      const int r = (g + 8) / G, gq = g + 8 - r * G;
+      lim1 = first_pos + r;
+      q1 = reinterpret_cast<const unsigned short*>(p.q) + (int64_t)(first_row + r) * p.q_stride +
+           (int64_t)(head * G + gq) * D;
+    }
+    auto pair = [](const unsigned short* base, int col) -> uint32_t {
+      if (base == nullptr) return 0u;
+      return (uint32_t)__ldg(base + col) | ((uint32_t)__ldg(base + col + 1) << 16);
+    };
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = pair(q0, ks * 16 + 2 * t);
+      qf[ks][1] = pair(q1, ks * 16 + 2 * t);
+      qf[ks][2] = pair(q0, ks * 16 + 8 + 2 * t);
+      qf[ks][3] = pair(q1, ks * 16 + 8 + 2 * t);
+    }
+  }
+
+  const int n_groups = (kv_end - kv_begin + kGroupTokens - 1) / kGroupTokens;
+  const int my_groups = n_groups > warp ? (n_groups - warp + WARPS - 1) / WARPS : 0;
+  const uint32_t ring = smem_u32(smem) + warp * C::kWarpBytes;
+  const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * D;
+  const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * D;
+  const int32_t* trow = p.table + (int64_t)table_row * p.table_stride;
+  const int page_mask = (1 << p.page_shift) - 1;
+
+  // Asynchronously stage the K and V rows of 16-token group `gi` into ring stage `stage`.
+  // Lanes 0..15 resolve one token each; rows past the range are zero-filled so that a masked
+  // probability of 0 never multiplies stale shared memory.
+  auto stage_group = [&](int gi, int stage) {
+    const int tok = kv_begin + gi * kGroupTokens + (lane & 15);
+    int slot = -1;
+    if (tok < kv_end) {
+      slot = __ldg(trow + (tok >> p.page_shift)) + (tok & page_mask);
+      if ((unsigned)slot >= (unsigned)p.slots) {
+        if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
+        slot = -1;
+      }
+    }
+    const uint32_t dst_k = ring + stage * C::kStageBytes, dst_v = dst_k + C::kTileBytes;
+#pragma unroll
+    for (int j = 0; j < kGroupTokens * C::kChunks / 32; ++j) {
+      const int c = j * 32 + lane;
+      const int row = c / C::kChunks, col = c % C::kChunks;
+      const int s = __shfl_sync(0xffffffffu, slot, row);
+      const int64_t src = (int64_t)(s < 0 ? 0 : s) * D + col * 8;
+      const int bytes = s < 0 ? 0 : 16;
+      const uint32_t off = row * C::kRowBytes + (((col & ~7) | ((col ^ row) & 7)) << 4);
+      cp_async_16(dst_k + off, kbase + src, bytes);
+      cp_async_16(dst_v + off, vbase + src, bytes);
+    }
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+
+  const bool capped = p.softcap > 0.f;
+  const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
+  const bool upper = mv > 8;
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < my_groups) stage_group(warp + s * WARPS, s);
+    cp_async_commit();
+  }
+
+  for (int i = 0; i < my_groups; ++i) {
+    cp_async_wait<STAGES - 2>();
+    __syncwarp();
+    {
+      const int nxt = i + STAGES - 1;
+      if (nxt < my_groups) stage_group(warp + nxt * WARPS, nxt % STAGES);
+      cp_async_commit();
+    }
+    const int stage = i % STAGES;
+    const uint32_t ks_base = ring + stage * C::kStageBytes, vs_base = ks_base + C::kTileBytes;
+
+    // ---- S = Q K^T for 16 keys: two n-tiles of 8 keys -----------------------------------
+    float sc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+    for (int kp = 0; kp < D / 32; ++kp) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int row = nt * 8 + (lane & 7), chunk = kp * 4 + (lane >> 3);
+        uint32_t b[4];
+        ldmatrix_x4(b, ks_base + row * C::kRowBytes + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+        mma_bf16_16816(sc[nt], qf[2 * kp], b[0], b[1]);
+        mma_bf16_16816(sc[nt], qf[2 * kp + 1], b[2], b[3]);
+      }
+    }
+
+    // ---- scale, softcap, mask -----------------------------------------------------------
+    const int tok0 = kv_begin + (warp + i * WARPS) * kGroupTokens;
+    if (capped) {
+      const float inv = p.scale / p.softcap;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] = p.softcap * tanhf(sc[nt][e] * inv);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[nt][e] *= to_log2;
+    const bool ragged = tok0 + kGroupTokens > kv_end || tok0 + kGroupTokens > first_pos + 1 ||
+                        (p.window > 0 && tok0 <= first_pos + n_rows - 1 - p.window);
+    if (ragged) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = tok0 + nt * 8 + 2 * t + (e & 1);
+          const int lim = e < 2 ? lim0 : lim1;
+          const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
+          if (!seen) sc[nt][e] = -CUDART_INF_F;
+        }
+    }
+
+    // ---- online softmax: rows g (lower) and g+8 (upper) ---------------------------------
+    float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    const float mn0 = fmaxf(m0, mx0);
+    const float mu0 = mn0 == -CUDART_INF_F ? 0.f : mn0;
+    const float a0 = fast_exp2(m0 - mu0);
+    m0 = mn0;
+    float pr[2][4];
+    pr[0][0] = fast_exp2(sc[0][0] - mu0);
+    pr[0][1] = fast_exp2(sc[0][1] - mu0);
+    pr[1][0] = fast_exp2(sc[1][0] - mu0);
+    pr[1][1] = fast_exp2(sc[1][1] - mu0);
+    l0 = l0 * a0 + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
+    float a1 = 1.f;
+    pr[0][2] = pr[0][3] = pr[1][2] = pr[1][3] = 0.f;
+    if (upper) {
+      float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn1 = fmaxf(m1, mx1);
+      const float mu1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+      a1 = fast_exp2(m1 - mu1);
+      m1 = mn1;
+      pr[0][2] = fast_exp2(sc[0][2] - mu1);
+      pr[0][3] = fast_exp2(sc[0][3] - mu1);
+      pr[1][2] = fast_exp2(sc[1][2] - mu1);
+      pr[1][3] = fast_exp2(sc[1][3] - mu1);
+      l1 = l1 * a1 + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      o[n][0] *= a0;
+      o[n][1] *= a0;
+      o[n][2] *= a1;
+      o[n][3] *= a1;
+    }
+
+    // ---- O += P V, P rounded to bf16 (the reference's boundary before the second product) --
+    uint32_t pa[4];
+    pa[0] = pack_bf16(pr[0][0], pr[0][1]);
+    pa[1] = pack_bf16(pr[0][2], pr[0][3]);
+    pa[2] = pack_bf16(pr[1][0], pr[1][1]);
+    pa[3] = pack_bf16(pr[1][2], pr[1][3]);
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      const int row = ((lane >> 3) & 1) * 8 + (lane & 7), chunk = np * 2 + (lane >> 4);
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vs_base + row * C::kRowBytes + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+      mma_bf16_16816(o[2 * np], pa, b[0], b[1]);
+      mma_bf16_16816(o[2 * np + 1], pa, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- merge the warps' partial states through the (now idle) rings ----------------------
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncwarp();
+  {
+    float* wo = reinterpret_cast<float*>(smem + warp * C::kWarpBytes);
+    float* wml = wo + GK_MAX_PACKED_ROWS * C::kMergeStride;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      *reinterpret_cast<float2*>(wo + g * C::kMergeStride + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+      *reinterpret_cast<float2*>(wo + (g + 8) * C::kMergeStride + n * 8 + 2 * t) = make_float2(o[n][2], o[n][3]);
+    }
+    if (t == 0) {
+      wml[2 * g] = m0;
+      wml[2 * g + 1] = l0;
+      wml[2 * (g + 8)] = m1;
+      wml[2 * (g + 8) + 1] = l1;
+    }
+  }
+  __syncthreads();
+
+  for (int idx = threadIdx.x; idx < mv * (D / 4); idx += WARPS * 32) {
+    const int prow = idx / (D / 4), c4 = idx - prow * (D / 4);
+    float mstar = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float* wml = reinterpret_cast<const float*>(smem + w * C::kWarpBytes) + GK_MAX_PACKED_ROWS * C::kMergeStride;
+      if (wml[2 * prow + 1] > 0.f) mstar = fmaxf(mstar, wml[2 * prow]);
+    }
+    float lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float* wo = reinterpret_cast<const float*>(smem + w * C::kWarpBytes);
+      const float* wml = wo + GK_MAX_PACKED_ROWS * C::kMergeStride;
+      const float lw = wml[2 * prow + 1];
+      if (lw > 0.f) {
+        const float wgt = fast_exp2(wml[2 * prow] - mstar);
+        const float4 v = *reinterpret_cast<const float4*>(wo + prow * C::kMergeStride + c4 * 4);
+        lsum += wgt * lw;
+        acc.x += wgt * v.x;
+        acc.y += wgt * v.y;
+        acc.z += wgt * v.z;
+        acc.w += wgt * v.w;
+      }
+    }
+    const int r = prow / G, gq = prow - r * G;
+    if (partial_base < 0) {
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      uint2 packed;
+      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r) * p.out_stride + (int64_t)(head * G + gq) * D + c4 * 4;
+      *reinterpret_cast<uint2*>(dst) = packed;
+    } else {
+      const int64_t entry = (int64_t)partial_base + (int64_t)r * p.q_heads + head * G + gq;
+      *reinterpret_cast<float4*>(p.part_o + entry * D + c4 * 4) = acc;
+      if (c4 == 0) *reinterpret_cast<float2*>(p.part_ml + entry * 2) = make_float2(mstar, lsum);
+    }
+  }
+}
+
+// Merge the split states of each combine record in split order and write bf16(O / l).
+// One warp per (row, query head) entry; lanes stride over head_dim in float4 steps.
+template <int D>
+__global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __restrict__ part_ml,
+                                                                const float* __restrict__ part_o,
+                                                                const int32_t* __restrict__ combine,
+                                                                __nv_bfloat16* __restrict__ out,
+                                                                int64_t out_stride, int q_heads) {
+  const int4 rec = __ldg(reinterpret_cast<const int4*>(combine) + blockIdx.x);
+  const int first_row = rec.x, n_rows = rec.y, base = rec.z, n_splits = rec.w;
+  const int entries = n_rows * q_heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = warp; e < entries; e += 4) {
+    float mstar = -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) {
+      const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml) + (int64_t)base + (int64_t)s * entries + e);
+      if (ml.y > 0.f) mstar = fmaxf(mstar, ml.x);
+    }
+    constexpr int kVec = D / 128 > 0 ? D / 128 : 1;              // float4 per lane
+    float4 acc[kVec];
+#pragma unroll
+    for (int v = 0; v < kVec; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.f;
+    const bool active = lane * 4 < D;
+    for (int s = 0; s < n_splits; ++s) {
+      const int64_t entry = (int64_t)base + (int64_t)s * entries + e;
+      const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml) + entry);
+      if (!(ml.y > 0.f)) continue;
+      const float wgt = fast_exp2(ml.x - mstar);
+      lsum += wgt * ml.y;
+      if (active) {
+#pragma unroll
+        for (int v = 0; v < kVec; ++v) {
+          const float4 x = __ldg(reinterpret_cast<const float4*>(part_o + entry * D) + v * 32 + lane);
+          acc[v].x += wgt * x.x;
+          acc[v].y += wgt * x.y;
+          acc[v].z += wgt * x.z;
+          acc[v].w += wgt * x.w;
+        }
+      }
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    const int r = e / q_heads, h = e - r * q_heads;
+    if (active) {
+#pragma unroll
+      for (int v = 0; v < kVec; ++v) {
+        uint2 packed;
+        packed.x = pack_bf16(acc[v].x * inv, acc[v].y * inv);
+        packed.y = pack_bf16(acc[v].z * inv, acc[v].w * inv);
+        __nv_bfloat16* dst = out + (int64_t)(first_row + r) * out_stride + (int64_t)h * D + (v * 32 + lane) * 4;
+        *reinterpret_cast<uint2*>(dst) = packed;
+      }
+    }
+  }
+}
+
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+
+template <int D>
+int launch_attn(const AttnParams& p, int64_t n_work, cudaStream_t stream) {
+  using C = AttnConfig<D, kWarps, kStages>;
+  auto kernel = paged_attn_kernel<D, kWarps, kStages>;
+  // The opt-in for more than 48 KB of dynamic shared memory is per device.
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
+  if (device < 0 || device >= 64 || !configured[device]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return check_launch();
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  const int64_t blocks = n_work * p.kv_heads;
+  kernel<<<(unsigned)blocks, kWarps * 32, C::kSmemBytes, stream>>>(p);
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace gk
+
+extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                  int64_t slots, const int32_t* table, int64_t table_stride, int page_tokens,
+                                  const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
+                                  float* part_ml, float* part_o, float scale, float softcap, int window,
+                                  int q_heads, int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
+  if (n_work == 0) return GK_OK;
+  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 ||
+      page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
+      !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (q_heads % kv_heads != 0 || q_heads / kv_heads > GK_MAX_PACKED_ROWS ||
+      (head_dim != 64 && head_dim != 128 && head_dim != 256))
+    return GK_ERR_UNSUPPORTED;
+  if (n_work * kv_heads > 0x7fffffffLL) return GK_ERR_UNSUPPORTED;
+  // K/V rows are moved in 16-byte pieces and the result is stored 8 bytes at a time.
+  if ((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v)) & 15) return GK_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(out) & 7) || (out_row_stride & 3) || (reinterpret_cast<uintptr_t>(work) & 15) ||
+      (reinterpret_cast<uintptr_t>(q) & 1))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (part_ml && ((reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15)))
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.pool_k = static_cast<const __nv_bfloat16*>(pool_k);
+  p.pool_v = static_cast<const __nv_bfloat16*>(pool_v);
+  p.table = table;
+  p.work = work;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_ml = part_ml;
+  p.part_o = part_o;
+  p.status = status;
+  p.q_stride = q_row_stride;
+  p.out_stride = out_row_stride;
+  p.slots = slots;
+  p.table_stride = table_stride;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.window = window;
+  p.page_shift = __builtin_ctz((unsigned)page_tokens);
+  p.q_heads = q_heads;
+  p.kv_heads = kv_heads;
+  p.group = q_heads / kv_heads;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (head_dim) {
+    case 64: return gk::launch_attn<64>(p, n_work, s);
+    case 128: return gk::launch_attn<128>(p, n_work, s);
+    default: return gk::launch_attn<256>(p, n_work, s);
+  }
+}
+
+extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
+                                          int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
+                                          int head_dim, gk_stream_t stream) {
+  if (n_combine == 0) return GK_OK;
+  if (!part_ml || !part_o || !combine || !out || n_combine < 0 || n_combine > 0x7fffffffLL || q_heads <= 0)
+    return GK_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(out) & 7) || (out_row_stride & 3) || (reinterpret_cast<uintptr_t>(combine) & 15) ||
+      (reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15))
+    return GK_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  auto* o = static_cast<__nv_bfloat16*>(out);
+  switch (head_dim) {
+    case 64: gk::paged_attn_combine_kernel<64><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    case 128: gk::paged_attn_combine_kernel<128><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    case 256: gk::paged_attn_combine_kernel<256><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    default: return GK_ERR_UNSUPPORTED;
+  }
+  return gk::check_launch();
+}

@@ -1,0 +1,155 @@
+/*
+ * gaudirt_b200 -- C ABI of the B200 (sm_100a) paged KV-store / paged-attention path.
+ *
+ * This is the drop-in boundary: plain C, device pointers + sizes + a CUDA stream.  No entry
+ * point allocates device memory, synchronises the device or throws; each returns a gk_status
+ * (0 = success) and enqueues its work on `stream`.  Validation that needs tensor metadata,
+ * allocation and error translation belong to the caller's framework layer.
+ *
+ * Citations are path:line inside the reference project (tracycam/GaudiRT); each entry point
+ * names the reference interface it replaces.
+ *
+ * Memory layouts (all bf16 unless stated):
+ *   pool      one layer of the combined KV pool, [2, kv_heads, slots, head_dim] contiguous
+ *             (src/bridge/paged_kv_pool.cpp:15-41).  pool_k = &pool[0], pool_v = &pool[1];
+ *             element (h, slot, c) of either half lives at (h*slots + slot)*head_dim + c.
+ *   q / out   [rows, q_heads*head_dim], row stride given in elements.
+ *   k / v     [rows, kv_heads*head_dim], row stride given in elements (column slices of a
+ *             packed QKV projection are allowed).
+ *   table     int32 slot table.  Row `t` starts at table + t*table_stride; entry j is the
+ *             slot of token j*page_tokens, and the page_tokens tokens of that page occupy
+ *             consecutive slots.  page_tokens == 1 is the reference's request-to-token
+ *             `mapping[requests, context]` itself (src/bridge/paged_metadata.cpp:104-140).
+ */
+#ifndef GAUDIRT_B200_H_
+#define GAUDIRT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* gk_stream_t; /* cudaStream_t */
+
+#if defined(__GNUC__)
+#define GK_API __attribute__((visibility("default")))
+#else
+#define GK_API
+#endif
+
+enum gk_status {
+  GK_OK = 0,
+  GK_ERR_INVALID_ARGUMENT = 1,  /* null pointer, negative size, misaligned pointer or stride   */
+  GK_ERR_UNSUPPORTED = 2,       /* geometry outside what the kernels implement: fail fast      */
+  GK_ERR_CUDA = 3,              /* the CUDA runtime refused the launch; see gk_last_cuda_error */
+  GK_ERR_CAPACITY = 4,          /* an output array or fixed scratch area is too small          */
+  GK_ERR_METADATA = 5           /* host metadata validation failed; see the message accessor   */
+};
+
+/* Bits a kernel may OR into the caller's int32 device status word (never cleared by kernels). */
+enum gk_device_status {
+  GK_DEV_BAD_SLOT = 1,          /* a slot outside [0, slots) was met: the access was skipped   */
+  GK_DEV_BAD_TABLE = 2,         /* a table entry outside [0, slots) was met: slot 0 was read   */
+  GK_DEV_WAIT_EXPIRED = 4       /* a bounded wait ran out                                      */
+};
+
+GK_API const char* gk_status_string(int status);
+GK_API int gk_abi_version(void);
+/* cudaError_t of the last failed launch on the calling thread (0 if none). */
+GK_API int gk_last_cuda_error(void);
+
+/* Size of a work record and of a combine record, in int32 words. */
+#define GK_WORK_WORDS 8
+#define GK_COMBINE_WORDS 4
+/* Largest number of packed query rows (rows of one sequence x query heads of one KV head)
+ * one work item may carry. */
+#define GK_MAX_PACKED_ROWS 16
+/* KV tile the independent tiled CPU reference must use for this implementation
+ * (_C._paged_attn_kv_tile, src/bridge/generic_private_use1.cpp; 512 in the reference). */
+#define GK_REFERENCE_KV_TILE 512
+
+/* ---- pool -------------------------------------------------------------------------------
+ * Replaces the geometry checks of allocate_paged_kv (src/bridge/paged_kv_pool.cpp:15-41).
+ * Writes the byte size of [layers, 2, kv_heads, slots, head_dim] bf16.  The reference's
+ * 131072-slot descriptor cap and descriptor tail do not exist here. */
+GK_API int gk_paged_kv_pool_bytes(int64_t layers, int64_t slots, int64_t kv_heads, int64_t head_dim,
+                           uint64_t* bytes_out);
+
+/* ---- metadata (host) --------------------------------------------------------------------
+ * Replaces the host half of the PagedMetadata constructor (src/bridge/paged_metadata.cpp:82-140):
+ * range checks, mapping[request, position] == location, unique output slots, visible prefix
+ * fully mapped and not aliased by an output slot.  Host arrays only.
+ *   seq_out   [rows*4] receives {first_row, n_rows, first_position, request} per sequence
+ *             (maximal runs of one request with consecutive positions).
+ *   page_tokens_out  largest power of two <= 128 such that every visible prefix is made of
+ *             slot-contiguous pages of that many tokens (1 if none).
+ * On GK_ERR_METADATA, gk_metadata_error() returns the reference's message. */
+GK_API int gk_paged_metadata_validate(const int32_t* locations, const int32_t* requests,
+                               const int32_t* positions, int64_t rows, const int32_t* mapping,
+                               int64_t n_requests, int64_t context, int64_t slots,
+                               int32_t* seq_out, int64_t* n_seq_out, int32_t* page_tokens_out);
+GK_API const char* gk_metadata_error(void);
+
+/* ---- attention plan (host) --------------------------------------------------------------
+ * Replaces PagedMetadata::attention_plan_for (src/bridge/attention_plan.cpp:146-361) and the
+ * gk_attn_tile_indices_i32_v1 gather-index kernel: the schedule is a list of work records
+ * (query block x KV range) balanced over the SMs; slots are looked up in the kernel.
+ *   seq       [n_seq*4] as written by gk_paged_metadata_validate.
+ *   window    sliding window (-1 = none): keys below position-window+1 are never scheduled.
+ *   split_tokens  0 = choose from sm_count; otherwise the longest KV range of one work item.
+ *   work_out  [work_cap*GK_WORK_WORDS] {first_row, n_rows, first_position, table_row,
+ *             kv_begin, kv_end, partial_base (-1 = writes the output itself), n_splits},
+ *             longest first.  combine_out [combine_cap*GK_COMBINE_WORDS] {first_row, n_rows,
+ *             partial_base, n_splits} for every query block cut into more than one range.
+ *   partial_entries_out  number of (row, query head) entries of fp32 split state needed.
+ * Pass work_out == NULL to obtain the three counts only. */
+GK_API int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_heads, int kv_heads,
+                            int head_dim, int window, int sm_count, int split_tokens,
+                            int32_t* work_out, int64_t work_cap, int64_t* n_work_out,
+                            int32_t* combine_out, int64_t combine_cap, int64_t* n_combine_out,
+                            int64_t* partial_entries_out);
+
+/* ---- KV store ---------------------------------------------------------------------------
+ * Replaces gk_kv_store_head_major_bf16_v1 / launch_layer_kv_store
+ * (src/bridge/paged_attention_tiles.cpp:37-55,236-260): for r < rows, h < kv_heads
+ *   pool_k[(h*slots + locations[r])*d ...] = k[r*k_row_stride + h*d ...]   (same for v).
+ * A bit copy; slots not named in `locations` are untouched.  `locations` must not repeat a
+ * slot.  Rows whose slot is outside [0, slots) are skipped and GK_DEV_BAD_SLOT is set in
+ * *status (status may be NULL).  Any row stride / 2-byte alignment is accepted; 16-byte
+ * aligned inputs take the vector path. */
+GK_API int gk_kv_store_head_major_bf16(const void* k, const void* v, int64_t k_row_stride,
+                                int64_t v_row_stride, const int32_t* locations, int64_t rows,
+                                void* pool_k, void* pool_v, int64_t slots, int kv_heads,
+                                int head_dim, int32_t* status, gk_stream_t stream);
+
+/* ---- paged attention --------------------------------------------------------------------
+ * Replaces the fused single-tile recipe and the multi-tile chunk recipes
+ * (src/bridge/paged_attention.cpp:39-127, src/bridge/paged_attention_tiles.cpp:57-195):
+ *   S = Q K^T (fp32) ; s = scale*S ; softcap c*tanh(s/c) if softcap > 0 ;
+ *   row at position p sees keys max(0, p-window+1) .. p ; P = softmax, rounded to bf16
+ *   before P V ; fp32 accumulation ; out = bf16(O / l).
+ * Query head h reads KV head h / (q_heads/kv_heads).  One CTA runs one work record for one
+ * KV head; records with partial_base >= 0 leave (m, l, O) fp32 split state in the workspace
+ * for gk_paged_attn_combine_bf16, the others write `out` directly.
+ *   part_ml   fp32 [partial_entries*2] (m in log2 units, l), part_o fp32 [partial_entries*d].
+ * head_dim in {64, 128, 256}; q_heads/kv_heads <= GK_MAX_PACKED_ROWS. */
+GK_API int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                       const void* pool_v, int64_t slots, const int32_t* table,
+                       int64_t table_stride, int page_tokens, const int32_t* work,
+                       int64_t n_work, void* out, int64_t out_row_stride, float* part_ml,
+                       float* part_o, float scale, float softcap, int window, int q_heads,
+                       int kv_heads, int head_dim, int32_t* status, gk_stream_t stream);
+
+/* Replaces gk_attn_online_merge_f32_v1 + gk_attn_online_finalize_bf16_v1
+ * (src/bridge/paged_attention_tiles.cpp:173-188): merges the n_splits partial states of every
+ * combine record in split order (deterministic) and writes bf16(O / l); l == 0 gives 0. */
+GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
+                               int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
+                               int head_dim, gk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GAUDIRT_B200_H_ */

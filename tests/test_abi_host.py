@@ -1,0 +1,115 @@
+"""CPU-only checks of the C ABI: the library loads, exports every declared symbol, and its
+host-side entry points (metadata validation, schedule) agree with the oracle's rules."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle
+from gaudirt_b200 import abi
+from tests import abi_harness as H
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    header = open(os.path.join(ROOT, "include", "gaudirt_b200.h")).read()
+    declared = set(re.findall(r"GK_API\s+[\w\s\*]+?\b(gk_\w+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = abi.lib()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert declared == set(abi.PROTOTYPES), declared ^ set(abi.PROTOTYPES)
+    assert lib.gk_abi_version() == 1
+    assert lib.gk_status_string(0) == b"ok"
+
+
+def test_pool_bytes_and_geometry_limits():
+    import ctypes as C
+    out = C.c_uint64(0)
+    assert abi.lib().gk_paged_kv_pool_bytes(32, 1153408, 8, 128, C.byref(out)) == 0
+    assert out.value == 32 * 2 * 8 * 1153408 * 128 * 2
+    for bad in ((1, 16, 8, 96), (0, 16, 8, 128), (1, 0, 8, 128), (1, 16, 257, 128)):
+        assert abi.lib().gk_paged_kv_pool_bytes(*bad, C.byref(out)) == 2
+
+
+def test_metadata_validation_matches_oracle_rules():
+    mapping = np.arange(1, 1 + 3 * 8).reshape(3, 8).astype(np.int32)
+    good = ([3, 4, 5, 12], [0, 0, 0, 1], [2, 3, 4, 3])
+    seq, page = H.validate(*good, mapping, 64)
+    assert [tuple(s[:3]) for s in seq] == oracle.validate_paged_metadata(*good, mapping, 64)
+    assert list(seq[:, 3]) == [0, 1] and page == 128   # every visible prefix is one contiguous run
+    holes = mapping.copy(); holes[0, 1] = -1
+    alias = mapping.copy(); alias[1, 0] = 3
+    for args, table, text in (
+            (([9], [0], [2]), mapping, "does not match"),
+            (([3, 3], [0, 0], [2, 2]), mapping, "duplicate output KV slot"),
+            (([3], [0], [9]), mapping, "out of range"),
+            (([3], [0], [2]), holes, "missing KV slot"),
+            (([3, 12], [0, 1], [2, 3]), alias, "aliases another visible prefix")):
+        with pytest.raises(abi.GkError, match=text):
+            H.validate(*args, table, 64)
+        with pytest.raises(ValueError, match=text):
+            oracle.validate_paged_metadata(*args, table, 64)
+
+
+def test_page_detection():
+    # pages of 16 contiguous slots, placed at arbitrary (unaligned) bases
+    bases = np.array([[70, 5, 300], [200, 40, 130]])
+    mapping = (bases[:, :, None] + np.arange(16)[None, None, :]).reshape(2, 48).astype(np.int32)
+    seq, page = H.validate([mapping[0, 47], mapping[1, 20]], [0, 1], [47, 20], mapping, 400)
+    assert page == 16
+    mapping[1, 18] = 399                                    # break inside a visible page
+    _, page = H.validate([mapping[0, 47], mapping[1, 20]], [0, 1], [47, 20], mapping, 400)
+    assert page == 1
+    full = np.arange(512, dtype=np.int32).reshape(1, 512)
+    assert H.validate([300], [0], [300], full, 512)[1] == 128
+
+
+def _coverage(work, combine, seq, q_heads, window):
+    """Every (row, key) pair that must be attended is covered exactly once."""
+    spans = {}
+    for first_row, n_rows, first_pos, table_row, lo, hi, base, splits in work:
+        assert 0 < n_rows and lo < hi <= first_pos + n_rows
+        spans.setdefault((first_row, n_rows, first_pos, table_row), []).append((lo, hi, base, splits))
+    merged = {(r, n): (b, s) for r, n, b, s in combine}
+    rows_seen = set()
+    for (first_row, n_rows, first_pos, _), parts in spans.items():
+        parts.sort()
+        lo0 = max(0, first_pos - window + 1) if window > 0 else 0
+        assert parts[0][0] == lo0 and parts[-1][1] == first_pos + n_rows
+        for a, b in zip(parts[:-1], parts[1:]):
+            assert a[1] == b[0]
+        if len(parts) == 1:
+            assert parts[0][2] == -1 and (first_row, n_rows) not in merged
+        else:
+            base, splits = merged[(first_row, n_rows)]
+            assert splits == len(parts)
+            assert [p[2] for p in parts] == [base + i * n_rows * q_heads for i in range(splits)]
+        for r in range(first_row, first_row + n_rows):
+            assert r not in rows_seen
+            rows_seen.add(r)
+    return rows_seen
+
+
+@pytest.mark.parametrize("split", [0, 64, 200, 4096])
+@pytest.mark.parametrize("window", [-1, 100])
+def test_schedule_covers_every_row_and_key_once(split, window):
+    seq = np.array([[0, 1, 4095, 0], [1, 37, 100, 1], [38, 1, 0, 2], [39, 1, 20000, 3], [40, 3, 0, 4]], np.int32)
+    for q_heads, kv_heads in ((32, 8), (8, 8), (64, 8), (7, 1)):
+        work, combine, entries = H.plan(seq, q_heads, kv_heads, 128, window=window, split_tokens=split)
+        rows = _coverage(work, combine, seq, q_heads, window)
+        assert rows == set(range(43))
+        spans = work[:, 5] - work[:, 4]
+        assert (np.diff(spans) <= 0).all(), "longest first"
+        assert entries == sum(n * q_heads * s for _, n, _, s in combine)
+        if split:
+            assert spans.max() <= max(split, 16) * 1.25 + 64
+
+
+def test_schedule_rejects_unsupported_geometry():
+    seq = np.array([[0, 1, 5, 0]], np.int32)
+    for q_heads, kv_heads, d in ((32, 8, 96), (34, 1, 128), (9, 2, 128)):
+        with pytest.raises(abi.GkError, match="unsupported"):
+            H.plan(seq, q_heads, kv_heads, d)
