@@ -1,4 +1,58 @@
-"""B200-native paged KV-store / paged-attention path behind the GaudiRT operator surface."""
-from . import abi  # noqa: F401
+"""B200-native paged KV-store / paged-attention path behind the GaudiRT operator surface.
 
-__all__ = ["abi"]
+Importing the package loads the two in-tree native libraries (``python -m gaudirt_b200.build``
+makes them) and exposes the reference's Python-visible names for this path:
+
+* ``torch.ops.gaudirt.paged_attn`` / ``_paged_attn_validated`` and
+  ``torch.classes.gaudirt.PagedMetadata`` (reference: ``src/bridge/generic_private_use1.cpp:430-489``);
+* ``gaudirt_b200._C._allocate_paged_kv`` / ``_C._paged_attn_kv_tile`` (reference: the ``gaudirt._C``
+  bindings of the same names);
+* fake-tensor registrations with the reference's shape contracts (``python/gaudirt/__init__.py:136-153``).
+
+There is no CPU or pure-PyTorch fallback: a missing library is an import error.
+"""
+from __future__ import annotations
+
+import os
+import types
+
+import torch
+
+from . import abi, build
+
+__all__ = ["abi", "build", "_C", "PagedMetadata", "synchronize"]
+
+if not os.path.exists(build.OPS_SO):
+    raise ImportError(f"{build.OPS_SO} is missing: run `python -m gaudirt_b200.build` (needs nvcc and g++)")
+abi.lib()
+torch.ops.load_library(build.OPS_SO)
+
+PagedMetadata = torch.classes.gaudirt.PagedMetadata
+
+_C = types.SimpleNamespace(
+    _allocate_paged_kv=lambda layers, slots, heads, head_dim: torch.ops.gaudirt._allocate_paged_kv(
+        layers, slots, heads, head_dim),
+    _paged_attn_kv_tile=lambda rows: int(torch.ops.gaudirt._paged_attn_kv_tile(rows)),
+    _take_device_status=lambda: int(torch.ops.gaudirt._take_device_status()),
+)
+
+
+def synchronize() -> None:
+    torch.cuda.synchronize()
+
+
+@torch.library.register_fake("gaudirt::paged_attn")
+def _fake_paged_attn(query, key, value, key_pool, value_pool, metadata, head_dim, scale,
+                     softcap=0.0, sliding_window=-1):
+    torch._check(key.shape[0] == query.shape[0])
+    torch._check(value.shape[0] == query.shape[0])
+    return torch.empty_like(query, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake("gaudirt::_paged_attn_validated")
+def _fake_paged_attn_validated(query, key, value, key_pool, value_pool, locations, requests, positions,
+                               mapping, header, head_dim, scale, softcap=0.0, sliding_window=-1):
+    torch._check(key.shape[0] == query.shape[0])
+    torch._check(value.shape[0] == query.shape[0])
+    torch._check(locations.shape[0] == query.shape[0])
+    return torch.empty_like(query, memory_format=torch.contiguous_format)

@@ -23,7 +23,7 @@ PROTOTYPES = {
     "gk_metadata_error": (C.c_char_p, []),
     "gk_attention_plan_build": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, vp, i64, i64p, vp, i64, i64p, i64p]),
     "gk_kv_store_head_major_bf16": (i32, [vp, vp, i64, i64, vp, i64, vp, vp, i64, i32, i32, vp, vp]),
-    "gk_paged_attn_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i32, vp, i64, vp, i64, vp, vp, f32, f32, i32,
+    "gk_paged_attn_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, vp, vp, f32, f32, i32,
                                  i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_bf16": (i32, [vp, vp, vp, i64, vp, i64, i32, i32, vp]),
 }

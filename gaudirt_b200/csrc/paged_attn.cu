@@ -24,12 +24,13 @@ struct AttnParams {
   const __nv_bfloat16* pool_k;
   const __nv_bfloat16* pool_v;
   const int32_t* table;
+  const int32_t* table_rows;
   const int32_t* work;
   __nv_bfloat16* out;
   float* part_ml;
   float* part_o;
   int32_t* status;
-  int64_t q_stride, out_stride, slots, table_stride;
+  int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group;
 };
@@ -98,7 +99,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
   const uint32_t ring = smem_u32(smem) + warp * C::kWarpBytes;
   const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * D;
   const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * D;
-  const int32_t* trow = p.table + (int64_t)table_row * p.table_stride;
+  const int32_t* trow =
+      p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
   const int page_mask = (1 << p.page_shift) - 1;
 
   // Asynchronously stage the K and V rows of 16-token group `gi` into ring stage `stage`.
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
     const int tok = kv_begin + gi * kGroupTokens + (lane & 15);
     int slot = -1;
     if (tok < kv_end) {
-      slot = __ldg(trow + (tok >> p.page_shift)) + (tok & page_mask);
+      slot = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
       if ((unsigned)slot >= (unsigned)p.slots) {
         if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
         slot = -1;
@@ -397,12 +399,13 @@ int launch_attn(const AttnParams& p, int64_t n_work, cudaStream_t stream) {
 }  // namespace gk
 
 extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
-                                  int64_t slots, const int32_t* table, int64_t table_stride, int page_tokens,
+                                  int64_t slots, const int32_t* table, int64_t table_stride,
+                                  int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
                                   const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
                                   float* part_ml, float* part_o, float scale, float softcap, int window,
                                   int q_heads, int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
   if (n_work == 0) return GK_OK;
-  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 ||
+  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 || table_entry_stride <= 0 ||
       page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
       !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
     return GK_ERR_INVALID_ARGUMENT;
@@ -422,6 +425,8 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
   p.pool_k = static_cast<const __nv_bfloat16*>(pool_k);
   p.pool_v = static_cast<const __nv_bfloat16*>(pool_v);
   p.table = table;
+  p.table_rows = table_rows;
+  p.entry_stride = table_entry_stride;
   p.work = work;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.part_ml = part_ml;

@@ -1,0 +1,478 @@
+// PyTorch operator layer: the `gaudirt` operator namespace and the PagedMetadata class of the
+// reference (src/bridge/generic_private_use1.cpp:430-489, src/bridge/paged_metadata.hpp), bound
+// to CUDA tensors and to the C ABI of include/gaudirt_b200.h.  This layer owns validation,
+// allocation and error translation; the kernels behind the ABI never allocate or synchronise.
+//
+// Error behaviour follows the reference: TORCH_CHECK -> RuntimeError with a "GaudiRT ..."
+// message raised before any pool write; there is no fallback path.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/custom_class.h>
+#include <torch/library.h>
+
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <tuple>
+#include <utility>
+#include <vector>
+
+#include "gaudirt_b200.h"
+
+namespace gaudirt_b200 {
+namespace {
+
+gk_stream_t stream_of(const c10::cuda::CUDAStream& s) { return reinterpret_cast<gk_stream_t>(s.stream()); }
+
+void check_status(int status, const char* where) {
+  if (status == GK_OK) return;
+  if (status == GK_ERR_METADATA) TORCH_CHECK(false, gk_metadata_error());
+  TORCH_CHECK(false, "GaudiRT: ", where, ": ", gk_status_string(status),
+              status == GK_ERR_CUDA ? " (cudaError " + std::to_string(gk_last_cuda_error()) + ")" : std::string());
+}
+
+// One int32 status word per device; kernels OR gk_device_status bits into it.
+at::Tensor& device_status(c10::DeviceIndex device) {
+  static std::mutex mutex;
+  static std::vector<at::Tensor> words(64);
+  std::lock_guard<std::mutex> lock(mutex);
+  TORCH_CHECK(device >= 0 && device < 64, "GaudiRT: device index out of range");
+  if (!words[device].defined())
+    words[device] = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(c10::Device(c10::kCUDA, device)));
+  return words[device];
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention plan carried by its device tensor (as in src/bridge/attention_plan.cpp:132-140,
+// 319-322: the tensor's storage context owns the host-side schedule, so the tensor's lifetime
+// is the plan's lifetime and a foreign or stale tensor is rejected).
+// ---------------------------------------------------------------------------------------------
+struct AttentionPlan {
+  at::Tensor buffer;      // int32 device words: work records, then combine records
+  at::Tensor part_ml;     // fp32 split state (m, l) per partial entry
+  at::Tensor part_o;      // fp32 split state O per partial entry
+  at::Tensor table;       // int32 slot table the work records index
+  at::Tensor table_rows;  // optional int32 row indirection (device-resident request ids)
+  void* address = nullptr;
+  cudaStream_t stream = nullptr;
+  c10::DeviceIndex device = -1;
+  int64_t rows = 0, slots = 0, query_heads = 0, kv_heads = 0, head_dim = 0, sliding_window = -1;
+  int64_t n_work = 0, n_combine = 0, combine_offset = 0, table_stride = 0, entry_stride = 1;
+  int page_tokens = 1;
+};
+
+void release_plan(void* context) { delete static_cast<AttentionPlan*>(context); }
+
+at::Tensor wrap_plan(std::unique_ptr<AttentionPlan> plan) {
+  const auto bytes = static_cast<size_t>(plan->buffer.nbytes());
+  const auto device = plan->buffer.device();
+  void* address = plan->buffer.data_ptr();
+  plan->address = address;
+  c10::DataPtr data(address, plan.release(), &release_plan, device);
+  auto storage = c10::make_intrusive<c10::StorageImpl>(c10::StorageImpl::use_byte_size_t(), bytes, std::move(data),
+                                                       /*allocator=*/nullptr, /*resizable=*/false);
+  auto tensor = at::detail::make_tensor<c10::TensorImpl>(std::move(storage), c10::DispatchKeySet(c10::DispatchKey::CUDA),
+                                                         caffe2::TypeMeta::Make<int32_t>());
+  tensor.unsafeGetTensorImpl()->set_sizes_contiguous({static_cast<int64_t>(bytes / sizeof(int32_t))});
+  return tensor;
+}
+
+const AttentionPlan& plan_of(const at::Tensor& tensor) {
+  TORCH_CHECK(tensor.defined() && tensor.is_cuda(), "GaudiRT attention: expected a device metadata plan");
+  const auto* plan = tensor.storage().data_ptr().cast_context<AttentionPlan>(&release_plan);
+  TORCH_CHECK(plan && tensor.data_ptr() == plan->address && tensor.device().index() == plan->device,
+              "GaudiRT attention: invalid or expired metadata plan");
+  return *plan;
+}
+
+std::vector<int32_t> host_i32(const at::Tensor& t) {
+  std::vector<int32_t> out(static_cast<size_t>(t.numel()));
+  if (t.scalar_type() == at::kInt) {
+    std::memcpy(out.data(), t.data_ptr<int32_t>(), out.size() * sizeof(int32_t));
+  } else {
+    const int64_t* src = t.data_ptr<int64_t>();
+    for (size_t i = 0; i < out.size(); ++i) {
+      TORCH_CHECK(src[i] >= INT32_MIN && src[i] <= INT32_MAX, "GaudiRT: paged metadata index is out of range");
+      out[i] = static_cast<int32_t>(src[i]);
+    }
+  }
+  return out;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// PagedMetadata
+// ---------------------------------------------------------------------------------------------
+class PagedMetadata : public torch::CustomClassHolder {
+ public:
+  // Host constructor (src/bridge/paged_metadata.cpp:82-174): validates on the host, then uploads
+  // locations / requests / positions / mapping / header with ONE pinned staging buffer and one
+  // asynchronous copy on the current stream.
+  PagedMetadata(const at::Tensor& locations, const at::Tensor& requests, const at::Tensor& positions,
+                const at::Tensor& mapping, int64_t slots) {
+    for (const auto& t : {locations, requests, positions, mapping})
+      TORCH_CHECK(t.device().is_cpu() && t.is_contiguous() && (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong),
+                  "GaudiRT: paged metadata must be contiguous CPU int32 or int64");
+    TORCH_CHECK(locations.dim() == 1 && requests.dim() == 1 && positions.dim() == 1 && mapping.dim() == 2 &&
+                    locations.size(0) == requests.size(0) && locations.size(0) == positions.size(0),
+                "GaudiRT: invalid paged metadata ranks or row counts");
+    const int64_t m = locations.size(0), n_req = mapping.size(0), context = mapping.size(1);
+    const auto loc = host_i32(locations), req = host_i32(requests), pos = host_i32(positions), map = host_i32(mapping);
+    sequences_.resize(static_cast<size_t>(std::max<int64_t>(m, 1)) * 4);
+    int64_t n_seq = 0;
+    int32_t page = 1;
+    check_status(gk_paged_metadata_validate(loc.data(), req.data(), pos.data(), m, map.data(), n_req, context, slots,
+                                            sequences_.data(), &n_seq, &page),
+                 "paged metadata");
+    sequences_.resize(static_cast<size_t>(n_seq) * 4);
+    page_tokens_ = page;
+    rows_ = m;
+    slots_ = slots;
+    request_count_ = n_req;
+    context_ = context;
+
+    const auto device = c10::Device(c10::kCUDA, at::cuda::current_device());
+    const int64_t words = 3 * m + n_req * context + 1;
+    auto staging = at::empty({words}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+    int32_t* host = staging.data_ptr<int32_t>();
+    std::memcpy(host, loc.data(), m * 4);
+    std::memcpy(host + m, req.data(), m * 4);
+    std::memcpy(host + 2 * m, pos.data(), m * 4);
+    std::memcpy(host + 3 * m, map.data(), n_req * context * 4);
+    host[words - 1] = static_cast<int32_t>(m);
+    auto all = staging.to(device, /*non_blocking=*/true);
+    locations_ = all.narrow(0, 0, m);
+    requests_ = all.narrow(0, m, m);
+    positions_ = all.narrow(0, 2 * m, m);
+    mapping_ = all.narrow(0, 3 * m, n_req * context).view({n_req, context});
+    header_ = all.narrow(0, words - 1, 1);
+  }
+
+  // Device-input constructor (src/bridge/paged_metadata.cpp:176-324): `batch_requests[batch]`
+  // indexes a persistent device table `mapping[max_requests, max_context]`; `prefixes` and
+  // `lengths` are the host lists of cached length and new-token count per sequence.
+  PagedMetadata(const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
+                const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
+                const at::Tensor& token_ids, int64_t vocabulary) {
+    for (const auto& t : {locations, batch_requests, positions, mapping})
+      TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong),
+                  "GaudiRT: device paged metadata must be contiguous CUDA int32 or int64");
+    TORCH_CHECK(locations.dim() == 1 && batch_requests.dim() == 1 && positions.dim() == 1 && mapping.dim() == 2 &&
+                    locations.size(0) == positions.size(0) && !prefixes.empty() && prefixes.size() == lengths.size() &&
+                    batch_requests.size(0) == static_cast<int64_t>(prefixes.size()),
+                "GaudiRT: invalid paged metadata ranks or row counts");
+    TORCH_CHECK(slots > 0 && slots <= INT32_MAX && mapping.numel() <= INT32_MAX && mapping.numel() > 0,
+                "GaudiRT: paged metadata dimensions outside supported range");
+    int64_t row = 0;
+    for (size_t i = 0; i < prefixes.size(); ++i) {
+      TORCH_CHECK(prefixes[i] >= 0 && lengths[i] > 0 && prefixes[i] + lengths[i] <= mapping.size(1),
+                  "GaudiRT: paged metadata index is out of range");
+      sequences_.insert(sequences_.end(), {static_cast<int32_t>(row), static_cast<int32_t>(lengths[i]),
+                                           static_cast<int32_t>(prefixes[i]), static_cast<int32_t>(i)});
+      row += lengths[i];
+    }
+    TORCH_CHECK(row == locations.size(0), "GaudiRT: invalid paged metadata ranks or row counts");
+    rows_ = row;
+    slots_ = slots;
+    request_count_ = mapping.size(0);
+    context_ = mapping.size(1);
+    locations_ = locations.to(at::kInt);
+    positions_ = positions.to(at::kInt);
+    mapping_ = mapping.to(at::kInt);
+    batch_requests_ = batch_requests.to(at::kInt);
+    if (static_cast<int64_t>(prefixes.size()) == rows_) {
+      requests_ = batch_requests_;
+    } else {
+      auto repeats = at::tensor(lengths, at::TensorOptions().dtype(at::kLong)).to(locations.device(), true);
+      requests_ = at::repeat_interleave(batch_requests_, repeats, 0, rows_);
+    }
+    header_ = at::full({1}, rows_, locations_.options());
+    if (token_ids.defined() && token_ids.numel()) {
+      TORCH_CHECK(token_ids.is_cuda() && token_ids.dim() == 1 && token_ids.size(0) == rows_ && vocabulary > 0,
+                  "GaudiRT: invalid token metadata");
+      token_ids_ = token_ids.to(at::kInt);
+      vocabulary_ = vocabulary;
+      std::vector<int64_t> last;
+      int64_t end = 0;
+      for (auto n : lengths) last.push_back((end += n) - 1);
+      last_token_indices_ = at::tensor(last, at::TensorOptions().dtype(at::kInt)).to(locations.device(), true);
+    }
+  }
+
+  static c10::intrusive_ptr<PagedMetadata> from_device(const at::Tensor& locations, const at::Tensor& batch_requests,
+                                                       const at::Tensor& positions, const at::Tensor& mapping,
+                                                       std::vector<int64_t> prefixes, std::vector<int64_t> lengths,
+                                                       int64_t slots) {
+    return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
+                                              std::move(lengths), slots, at::Tensor(), 0);
+  }
+  static c10::intrusive_ptr<PagedMetadata> from_device_with_tokens(
+      const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
+      const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
+      const at::Tensor& token_ids, int64_t vocabulary) {
+    return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
+                                              std::move(lengths), slots, token_ids, vocabulary);
+  }
+  static c10::intrusive_ptr<PagedMetadata> from_scheduler(const at::Tensor& locations, const at::Tensor& batch_requests,
+                                                          const at::Tensor& positions, const at::Tensor& mapping,
+                                                          std::vector<int64_t> prefixes, std::vector<int64_t> lengths,
+                                                          int64_t slots, const c10::optional<at::Tensor>& token_ids,
+                                                          int64_t vocabulary) {
+    return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
+                                              std::move(lengths), slots, token_ids.value_or(at::Tensor()), vocabulary);
+  }
+  static c10::intrusive_ptr<PagedMetadata> from_scheduler_fused(
+      const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
+      const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
+      const c10::optional<at::Tensor>& token_ids, int64_t vocabulary, int64_t query_heads, int64_t kv_heads,
+      int64_t head_dim) {
+    auto md = from_scheduler(locations, batch_requests, positions, mapping, std::move(prefixes), std::move(lengths),
+                             slots, token_ids, vocabulary);
+    md->attention_plan(query_heads, kv_heads, head_dim);
+    return md;
+  }
+
+  int64_t rows() const { return rows_; }
+  int64_t slots() const { return slots_; }
+  int64_t context() const { return context_; }
+  int64_t page_tokens() const { return page_tokens_; }
+  at::Tensor rotary_positions() const { return positions_; }
+  at::Tensor rotary_header() const { return header_; }
+  at::Tensor row_locations() const { return locations_; }
+  at::Tensor row_requests() const { return requests_; }
+  at::Tensor request_mapping() const { return mapping_; }
+  at::Tensor last_token_indices() const {
+    TORCH_CHECK(last_token_indices_.defined(), "GaudiRT: last-token indices require batched metadata");
+    return last_token_indices_;
+  }
+  at::Tensor token_ids() const {
+    TORCH_CHECK(token_ids_.defined(), "GaudiRT: token IDs were not validated in this metadata");
+    return token_ids_;
+  }
+  int64_t vocabulary() const { return vocabulary_; }
+  std::vector<int64_t> sequences() const { return std::vector<int64_t>(sequences_.begin(), sequences_.end()); }
+
+  at::Tensor attention_plan(int64_t query_heads, int64_t kv_heads, int64_t head_dim) {
+    return attention_plan_for(query_heads, kv_heads, head_dim, -1);
+  }
+
+  // Schedule for one step, shared by all layers (src/bridge/attention_plan.cpp:146-361).
+  at::Tensor attention_plan_for(int64_t query_heads, int64_t kv_heads, int64_t head_dim, int64_t sliding_window) {
+    TORCH_CHECK(sliding_window == -1 || (sliding_window > 0 && sliding_window <= INT32_MAX),
+                "GaudiRT attention: invalid sliding window size");
+    for (const auto& entry : plans_) {
+      if (entry.first != sliding_window) continue;
+      const auto& plan = plan_of(entry.second);
+      TORCH_CHECK(plan.query_heads == query_heads && plan.kv_heads == kv_heads && plan.head_dim == head_dim,
+                  "GaudiRT attention: metadata already bound to different head geometry");
+      return entry.second;
+    }
+    TORCH_CHECK(query_heads > 0 && query_heads <= 256 && kv_heads > 0 && kv_heads <= 256 &&
+                    query_heads % kv_heads == 0 && (head_dim == 64 || head_dim == 128 || head_dim == 256),
+                "GaudiRT attention: unsupported head or request-map geometry");
+    const auto device = locations_.device();
+    c10::cuda::CUDAGuard guard(device);
+    const int sm_count = at::cuda::getDeviceProperties(device.index())->multiProcessorCount;
+    const int64_t n_seq = static_cast<int64_t>(sequences_.size() / 4);
+    int64_t n_work = 0, n_combine = 0, entries = 0;
+    const int window = static_cast<int>(sliding_window);
+    check_status(gk_attention_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, (int)head_dim, window,
+                                         sm_count, split_tokens_, nullptr, 0, &n_work, nullptr, 0, &n_combine, &entries),
+                 "attention plan");
+    const int64_t combine_offset = n_work * GK_WORK_WORDS;
+    const int64_t words = std::max<int64_t>(4, combine_offset + n_combine * GK_COMBINE_WORDS);
+    auto staging = at::empty({words}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+    int32_t* host = staging.data_ptr<int32_t>();
+    check_status(gk_attention_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, (int)head_dim, window,
+                                         sm_count, split_tokens_, host, n_work, &n_work, host + combine_offset,
+                                         n_combine, &n_combine, &entries),
+                 "attention plan");
+    auto plan = std::make_unique<AttentionPlan>();
+    plan->buffer = staging.to(device, /*non_blocking=*/true);
+    const auto f32 = at::TensorOptions().dtype(at::kFloat).device(device);
+    plan->part_ml = at::empty({std::max<int64_t>(entries, 1) * 2}, f32);
+    plan->part_o = at::empty({std::max<int64_t>(entries, 1) * head_dim}, f32);
+    plan->table = mapping_;
+    plan->table_rows = batch_requests_;
+    plan->table_stride = mapping_.stride(0);
+    plan->page_tokens = static_cast<int>(page_tokens_);
+    plan->entry_stride = page_tokens_;
+    plan->stream = at::cuda::getCurrentCUDAStream(device.index()).stream();
+    plan->device = device.index();
+    plan->rows = rows_;
+    plan->slots = slots_;
+    plan->query_heads = query_heads;
+    plan->kv_heads = kv_heads;
+    plan->head_dim = head_dim;
+    plan->sliding_window = sliding_window;
+    plan->n_work = n_work;
+    plan->n_combine = n_combine;
+    plan->combine_offset = combine_offset;
+    auto tensor = wrap_plan(std::move(plan));
+    plans_.emplace_back(sliding_window, tensor);
+    return tensor;
+  }
+
+  std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, int64_t>
+  forward_tensors(int64_t query_heads, int64_t kv_heads, int64_t head_dim) {
+    return {token_ids(), last_token_indices(), rotary_positions(), rotary_header(), row_locations(),
+            row_requests(), attention_plan(query_heads, kv_heads, head_dim), context_};
+  }
+
+  // Longest KV range of one work item for plans built after this call (0 = chosen from the SM
+  // count).  Not part of the reference surface: a test and tuning hook.
+  void set_split_tokens(int64_t tokens) {
+    TORCH_CHECK(tokens >= 0 && tokens <= INT32_MAX, "GaudiRT attention: invalid split size");
+    split_tokens_ = static_cast<int>(tokens);
+  }
+
+  int64_t rows_ = 0, slots_ = 0, request_count_ = 0, context_ = 0, vocabulary_ = 0, page_tokens_ = 1;
+  int split_tokens_ = 0;
+  at::Tensor locations_, requests_, positions_, mapping_, header_, batch_requests_, token_ids_, last_token_indices_;
+  std::vector<int32_t> sequences_;   // {first_row, n_rows, first_position, table_row} per sequence
+  std::vector<std::pair<int64_t, at::Tensor>> plans_;
+};
+
+// ---------------------------------------------------------------------------------------------
+// operators
+// ---------------------------------------------------------------------------------------------
+at::Tensor allocate_paged_kv(int64_t layers, int64_t slots, int64_t heads, int64_t head_dim) {
+  uint64_t bytes = 0;
+  TORCH_CHECK(gk_paged_kv_pool_bytes(layers, slots, heads, head_dim, &bytes) == GK_OK,
+              "GaudiRT: unsupported head-major KV pool geometry");
+  return at::zeros({layers, 2, heads, slots, head_dim},
+                   at::TensorOptions().dtype(at::kBFloat16).device(c10::Device(c10::kCUDA, at::cuda::current_device())));
+}
+
+int64_t paged_attn_kv_tile(int64_t) { return GK_REFERENCE_KV_TILE; }
+
+at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                at::Tensor& key_pool, at::Tensor& value_pool, const at::Tensor& locations,
+                                const at::Tensor& /*requests*/, const at::Tensor& /*positions*/,
+                                const at::Tensor& plan_tensor, const at::Tensor& /*header*/, int64_t head_dim,
+                                double scale, double softcap, int64_t sliding_window) {
+  const auto& plan = plan_of(plan_tensor);
+  const auto device = plan_tensor.device();
+  c10::cuda::CUDAGuard guard(device);
+  const auto stream = at::cuda::getCurrentCUDAStream(device.index());
+  const float scale_f = static_cast<float>(scale), softcap_f = static_cast<float>(softcap);
+  TORCH_CHECK(plan.stream == stream.stream() && std::isfinite(scale) && std::isfinite(scale_f) && scale_f > 0 &&
+                  std::isfinite(softcap) && std::isfinite(softcap_f) && softcap_f >= 0.0f &&
+                  (sliding_window == -1 || (sliding_window > 0 && sliding_window <= INT32_MAX)) &&
+                  head_dim == plan.head_dim,
+              "GaudiRT attention: invalid scale, stream, or head dimension");
+  TORCH_CHECK(plan.sliding_window == sliding_window, "GaudiRT attention: plan sliding_window mismatch");
+  for (const auto& input : {query, key, value})
+    TORCH_CHECK(input.is_cuda() && input.device() == device && input.scalar_type() == at::kBFloat16 &&
+                    input.dim() == 2 && input.size(0) == plan.rows,
+                "GaudiRT attention: Q/K/V must be BF16 device matrices with matching rows");
+  TORCH_CHECK(query.size(1) == plan.query_heads * head_dim && key.size(1) == plan.kv_heads * head_dim &&
+                  value.size(1) == key.size(1) && locations.dim() == 1 && locations.numel() == plan.rows &&
+                  locations.scalar_type() == at::kInt && locations.device() == device && locations.is_contiguous(),
+              "GaudiRT attention: Q/K/V or slot dimensions do not match metadata");
+  for (const auto& pool : {key_pool, value_pool})
+    TORCH_CHECK(pool.is_cuda() && pool.device() == device && pool.scalar_type() == at::kBFloat16 && pool.dim() == 3 &&
+                    pool.size(0) == plan.slots && pool.size(1) == plan.kv_heads && pool.size(2) == head_dim &&
+                    pool.stride(0) == head_dim && pool.stride(1) == plan.slots * head_dim && pool.stride(2) == 1,
+                "GaudiRT attention: head-major combined KV pool is required");
+  const auto key_address = reinterpret_cast<uintptr_t>(key_pool.data_ptr());
+  const auto value_address = reinterpret_cast<uintptr_t>(value_pool.data_ptr());
+  const uint64_t half_bytes = static_cast<uint64_t>(plan.slots) * plan.kv_heads * head_dim * sizeof(uint16_t);
+  TORCH_CHECK(key_pool.storage().unsafeGetStorageImpl() == value_pool.storage().unsafeGetStorageImpl() &&
+                  value_address == key_address + half_bytes && key_address % 16 == 0,
+              "GaudiRT attention: KV pool descriptor is not backed by combined storage");
+  // Row-strided column slices are read in place; anything else is packed first.
+  const at::Tensor q = query.stride(1) == 1 ? query : query.contiguous();
+  const at::Tensor k = key.stride(1) == 1 ? key : key.contiguous();
+  const at::Tensor v = value.stride(1) == 1 ? value : value.contiguous();
+  auto output = at::empty({plan.rows, query.size(1)}, query.options().memory_format(at::MemoryFormat::Contiguous));
+  int32_t* status = device_status(device.index()).data_ptr<int32_t>();
+  const gk_stream_t s = stream_of(stream);
+  check_status(gk_kv_store_head_major_bf16(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                                           locations.data_ptr<int32_t>(), plan.rows, key_pool.data_ptr(),
+                                           value_pool.data_ptr(), plan.slots, (int)plan.kv_heads, (int)head_dim, status, s),
+               "KV store");
+  const int32_t* words = plan.buffer.data_ptr<int32_t>();
+  check_status(gk_paged_attn_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
+                                  plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride, plan.page_tokens,
+                                  plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr, words,
+                                  plan.n_work, output.data_ptr(), output.stride(0), plan.part_ml.data_ptr<float>(),
+                                  plan.part_o.data_ptr<float>(), scale_f, softcap_f, (int)sliding_window,
+                                  (int)plan.query_heads, (int)plan.kv_heads, (int)head_dim, status, s),
+               "paged attention");
+  check_status(gk_paged_attn_combine_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
+                                          words + plan.combine_offset, plan.n_combine, output.data_ptr(), output.stride(0),
+                                          (int)plan.query_heads, (int)head_dim, s),
+               "split-KV combine");
+  return output;
+}
+
+at::Tensor paged_attn(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, at::Tensor& key_pool,
+                      at::Tensor& value_pool, const c10::intrusive_ptr<PagedMetadata>& metadata, int64_t head_dim,
+                      double scale, double softcap, int64_t sliding_window) {
+  TORCH_CHECK(metadata, "GaudiRT paged attention: metadata is required");
+  TORCH_CHECK(query.dim() == 2 && key_pool.dim() == 3 && (head_dim == 64 || head_dim == 128 || head_dim == 256),
+              "GaudiRT paged attention: invalid tensor ranks or head dimension");
+  const auto q_heads = query.size(1) / head_dim;
+  const auto kv_heads = key_pool.size(1);
+  auto plan = sliding_window > 0 ? metadata->attention_plan_for(q_heads, kv_heads, head_dim, sliding_window)
+                                 : metadata->attention_plan(q_heads, kv_heads, head_dim);
+  return paged_attn_validated(query, key, value, key_pool, value_pool, metadata->row_locations(),
+                              metadata->row_requests(), metadata->rotary_positions(), plan, metadata->rotary_header(),
+                              head_dim, scale, softcap, sliding_window);
+}
+
+// Reads and clears the device status word of the current device (synchronises the stream).
+int64_t take_device_status() {
+  auto& word = device_status(at::cuda::current_device());
+  const int64_t value = word.item<int32_t>();
+  if (value) word.zero_();
+  return value;
+}
+
+}  // namespace gaudirt_b200
+
+TORCH_LIBRARY(gaudirt, m) {
+  using gaudirt_b200::PagedMetadata;
+  m.class_<PagedMetadata>("PagedMetadata")
+      .def(torch::init<at::Tensor, at::Tensor, at::Tensor, at::Tensor, int64_t>())
+      .def_static("from_device", &PagedMetadata::from_device)
+      .def_static("from_device_with_tokens", &PagedMetadata::from_device_with_tokens)
+      .def_static("_from_scheduler", &PagedMetadata::from_scheduler)
+      .def_static("_from_scheduler_fused", &PagedMetadata::from_scheduler_fused)
+      .def("rows", &PagedMetadata::rows)
+      .def("slots", &PagedMetadata::slots)
+      .def("context", &PagedMetadata::context)
+      .def("page_tokens", &PagedMetadata::page_tokens)
+      .def("sequences", &PagedMetadata::sequences)
+      .def("forward_tensors", &PagedMetadata::forward_tensors)
+      .def("rotary_positions", &PagedMetadata::rotary_positions)
+      .def("rotary_header", &PagedMetadata::rotary_header)
+      .def("row_locations", &PagedMetadata::row_locations)
+      .def("row_requests", &PagedMetadata::row_requests)
+      .def("request_mapping", &PagedMetadata::request_mapping)
+      .def("attention_plan", &PagedMetadata::attention_plan)
+      .def("attention_plan_for", &PagedMetadata::attention_plan_for)
+      .def("last_token_indices", &PagedMetadata::last_token_indices)
+      .def("token_ids", &PagedMetadata::token_ids)
+      .def("vocabulary", &PagedMetadata::vocabulary)
+      .def("_set_split_tokens", &PagedMetadata::set_split_tokens);
+  m.def("paged_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+        "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, float scale, "
+        "float softcap=0.0, int sliding_window=-1) -> Tensor");
+  m.def("_paged_attn_validated(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+        "Tensor locations, Tensor requests, Tensor positions, Tensor mapping, Tensor header, "
+        "int head_dim, float scale, float softcap=0.0, int sliding_window=-1) -> Tensor");
+  m.def("_allocate_paged_kv(int layers, int slots, int heads, int head_dim) -> Tensor", &gaudirt_b200::allocate_paged_kv);
+  m.def("_paged_attn_kv_tile(int rows) -> int", &gaudirt_b200::paged_attn_kv_tile);
+  m.def("_take_device_status() -> int", &gaudirt_b200::take_device_status);
+}
+
+TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
+  m.impl("paged_attn", TORCH_FN(gaudirt_b200::paged_attn));
+  m.impl("_paged_attn_validated", TORCH_FN(gaudirt_b200::paged_attn_validated));
+}

@@ -16,10 +16,16 @@
  *   q / out   [rows, q_heads*head_dim], row stride given in elements.
  *   k / v     [rows, kv_heads*head_dim], row stride given in elements (column slices of a
  *             packed QKV projection are allowed).
- *   table     int32 slot table.  Row `t` starts at table + t*table_stride; entry j is the
- *             slot of token j*page_tokens, and the page_tokens tokens of that page occupy
- *             consecutive slots.  page_tokens == 1 is the reference's request-to-token
- *             `mapping[requests, context]` itself (src/bridge/paged_metadata.cpp:104-140).
+ *   table     int32 slot table.  Row `t` starts at table + t*table_stride; page j of that row
+ *             is described by the entry at j*table_entry_stride, which holds the slot of token
+ *             j*page_tokens; the page_tokens tokens of a page occupy consecutive slots.
+ *             page_tokens == 1, table_entry_stride == 1 is the reference's request-to-token
+ *             `mapping[requests, context]` itself (src/bridge/paged_metadata.cpp:104-140);
+ *             the same array with page_tokens == table_entry_stride == P reads one entry per
+ *             page; a block table is table_entry_stride == 1 with page_tokens == block size.
+ *   table_rows  optional int32 device array: the table row of a work record is
+ *             table_rows[record.table_row] instead of record.table_row (request ids that only
+ *             exist on the device, PagedMetadata::from_device, src/bridge/paged_metadata.hpp:26-64).
  */
 #ifndef GAUDIRT_B200_H_
 #define GAUDIRT_B200_H_
@@ -51,7 +57,7 @@ enum gk_status {
 /* Bits a kernel may OR into the caller's int32 device status word (never cleared by kernels). */
 enum gk_device_status {
   GK_DEV_BAD_SLOT = 1,          /* a slot outside [0, slots) was met: the access was skipped   */
-  GK_DEV_BAD_TABLE = 2,         /* a table entry outside [0, slots) was met: slot 0 was read   */
+  GK_DEV_BAD_TABLE = 2,         /* a table entry outside [0, slots) was met: key left out      */
   GK_DEV_WAIT_EXPIRED = 4       /* a bounded wait ran out                                      */
 };
 
@@ -137,7 +143,8 @@ GK_API int gk_kv_store_head_major_bf16(const void* k, const void* v, int64_t k_r
  * head_dim in {64, 128, 256}; q_heads/kv_heads <= GK_MAX_PACKED_ROWS. */
 GK_API int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
                        const void* pool_v, int64_t slots, const int32_t* table,
-                       int64_t table_stride, int page_tokens, const int32_t* work,
+                       int64_t table_stride, int64_t table_entry_stride, int page_tokens,
+                       const int32_t* table_rows, const int32_t* work,
                        int64_t n_work, void* out, int64_t out_row_stride, float* part_ml,
                        float* part_o, float scale, float softcap, int window, int q_heads,
                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream);

@@ -56,7 +56,7 @@ def kv_store(pool_layer, key, value, locations, status=None):
 
 
 def paged_attn(query, pool_layer, table, page_tokens, work, combine, entries, q_heads, scale,
-               softcap=0.0, window=-1, status=None):
+               softcap=0.0, window=-1, status=None, entry_stride=1, table_rows=None):
     """Launch attention (+ combine) for a prepared schedule; returns the bf16 output tensor."""
     _, kv_heads, slots, d = pool_layer.shape
     dev = query.device
@@ -67,7 +67,8 @@ def paged_attn(query, pool_layer, table, page_tokens, work, combine, entries, q_
     lib = abi.lib()
     st = lib.gk_paged_attn_bf16(
         query.data_ptr(), query.stride(0), pool_layer[0].data_ptr(), pool_layer[1].data_ptr(), slots,
-        table.data_ptr(), table.stride(0), page_tokens, work_d.data_ptr(), work.shape[0], out.data_ptr(),
+        table.data_ptr(), table.stride(0), entry_stride, page_tokens,
+        table_rows.data_ptr() if table_rows is not None else None, work_d.data_ptr(), work.shape[0], out.data_ptr(),
         out.stride(0), part_ml.data_ptr(), part_o.data_ptr(), scale, softcap, window, q_heads, kv_heads, d,
         status.data_ptr() if status is not None else None, stream_ptr())
     abi.check(st, "gk_paged_attn_bf16")
