@@ -1,5 +1,7 @@
-"""Test-side driver of the raw C ABI (ctypes): builds host metadata and schedules through the
-library's host entry points and launches the kernels on torch CUDA tensors."""
+"""Thin ctypes driver of the raw C ABI: host metadata and schedules through the library's host
+entry points, kernel launches on torch CUDA tensors.  Used by the parity tests and by the
+benchmark's kernel-only timing pass; the operator layer (torch.ops.gaudirt.*) does not go
+through here."""
 from __future__ import annotations
 
 import ctypes as C
@@ -7,7 +9,7 @@ import ctypes as C
 import numpy as np
 import torch
 
-from gaudirt_b200 import abi
+from . import abi
 
 
 def _ptr(a: np.ndarray):

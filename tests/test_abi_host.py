@@ -8,7 +8,7 @@ import pytest
 
 import oracle
 from gaudirt_b200 import abi
-from tests import abi_harness as H
+from gaudirt_b200 import raw as H
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import oracle
-from tests import abi_harness as H
+from gaudirt_b200 import raw as H
 from tests import cases
 
 pytestmark = pytest.mark.gpu
