@@ -32,6 +32,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "paged_decode_tokens_per_s"
+# DRAM bytes moved per algorithmic KV byte by the attention kernel: (dram__bytes_read.sum +
+# dram__bytes_write.sum) of one ncu capture on a batch-128 launch; traffic is one pass over the
+# visible K/V rows, so it is scaled to the benchmark launch by its KV bytes.
+TRAFFIC_PER_KV_BYTE = 1.0037
+TRAFFIC_SOURCE = "profiles/paged_attn_kernel_decode_b128_ctx4096_ncu_full.md, scaled by KV bytes"
 GEOM = dict(batch=256, ctx=4096, q_heads=32, kv_heads=8, head_dim=128, block=128, layers=32)
 
 
@@ -339,13 +344,8 @@ def run_b200(args):
         "gpu_launches": args.steps * L * (2 + (1 if len(combine) else 0)),
         "clocks": clocks.summary(),
     }
-    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_path):
-        with open(traffic_path) as f:
-            t = json.load(f)
-        if t.get("bytes_per_kv_byte"):
-            line["roofline"]["traffic"] = t["bytes_per_kv_byte"] * kv_bytes
-            line["roofline"]["traffic_source"] = t.get("source")
+    line["roofline"]["traffic"] = TRAFFIC_PER_KV_BYTE * kv_bytes
+    line["roofline"]["traffic_source"] = TRAFFIC_SOURCE
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
