@@ -1,6 +1,6 @@
 """B200-native paged KV-store / paged-attention path behind the GaudiRT operator surface.
 
-Importing the package loads the two in-tree native libraries (``python -m gaudirt_b200.build``
+Importing the package loads the two in-tree native libraries (``python gaudirt_b200/build.py``
 makes them) and exposes the reference's Python-visible names for this path:
 
 * ``torch.ops.gaudirt.paged_attn`` / ``_paged_attn_validated`` and
@@ -23,7 +23,7 @@ from . import abi, build
 __all__ = ["abi", "build", "_C", "PagedMetadata", "synchronize"]
 
 if not os.path.exists(build.OPS_SO):
-    raise ImportError(f"{build.OPS_SO} is missing: run `python -m gaudirt_b200.build` (needs nvcc and g++)")
+    raise ImportError(f"{build.OPS_SO} is missing: run `python gaudirt_b200/build.py` (needs nvcc and g++)")
 abi.lib()
 torch.ops.load_library(build.OPS_SO)
 

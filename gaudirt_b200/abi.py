@@ -26,6 +26,8 @@ PROTOTYPES = {
     "gk_paged_attn_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, vp, vp, f32, f32, i32,
                                  i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_bf16": (i32, [vp, vp, vp, i64, vp, i64, i32, i32, vp]),
+    "gk_paged_attn_static_scratch_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, i64,
+                                                vp, i64, f32, f32, i32, i32, i32, i32, vp, vp]),
 }
 
 _lib = None
@@ -40,7 +42,7 @@ def lib() -> C.CDLL:
     if _lib is None:
         path = library_path()
         if not os.path.exists(path):
-            raise RuntimeError(f"{path} is missing: run `python -m gaudirt_b200.build` (needs nvcc, sm_100a)")
+            raise RuntimeError(f"{path} is missing: run `python gaudirt_b200/build.py` (needs nvcc, sm_100a)")
         handle = C.CDLL(path)
         for name, (res, args) in PROTOTYPES.items():
             fn = getattr(handle, name)

@@ -1,6 +1,6 @@
 """In-tree build of the native libraries (no JIT cache: the built files travel with the tree).
 
-``python -m gaudirt_b200.build`` compiles
+``python gaudirt_b200/build.py`` compiles
 
 * ``lib/libgaudirt_b200.so``  -- the C ABI (``include/gaudirt_b200.h``): CUDA kernels for sm_100a
   plus the host-side metadata/plan code; depends on nothing but the CUDA runtime;
@@ -71,7 +71,7 @@ def build_ops(force: bool = False) -> str:
     build_abi(force)
     if not sources:
         raise RuntimeError("operator-layer sources are missing")
-    if force or _stale(OPS_SO, deps + [ABI_SO]):
+    if force or _stale(OPS_SO, deps):
         inc = [f"-I{p}" for p in cpp_extension.include_paths(device_type="cuda")]
         torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
         abi_flag = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"

@@ -13,6 +13,8 @@
 
 #include <math_constants.h>
 
+#include <mutex>
+
 namespace gk {
 namespace {
 
@@ -469,4 +471,63 @@ extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* par
     default: return GK_ERR_UNSUPPORTED;
   }
   return gk::check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention + combine for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+namespace gk {
+namespace {
+// Split state for gk_paged_attn_static_scratch_bf16: (m, l) pairs for every entry first, the
+// O rows after them.  Lives in every GPU context that loads this library, until exit.
+constexpr size_t kStaticMlFloats = (size_t)GK_STATIC_SCRATCH_MAX_ENTRIES * 2;
+constexpr size_t kStaticFloats = kStaticMlFloats + (size_t)GK_STATIC_SCRATCH_MAX_ENTRIES * GK_STATIC_SCRATCH_MAX_HEAD_DIM;
+static __device__ __align__(256) float g_static_scratch[kStaticFloats];
+
+std::mutex g_static_mutex;
+float* g_static_address[64] = {};   // device address of g_static_scratch, per device ordinal
+
+// `g_static_scratch` names a host-side stand-in here, not device memory: the address a kernel may
+// use has to be asked for, once per device, with that device current.
+int static_scratch_address(float** out) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
+  if (device < 0 || device >= 64) return GK_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_address[device]) {
+    void* address = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&address, g_static_scratch);
+    if (e != cudaSuccess || !address) {
+      g_last_cuda_error = static_cast<int>(e);
+      (void)cudaGetLastError();
+      return GK_ERR_CUDA;
+    }
+    g_static_address[device] = static_cast<float*>(address);
+  }
+  *out = g_static_address[device];
+  return GK_OK;
+}
+}  // namespace
+}  // namespace gk
+
+extern "C" int gk_paged_attn_static_scratch_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                                                 const void* pool_v, int64_t slots, const int32_t* table,
+                                                 int64_t table_stride, int64_t table_entry_stride, int page_tokens,
+                                                 const int32_t* table_rows, const int32_t* work, int64_t n_work,
+                                                 const int32_t* combine, int64_t n_combine, int64_t partial_entries,
+                                                 void* out, int64_t out_row_stride, float scale, float softcap,
+                                                 int window, int q_heads, int kv_heads, int head_dim, int32_t* status,
+                                                 gk_stream_t stream) {
+  if (partial_entries < 0 || n_combine < 0) return GK_ERR_INVALID_ARGUMENT;
+  if (partial_entries > GK_STATIC_SCRATCH_MAX_ENTRIES || head_dim > GK_STATIC_SCRATCH_MAX_HEAD_DIM) return GK_ERR_CAPACITY;
+  float* base = nullptr;
+  const int got = gk::static_scratch_address(&base);
+  if (got != GK_OK) return got;
+  float* part_ml = base;
+  float* part_o = base + gk::kStaticMlFloats;
+  const int rc = gk_paged_attn_bf16(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
+                                    page_tokens, table_rows, work, n_work, out, out_row_stride, part_ml, part_o, scale,
+                                    softcap, window, q_heads, kv_heads, head_dim, status, stream);
+  if (rc != GK_OK) return rc;
+  return gk_paged_attn_combine_bf16(part_ml, part_o, combine, n_combine, out, out_row_stride, q_heads, head_dim, stream);
 }

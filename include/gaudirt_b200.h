@@ -156,6 +156,37 @@ GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o,
                                int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
                                int head_dim, gk_stream_t stream);
 
+/* ---- attention without any device allocation ---------------------------------------------
+ * This entry point has no counterpart in the reference.  It is for callers that must not
+ * allocate device memory on their hot path: a serving engine that has handed all HBM to its own
+ * KV pool, a plugin called under a framework whose allocator it may not enter, a real-time loop
+ * where cudaMalloc's implicit synchronisation is not acceptable.  It runs gk_paged_attn_bf16 and
+ * then gk_paged_attn_combine_bf16 with the fp32 split state kept in an array that is part of
+ * the library image itself (GK_STATIC_SCRATCH_MAX_ENTRIES entries of up to
+ * GK_STATIC_SCRATCH_MAX_HEAD_DIM floats plus (m, l): about 8.5 MB, resident on every GPU that
+ * loads the library until the process exits).  It calls no cudaMalloc, cudaFree or allocating
+ * library routine.
+ *   partial_entries   what gk_attention_plan_build reported for this schedule; more than
+ *                     GK_STATIC_SCRATCH_MAX_ENTRIES (or head_dim above the maximum) is refused
+ *                     with GK_ERR_CAPACITY before anything is launched.
+ *   combine, n_combine  the schedule's combine records (may be empty).
+ * The first call on each device looks up the device address of the array (a host-side query,
+ * no allocation); make that first call before starting any stream capture.  All calls share the
+ * one array: it keeps the previous call's contents (nothing in it needs clearing, every entry a
+ * combine record reads is written by that call's attention kernel first), and two calls whose
+ * kernels overlap on the GPU (different streams, or different threads) race on it. */
+#define GK_STATIC_SCRATCH_MAX_ENTRIES 8192
+#define GK_STATIC_SCRATCH_MAX_HEAD_DIM 256
+GK_API int gk_paged_attn_static_scratch_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                                      const void* pool_v, int64_t slots, const int32_t* table,
+                                      int64_t table_stride, int64_t table_entry_stride,
+                                      int page_tokens, const int32_t* table_rows,
+                                      const int32_t* work, int64_t n_work, const int32_t* combine,
+                                      int64_t n_combine, int64_t partial_entries, void* out,
+                                      int64_t out_row_stride, float scale, float softcap,
+                                      int window, int q_heads, int kv_heads, int head_dim,
+                                      int32_t* status, gk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
