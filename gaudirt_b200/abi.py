@@ -26,6 +26,11 @@ PROTOTYPES = {
     "gk_paged_attn_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, vp, vp, f32, f32, i32,
                                  i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_bf16": (i32, [vp, vp, vp, i64, vp, i64, i32, i32, vp]),
+    "gk_rms_norm_bf16": (i32, [vp, vp, f32, f32, i64, i64, i64, vp, vp]),
+    "gk_fused_add_rms_norm_bf16": (i32, [vp, vp, vp, f32, f32, i64, i64, i64, i64, vp, vp, vp]),
+    "gk_rotary_bf16": (i32, [vp, vp, i64, i64, vp, i64, vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
+    "gk_rotary_kv_store_bf16": (i32, [vp, vp, vp, i64, i64, i64, vp, i64, vp, vp, i64, i64, i64, i32, i32, i32,
+                                      vp, vp, vp, vp, i64, vp, vp]),
     "gk_paged_attn_static_scratch_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, i64,
                                                 vp, i64, f32, f32, i32, i32, i32, i32, vp, vp]),
 }

@@ -1,0 +1,329 @@
+// Front of a decode layer: (fused residual-add) RMS norm and rotary position embedding.
+//
+// Both are HBM-bound elementwise/row kernels.  Every bf16 boundary of the reference (the updated
+// residual, the normalised output, each rotated element) is rounded ONCE from an exactly computed
+// value: the arithmetic between boundaries runs in fp64, and fp64 -> bf16 goes through a
+// round-to-odd fp32 so that no double rounding can occur.  That reproduces the reference's
+// binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35, tests/rotary_runtime_smoke.py:28-40)
+// bit for bit wherever fp64 itself is exact, at no cost: the kernels stay memory-bound.
+#include "gk_common.cuh"
+
+namespace gk {
+namespace {
+
+// Correctly rounded binary64 -> bf16 (nearest, ties to even).
+__device__ __forceinline__ unsigned short bf16_from_double(double v) {
+  float f = __double2float_rz(v);
+  if ((double)f != v) {                                       // inexact: force the sticky (odd) bit
+    f = __uint_as_float(__float_as_uint(f) | 1u);
+  }
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ double bf16_to_double(unsigned short b) {
+  return (double)__uint_as_float((uint32_t)b << 16);
+}
+
+__device__ __forceinline__ double block_sum(double v, double* shared) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) shared[warp] = v;
+  __syncthreads();
+  double total = 0.0;
+  for (int w = 0; w < warps; ++w) total += shared[w];          // same order in every thread
+  return total;
+}
+
+// One CTA per row.  VEC = 8: 16-byte loads, the row is held in registers between the reduction
+// and the write (hidden <= 256 threads * 8 * 4).  VEC = 1: any alignment, second pass re-reads.
+template <int VEC, bool FUSED>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __restrict__ x,
+                                                       const unsigned short* __restrict__ residual,
+                                                       const unsigned short* __restrict__ weight,
+                                                       unsigned short* __restrict__ y, unsigned short* __restrict__ u_out,
+                                                       int64_t x_stride, int64_t r_stride, int hidden, double epsilon,
+                                                       double weight_offset) {
+  __shared__ double partial[8];
+  const int64_t row = blockIdx.x;
+  const unsigned short* xr = x + row * x_stride;
+  const unsigned short* rr = FUSED ? residual + row * r_stride : nullptr;
+  unsigned short* yr = y + row * (int64_t)hidden;
+  unsigned short* ur = FUSED ? u_out + row * (int64_t)hidden : nullptr;
+  double sumsq = 0.0;
+  if (VEC == 8) {
+    constexpr int kItems = 4;
+    unsigned short u[kItems][8];
+#pragma unroll
+    for (int it = 0; it < kItems; ++it) {
+      const int col = (it * 256 + threadIdx.x) * 8;
+      if (col < hidden) {
+        uint4 a = __ldg(reinterpret_cast<const uint4*>(xr + col));
+        const unsigned short* av = reinterpret_cast<const unsigned short*>(&a);
+        if (FUSED) {
+          uint4 b = __ldg(reinterpret_cast<const uint4*>(rr + col));
+          const unsigned short* bv = reinterpret_cast<const unsigned short*>(&b);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) u[it][e] = bf16_from_double(bf16_to_double(av[e]) + bf16_to_double(bv[e]));
+          *reinterpret_cast<uint4*>(ur + col) = *reinterpret_cast<const uint4*>(u[it]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) u[it][e] = av[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const double v = bf16_to_double(u[it][e]);
+          sumsq = fma(v, v, sumsq);
+        }
+      }
+    }
+    const double total = block_sum(sumsq, partial);
+    const double inv = rsqrt(total / (double)hidden + epsilon);
+#pragma unroll
+    for (int it = 0; it < kItems; ++it) {
+      const int col = (it * 256 + threadIdx.x) * 8;
+      if (col < hidden) {
+        uint4 w = __ldg(reinterpret_cast<const uint4*>(weight + col));
+        const unsigned short* wv = reinterpret_cast<const unsigned short*>(&w);
+        unsigned short out[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          out[e] = bf16_from_double(bf16_to_double(u[it][e]) * inv * (bf16_to_double(wv[e]) + weight_offset));
+        *reinterpret_cast<uint4*>(yr + col) = *reinterpret_cast<const uint4*>(out);
+      }
+    }
+  } else {
+    for (int col = threadIdx.x; col < hidden; col += 256) {
+      unsigned short v = __ldg(xr + col);
+      if (FUSED) {
+        v = bf16_from_double(bf16_to_double(v) + bf16_to_double(__ldg(rr + col)));
+        ur[col] = v;
+      }
+      const double d = bf16_to_double(v);
+      sumsq = fma(d, d, sumsq);
+    }
+    const double total = block_sum(sumsq, partial);
+    const double inv = rsqrt(total / (double)hidden + epsilon);
+    for (int col = threadIdx.x; col < hidden; col += 256) {
+      // each thread re-reads only what it wrote (or the untouched input)
+      const unsigned short v = FUSED ? ur[col] : __ldg(xr + col);
+      yr[col] = bf16_from_double(bf16_to_double(v) * inv * (bf16_to_double(__ldg(weight + col)) + weight_offset));
+    }
+  }
+}
+
+struct RotaryParams {
+  const unsigned short* q;
+  const unsigned short* k;
+  const unsigned short* cache;
+  const int32_t* positions;
+  unsigned short* q_out;
+  unsigned short* k_out;
+  // fused store (optional): rotated K and the untouched V go straight to their pool slots
+  const unsigned short* v;
+  const int32_t* locations;
+  unsigned short* pool_k;
+  unsigned short* pool_v;
+  int32_t* status;
+  int64_t rows, q_stride, k_stride, v_stride, cache_rows, slots;
+  int q_heads, k_heads, head_dim, rotary_dim, is_neox;
+};
+
+__device__ __forceinline__ unsigned short rotate_element(const unsigned short* head, const unsigned short* table,
+                                                         int e, int rotary_dim, int is_neox) {
+  if (e >= rotary_dim) return __ldg(head + e);
+  const int half = rotary_dim >> 1;
+  int i, partner;
+  bool first;
+  if (is_neox) {
+    first = e < half;
+    i = first ? e : e - half;
+    partner = first ? e + half : e - half;
+  } else {
+    first = !(e & 1);
+    i = e >> 1;
+    partner = e ^ 1;
+  }
+  const double self = bf16_to_double(__ldg(head + e)), other = bf16_to_double(__ldg(head + partner));
+  const double c = bf16_to_double(__ldg(table + i)), s = bf16_to_double(__ldg(table + half + i));
+  // first of a pair: a*cos - b*sin ; second: b*cos + a*sin   (self is a resp. b)
+  return bf16_from_double(first ? self * c - other * s : self * c + other * s);
+}
+
+// One thread per element of q, k (and v when the store is fused).
+template <bool STORE>
+__global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
+  const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
+  const int64_t per_row = (int64_t)heads * p.head_dim;
+  const int64_t total = p.rows * per_row;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = idx / per_row;
+    const int rem = (int)(idx - row * per_row);
+    const int head = rem / p.head_dim, e = rem - head * p.head_dim;
+    int pos = __ldg(p.positions + row);
+    int rotary_dim = p.rotary_dim;
+    if ((unsigned)pos >= (unsigned)p.cache_rows) {          // position outside the table: pass through, report
+      if (p.status && rem == 0) atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+      pos = 0;
+      rotary_dim = 0;
+    }
+    const unsigned short* table = p.cache + (int64_t)pos * p.rotary_dim;
+    if (head < p.q_heads) {
+      const unsigned short* src = p.q + row * p.q_stride + (int64_t)head * p.head_dim;
+      p.q_out[row * (int64_t)p.q_heads * p.head_dim + rem] = rotate_element(src, table, e, rotary_dim, p.is_neox);
+      continue;
+    }
+    const int kh = head - p.q_heads;
+    if (kh < p.k_heads) {
+      const unsigned short* src = p.k + row * p.k_stride + (int64_t)kh * p.head_dim;
+      const unsigned short out = rotate_element(src, table, e, rotary_dim, p.is_neox);
+      if (p.k_out) p.k_out[row * (int64_t)p.k_heads * p.head_dim + kh * p.head_dim + e] = out;
+      if (STORE) {
+        const int slot = __ldg(p.locations + row);
+        if ((unsigned)slot < (unsigned)p.slots) {
+          p.pool_k[((int64_t)kh * p.slots + slot) * p.head_dim + e] = out;
+        } else if (p.status && e == 0 && kh == 0) {
+          atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+        }
+      }
+      continue;
+    }
+    if (STORE) {
+      const int vh = kh - p.k_heads;
+      const int slot = __ldg(p.locations + row);
+      if ((unsigned)slot < (unsigned)p.slots)
+        p.pool_v[((int64_t)vh * p.slots + slot) * p.head_dim + e] = __ldg(p.v + row * p.v_stride + (int64_t)vh * p.head_dim + e);
+    }
+  }
+}
+
+int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
+  const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
+  const int64_t total = p.rows * heads * p.head_dim;
+  const int64_t want = (total + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (store)
+    rotary_kernel<true><<<blocks, 256, 0, stream>>>(p);
+  else
+    rotary_kernel<false><<<blocks, 256, 0, stream>>>(p);
+  return check_launch();
+}
+
+bool rotary_args_ok(const void* q, const void* k, const void* cache, const int32_t* positions, int64_t rows,
+                    int64_t q_width, int64_t k_width, int64_t cache_rows, int head_dim, int rotary_dim) {
+  return q && k && cache && positions && rows >= 0 && q_width > 0 && k_width > 0 && cache_rows > 0 && head_dim > 0 &&
+         rotary_dim > 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0 && q_width % head_dim == 0 &&
+         k_width % head_dim == 0;
+}
+
+}  // namespace
+}  // namespace gk
+
+static int norm_common(const void* x, const void* residual, const void* weight, double epsilon, double weight_offset,
+                       int64_t rows, int64_t hidden, int64_t x_row_stride, int64_t residual_row_stride, void* y,
+                       void* u, gk_stream_t stream) {
+  const bool fused = residual != nullptr;
+  if (rows == 0) return GK_OK;
+  if (!x || !weight || !y || (fused && !u) || rows < 0 || hidden <= 0 || !(epsilon > 0.0) || x_row_stride < hidden ||
+      (fused && residual_row_stride < hidden))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (hidden > 8192 || rows > 0x7fffffffLL) return GK_ERR_UNSUPPORTED;   // bound of the reference's op (eager_ops.cpp:1147)
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+                         reinterpret_cast<uintptr_t>(y) | (fused ? reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(u) : 0);
+  if (bits & 1) return GK_ERR_INVALID_ARGUMENT;
+  const bool vec = !(bits & 15) && hidden % 8 == 0 && x_row_stride % 8 == 0 && (!fused || residual_row_stride % 8 == 0);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  auto xs = static_cast<const unsigned short*>(x);
+  auto rs = static_cast<const unsigned short*>(residual);
+  auto ws = static_cast<const unsigned short*>(weight);
+  auto ys = static_cast<unsigned short*>(y);
+  auto us = static_cast<unsigned short*>(u);
+  const unsigned grid = (unsigned)rows;
+  const int h = (int)hidden;
+  if (fused) {
+    if (vec) gk::rms_norm_kernel<8, true><<<grid, 256, 0, s>>>(xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset);
+    else gk::rms_norm_kernel<1, true><<<grid, 256, 0, s>>>(xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset);
+  } else {
+    if (vec) gk::rms_norm_kernel<8, false><<<grid, 256, 0, s>>>(xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset);
+    else gk::rms_norm_kernel<1, false><<<grid, 256, 0, s>>>(xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset);
+  }
+  return gk::check_launch();
+}
+
+extern "C" int gk_rms_norm_bf16(const void* x, const void* weight, float epsilon, float weight_offset, int64_t rows,
+                                int64_t hidden, int64_t x_row_stride, void* y, gk_stream_t stream) {
+  return norm_common(x, nullptr, weight, (double)epsilon, (double)weight_offset, rows, hidden, x_row_stride, 0, y,
+                     nullptr, stream);
+}
+
+extern "C" int gk_fused_add_rms_norm_bf16(const void* x, const void* residual, const void* weight, float epsilon,
+                                          float weight_offset, int64_t rows, int64_t hidden, int64_t x_row_stride,
+                                          int64_t residual_row_stride, void* y, void* u, gk_stream_t stream) {
+  if (!residual) return GK_ERR_INVALID_ARGUMENT;
+  return norm_common(x, residual, weight, (double)epsilon, (double)weight_offset, rows, hidden, x_row_stride,
+                     residual_row_stride, y, u, stream);
+}
+
+extern "C" int gk_rotary_bf16(const void* q, const void* k, int64_t q_row_stride, int64_t k_row_stride,
+                              const void* cache, int64_t cache_rows, const int32_t* positions, int64_t rows,
+                              int64_t q_width, int64_t k_width, int head_dim, int rotary_dim, int is_neox, void* q_out,
+                              void* k_out, int32_t* status, gk_stream_t stream) {
+  if (rows == 0) return GK_OK;
+  if (!gk::rotary_args_ok(q, k, cache, positions, rows, q_width, k_width, cache_rows, head_dim, rotary_dim) || !q_out ||
+      !k_out || q_row_stride < q_width || k_row_stride < k_width)
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::RotaryParams p{};
+  p.q = static_cast<const unsigned short*>(q);
+  p.k = static_cast<const unsigned short*>(k);
+  p.cache = static_cast<const unsigned short*>(cache);
+  p.positions = positions;
+  p.q_out = static_cast<unsigned short*>(q_out);
+  p.k_out = static_cast<unsigned short*>(k_out);
+  p.status = status;
+  p.rows = rows;
+  p.q_stride = q_row_stride;
+  p.k_stride = k_row_stride;
+  p.cache_rows = cache_rows;
+  p.q_heads = (int)(q_width / head_dim);
+  p.k_heads = (int)(k_width / head_dim);
+  p.head_dim = head_dim;
+  p.rotary_dim = rotary_dim;
+  p.is_neox = is_neox ? 1 : 0;
+  return gk::launch_rotary(p, false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gk_rotary_kv_store_bf16(const void* q, const void* k, const void* v, int64_t q_row_stride,
+                                       int64_t k_row_stride, int64_t v_row_stride, const void* cache,
+                                       int64_t cache_rows, const int32_t* positions, const int32_t* locations,
+                                       int64_t rows, int64_t q_width, int64_t k_width, int head_dim, int rotary_dim,
+                                       int is_neox, void* q_out, void* k_out, void* pool_k, void* pool_v, int64_t slots,
+                                       int32_t* status, gk_stream_t stream) {
+  if (rows == 0) return GK_OK;
+  if (!gk::rotary_args_ok(q, k, cache, positions, rows, q_width, k_width, cache_rows, head_dim, rotary_dim) || !q_out ||
+      !v || !locations || !pool_k || !pool_v || slots <= 0 || q_row_stride < q_width || k_row_stride < k_width ||
+      v_row_stride < k_width)
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::RotaryParams p{};
+  p.q = static_cast<const unsigned short*>(q);
+  p.k = static_cast<const unsigned short*>(k);
+  p.v = static_cast<const unsigned short*>(v);
+  p.cache = static_cast<const unsigned short*>(cache);
+  p.positions = positions;
+  p.locations = locations;
+  p.q_out = static_cast<unsigned short*>(q_out);
+  p.k_out = static_cast<unsigned short*>(k_out);   // may be NULL: the rotated K is only needed in the pool
+  p.pool_k = static_cast<unsigned short*>(pool_k);
+  p.pool_v = static_cast<unsigned short*>(pool_v);
+  p.status = status;
+  p.rows = rows;
+  p.q_stride = q_row_stride;
+  p.k_stride = k_row_stride;
+  p.v_stride = v_row_stride;
+  p.cache_rows = cache_rows;
+  p.slots = slots;
+  p.q_heads = (int)(q_width / head_dim);
+  p.k_heads = (int)(k_width / head_dim);
+  p.head_dim = head_dim;
+  p.rotary_dim = rotary_dim;
+  p.is_neox = is_neox ? 1 : 0;
+  return gk::launch_rotary(p, true, reinterpret_cast<cudaStream_t>(stream));
+}

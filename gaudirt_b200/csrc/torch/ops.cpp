@@ -426,6 +426,116 @@ at::Tensor paged_attn(const at::Tensor& query, const at::Tensor& key, const at::
                               head_dim, scale, softcap, sliding_window);
 }
 
+// ---------------------------------------------------------------------------------------------
+// front of a decode layer
+// ---------------------------------------------------------------------------------------------
+namespace {
+void check_norm_inputs(const at::Tensor& input, const at::Tensor* residual, const at::Tensor& weight, double epsilon,
+                       double weight_offset, const char* what) {
+  const float eps = static_cast<float>(epsilon), offset = static_cast<float>(weight_offset);
+  TORCH_CHECK(std::isfinite(epsilon) && std::isfinite(eps) && eps > 0 && std::isfinite(weight_offset) &&
+                  std::isfinite(offset),
+              "GaudiRT: ", what, " epsilon must be positive finite and weight_offset finite");
+  TORCH_CHECK(input.is_cuda() && weight.device() == input.device() && input.scalar_type() == at::kBFloat16 &&
+                  weight.scalar_type() == at::kBFloat16 &&
+                  (!residual || (residual->device() == input.device() && residual->scalar_type() == at::kBFloat16)),
+              "GaudiRT: ", what, " requires same-device CUDA BF16 tensors");
+  TORCH_CHECK(input.dim() >= 2 && input.dim() <= 5 && weight.dim() == 1 && weight.size(0) == input.size(-1) &&
+                  input.size(-1) <= 8192 && (!residual || residual->sizes() == input.sizes()),
+              "GaudiRT: invalid ", what, " tensor geometry");
+}
+
+// [.., hidden] -> 2-D [rows, hidden] with unit inner stride (a view when possible).
+at::Tensor as_rows(const at::Tensor& t) {
+  const auto hidden = t.size(-1);
+  if (t.dim() == 2 && t.stride(1) == 1) return t;
+  return t.contiguous().view({-1, hidden});
+}
+}  // namespace
+
+at::Tensor rms_norm(const at::Tensor& input, const at::Tensor& weight, double epsilon, double weight_offset) {
+  check_norm_inputs(input, nullptr, weight, epsilon, weight_offset, "RMSNorm");
+  auto out = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::Contiguous));
+  if (!input.numel()) return out;
+  c10::cuda::CUDAGuard guard(input.device());
+  const auto x = as_rows(input);
+  const auto w = weight.contiguous();
+  check_status(gk_rms_norm_bf16(x.data_ptr(), w.data_ptr(), (float)epsilon, (float)weight_offset, x.size(0), x.size(1),
+                                x.stride(0), out.data_ptr(), stream_of(at::cuda::getCurrentCUDAStream())),
+               "RMSNorm");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> fused_add_rms_norm(const at::Tensor& input, const at::Tensor& residual,
+                                                      const at::Tensor& weight, double epsilon, double weight_offset) {
+  check_norm_inputs(input, &residual, weight, epsilon, weight_offset, "fused RMSNorm");
+  auto norm = at::empty(input.sizes(), input.options().memory_format(at::MemoryFormat::Contiguous));
+  auto updated = at::empty(residual.sizes(), residual.options().memory_format(at::MemoryFormat::Contiguous));
+  if (!input.numel()) return {norm, updated};
+  c10::cuda::CUDAGuard guard(input.device());
+  const auto x = as_rows(input), r = as_rows(residual);
+  const auto w = weight.contiguous();
+  check_status(gk_fused_add_rms_norm_bf16(x.data_ptr(), r.data_ptr(), w.data_ptr(), (float)epsilon, (float)weight_offset,
+                                          x.size(0), x.size(1), x.stride(0), r.stride(0), norm.data_ptr(),
+                                          updated.data_ptr(), stream_of(at::cuda::getCurrentCUDAStream())),
+               "fused RMSNorm");
+  return {norm, updated};
+}
+
+std::tuple<at::Tensor, at::Tensor> rotary_embedding_validated(const at::Tensor& query, const at::Tensor& key,
+                                                              const at::Tensor& cache, const at::Tensor& positions,
+                                                              const at::Tensor& header, int64_t context, int64_t head_dim,
+                                                              int64_t rotary_dim, bool is_neox) {
+  TORCH_CHECK(head_dim > 0 && head_dim <= INT32_MAX && rotary_dim > 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+              "GaudiRT rotary: invalid head or rotary dimension");
+  for (const auto& t : {query, key, cache})
+    TORCH_CHECK(t.is_cuda() && t.device() == query.device() && t.scalar_type() == at::kBFloat16,
+                "GaudiRT rotary: expected CUDA BF16 tensors");
+  TORCH_CHECK(query.dim() == 2 && key.dim() == 2 && query.size(0) > 0 && key.size(0) == query.size(0) &&
+                  query.size(1) > 0 && key.size(1) > 0 && query.size(1) % head_dim == 0 && key.size(1) % head_dim == 0,
+              "GaudiRT rotary: invalid query or key geometry");
+  TORCH_CHECK(cache.dim() == 2 && context > 0 && cache.size(0) >= context && cache.size(0) <= INT32_MAX &&
+                  cache.size(1) == rotary_dim,
+              "GaudiRT rotary: cache does not cover validated positions");
+  const auto rows = query.size(0);
+  TORCH_CHECK(positions.device() == query.device() && positions.scalar_type() == at::kInt && positions.dim() == 1 &&
+                  positions.size(0) == rows && positions.is_contiguous() &&
+                  (!header.defined() || (header.device() == query.device() && header.scalar_type() == at::kInt)),
+              "GaudiRT rotary: invalid validated metadata tensors");
+  c10::cuda::CUDAGuard guard(query.device());
+  const at::Tensor q = query.stride(1) == 1 ? query : query.contiguous();
+  const at::Tensor k = key.stride(1) == 1 ? key : key.contiguous();
+  const at::Tensor table = cache.contiguous();
+  auto q_out = at::empty({rows, query.size(1)}, query.options().memory_format(at::MemoryFormat::Contiguous));
+  auto k_out = at::empty({rows, key.size(1)}, key.options().memory_format(at::MemoryFormat::Contiguous));
+  check_status(gk_rotary_bf16(q.data_ptr(), k.data_ptr(), q.stride(0), k.stride(0), table.data_ptr(), table.size(0),
+                              positions.data_ptr<int32_t>(), rows, query.size(1), key.size(1), (int)head_dim,
+                              (int)rotary_dim, is_neox ? 1 : 0, q_out.data_ptr(), k_out.data_ptr(),
+                              device_status(query.device().index()).data_ptr<int32_t>(),
+                              stream_of(at::cuda::getCurrentCUDAStream())),
+               "rotary");
+  return {q_out, k_out};
+}
+
+std::tuple<at::Tensor, at::Tensor> rotary_embedding(const at::Tensor& query, const at::Tensor& key, const at::Tensor& cache,
+                                                    const c10::intrusive_ptr<PagedMetadata>& metadata, int64_t head_dim,
+                                                    int64_t rotary_dim, bool is_neox) {
+  TORCH_CHECK(metadata, "GaudiRT rotary: metadata is required");
+  return rotary_embedding_validated(query, key, cache, metadata->rotary_positions(), metadata->rotary_header(),
+                                    metadata->context(), head_dim, rotary_dim, is_neox);
+}
+
+// Positions come from a device tensor: the range check happens in the kernel (status word).
+std::tuple<at::Tensor, at::Tensor> rotary_embedding_positions(const at::Tensor& query, const at::Tensor& key,
+                                                              const at::Tensor& cache, const at::Tensor& positions,
+                                                              int64_t head_dim, int64_t rotary_dim, bool is_neox) {
+  TORCH_CHECK(positions.is_cuda() && positions.dim() == 1 &&
+                  (positions.scalar_type() == at::kInt || positions.scalar_type() == at::kLong),
+              "GaudiRT rotary: invalid validated metadata tensors");
+  return rotary_embedding_validated(query, key, cache, positions.to(at::kInt).contiguous(), at::Tensor(),
+                                    cache.dim() == 2 ? cache.size(0) : 0, head_dim, rotary_dim, is_neox);
+}
+
 // Reads and clears the device status word of the current device (synchronises the stream).
 int64_t take_device_status() {
   auto& word = device_status(at::cuda::current_device());
@@ -467,6 +577,15 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_paged_attn_validated(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "Tensor locations, Tensor requests, Tensor positions, Tensor mapping, Tensor header, "
         "int head_dim, float scale, float softcap=0.0, int sliding_window=-1) -> Tensor");
+  m.def("rms_norm(Tensor input, Tensor weight, float epsilon, float weight_offset=0.0) -> Tensor");
+  m.def("fused_add_rms_norm(Tensor input, Tensor residual, Tensor weight, float epsilon, float weight_offset=0.0) -> (Tensor, Tensor)");
+  m.def("rotary_embedding(Tensor query, Tensor key, Tensor cache, "
+        "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, int rotary_dim, bool is_neox) "
+        "-> (Tensor, Tensor)");
+  m.def("rotary_embedding_positions(Tensor query, Tensor key, Tensor cache, Tensor positions, "
+        "int head_dim, int rotary_dim, bool is_neox) -> (Tensor, Tensor)");
+  m.def("_rotary_embedding_validated(Tensor query, Tensor key, Tensor cache, Tensor positions, "
+        "Tensor header, int context, int head_dim, int rotary_dim, bool is_neox) -> (Tensor, Tensor)");
   m.def("_allocate_paged_kv(int layers, int slots, int heads, int head_dim) -> Tensor", &gaudirt_b200::allocate_paged_kv);
   m.def("_paged_attn_kv_tile(int rows) -> int", &gaudirt_b200::paged_attn_kv_tile);
   m.def("_take_device_status() -> int", &gaudirt_b200::take_device_status);
@@ -475,4 +594,9 @@ TORCH_LIBRARY(gaudirt, m) {
 TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("paged_attn", TORCH_FN(gaudirt_b200::paged_attn));
   m.impl("_paged_attn_validated", TORCH_FN(gaudirt_b200::paged_attn_validated));
+  m.impl("rms_norm", TORCH_FN(gaudirt_b200::rms_norm));
+  m.impl("fused_add_rms_norm", TORCH_FN(gaudirt_b200::fused_add_rms_norm));
+  m.impl("rotary_embedding", TORCH_FN(gaudirt_b200::rotary_embedding));
+  m.impl("rotary_embedding_positions", TORCH_FN(gaudirt_b200::rotary_embedding_positions));
+  m.impl("_rotary_embedding_validated", TORCH_FN(gaudirt_b200::rotary_embedding_validated));
 }

@@ -156,6 +156,45 @@ GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o,
                                int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
                                int head_dim, gk_stream_t stream);
 
+/* ---- front of a decode layer ---------------------------------------------------------------
+ * Replace gk_rms_norm_bf16_v1 / gk_fused_add_rms_norm_bf16_v1 (src/bridge/fx_op_lowering.cpp:450-478,
+ * entry checks src/bridge/eager_ops.cpp:1140-1212):
+ *   u = bf16(x + residual)              (fused form only; written to `u`)
+ *   y = bf16(u * rsqrt(mean(u^2) + epsilon) * (weight + weight_offset))
+ * x, residual: [rows, hidden] with the given row strides (elements); y, u: [rows, hidden]
+ * contiguous; weight: [hidden]; hidden <= 8192.  Each boundary is rounded once from fp64. */
+GK_API int gk_rms_norm_bf16(const void* x, const void* weight, float epsilon, float weight_offset,
+                     int64_t rows, int64_t hidden, int64_t x_row_stride, void* y,
+                     gk_stream_t stream);
+GK_API int gk_fused_add_rms_norm_bf16(const void* x, const void* residual, const void* weight,
+                               float epsilon, float weight_offset, int64_t rows, int64_t hidden,
+                               int64_t x_row_stride, int64_t residual_row_stride, void* y,
+                               void* u, gk_stream_t stream);
+
+/* Replaces gk_rotary_bf16_v1 / gk_rotary_pos_bf16_v1 (src/bridge/generic_private_use1.cpp:295-418,
+ * src/bridge/bucket_program.cpp:499-516): per head of q [rows, q_width] and k [rows, k_width],
+ * with (cos, sin) = cache[positions[row]] (cache [cache_rows, rotary_dim] = cos || sin):
+ *   neox: pairs (i, i + rotary_dim/2), otherwise pairs (2i, 2i+1);
+ *   a' = bf16(a*cos - b*sin), b' = bf16(b*cos + a*sin); elements past rotary_dim are copied.
+ * q_out / k_out are contiguous.  A position outside [0, cache_rows) passes the row through
+ * unrotated and sets GK_DEV_BAD_SLOT in *status. */
+GK_API int gk_rotary_bf16(const void* q, const void* k, int64_t q_row_stride, int64_t k_row_stride,
+                   const void* cache, int64_t cache_rows, const int32_t* positions, int64_t rows,
+                   int64_t q_width, int64_t k_width, int head_dim, int rotary_dim, int is_neox,
+                   void* q_out, void* k_out, int32_t* status, gk_stream_t stream);
+
+/* gk_rotary_bf16 fused with gk_kv_store_head_major_bf16 (the two reference kernels above it in
+ * the decoder layer, tests/frozen_same_geometry_layer_smoke.py:22-37, as one launch): the rotated
+ * K row and the V row go straight to slot locations[row] of the head-major pool; k_out may be
+ * NULL when the rotated K is not needed elsewhere. */
+GK_API int gk_rotary_kv_store_bf16(const void* q, const void* k, const void* v, int64_t q_row_stride,
+                            int64_t k_row_stride, int64_t v_row_stride, const void* cache,
+                            int64_t cache_rows, const int32_t* positions,
+                            const int32_t* locations, int64_t rows, int64_t q_width,
+                            int64_t k_width, int head_dim, int rotary_dim, int is_neox,
+                            void* q_out, void* k_out, void* pool_k, void* pool_v, int64_t slots,
+                            int32_t* status, gk_stream_t stream);
+
 /* ---- attention without any device allocation ---------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that must not
  * allocate device memory on their hot path: a serving engine that has handed all HBM to its own
