@@ -28,13 +28,13 @@ struct AttnParams {
   const int32_t* table;
   const int32_t* table_rows;
   const int32_t* work;
-  __nv_bfloat16* out;
+  __nv_bfloat16* out[GK_MAX_OUTPUTS];   // every destination receives the same rows (peers under TP)
   float* part_ml;
   float* part_o;
   int32_t* status;
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
-  int window, page_shift, q_heads, kv_heads, group;
+  int window, page_shift, q_heads, kv_heads, group, n_out;
 };
 
 template <int D, int WARPS, int STAGES>
@@ -310,8 +310,8 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       uint2 packed;
       packed.x = pack_bf16(acc.x * inv, acc.y * inv);
       packed.y = pack_bf16(acc.z * inv, acc.w * inv);
-      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r) * p.out_stride + (int64_t)(head * G + gq) * D + c4 * 4;
-      *reinterpret_cast<uint2*>(dst) = packed;
+      const int64_t at = (int64_t)(first_row + r) * p.out_stride + (int64_t)(head * G + gq) * D + c4 * 4;
+      for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint2*>(p.out[dst] + at) = packed;
     } else {
       const int64_t entry = (int64_t)partial_base + (int64_t)r * p.q_heads + head * G + gq;
       *reinterpret_cast<float4*>(p.part_o + entry * D + c4 * 4) = acc;
@@ -320,14 +320,19 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
   }
 }
 
+struct OutputList {
+  __nv_bfloat16* ptr[GK_MAX_OUTPUTS];
+  int n;
+};
+
 // Merge the split states of each combine record in split order and write bf16(O / l).
 // One warp per (row, query head) entry; lanes stride over head_dim in float4 steps.
 template <int D>
 __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __restrict__ part_ml,
                                                                 const float* __restrict__ part_o,
                                                                 const int32_t* __restrict__ combine,
-                                                                __nv_bfloat16* __restrict__ out,
-                                                                int64_t out_stride, int q_heads) {
+                                                                const OutputList outs, int64_t out_stride,
+                                                                int q_heads) {
   const int4 rec = __ldg(reinterpret_cast<const int4*>(combine) + blockIdx.x);
   const int first_row = rec.x, n_rows = rec.y, base = rec.z, n_splits = rec.w;
   const int entries = n_rows * q_heads;
@@ -369,8 +374,8 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
         uint2 packed;
         packed.x = pack_bf16(acc[v].x * inv, acc[v].y * inv);
         packed.y = pack_bf16(acc[v].z * inv, acc[v].w * inv);
-        __nv_bfloat16* dst = out + (int64_t)(first_row + r) * out_stride + (int64_t)h * D + (v * 32 + lane) * 4;
-        *reinterpret_cast<uint2*>(dst) = packed;
+        const int64_t at = (int64_t)(first_row + r) * out_stride + (int64_t)h * D + (v * 32 + lane) * 4;
+        for (int dst = 0; dst < outs.n; ++dst) *reinterpret_cast<uint2*>(outs.ptr[dst] + at) = packed;
       }
     }
   }
@@ -400,14 +405,18 @@ int launch_attn(const AttnParams& p, int64_t n_work, cudaStream_t stream) {
 }  // namespace
 }  // namespace gk
 
-extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
-                                  int64_t slots, const int32_t* table, int64_t table_stride,
-                                  int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
-                                  const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
-                                  float* part_ml, float* part_o, float scale, float softcap, int window,
-                                  int q_heads, int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
+extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                        int64_t slots, const int32_t* table, int64_t table_stride,
+                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
+                                        const int32_t* work, int64_t n_work, void* const* outs, int n_outs,
+                                        int64_t out_row_stride, float* part_ml, float* part_o, float scale,
+                                        float softcap, int window, int q_heads, int kv_heads, int head_dim,
+                                        int32_t* status, gk_stream_t stream) {
   if (n_work == 0) return GK_OK;
-  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 || table_entry_stride <= 0 ||
+  if (!outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS) return GK_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < n_outs; ++i)
+    if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 7)) return GK_ERR_INVALID_ARGUMENT;
+  if (!q || !pool_k || !pool_v || !table || !work || n_work < 0 || slots <= 0 || table_stride < 0 || table_entry_stride <= 0 ||
       page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
       !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
     return GK_ERR_INVALID_ARGUMENT;
@@ -417,8 +426,7 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
   if (n_work * kv_heads > 0x7fffffffLL) return GK_ERR_UNSUPPORTED;
   // K/V rows are moved in 16-byte pieces and the result is stored 8 bytes at a time.
   if ((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v)) & 15) return GK_ERR_INVALID_ARGUMENT;
-  if ((reinterpret_cast<uintptr_t>(out) & 7) || (out_row_stride & 3) || (reinterpret_cast<uintptr_t>(work) & 15) ||
-      (reinterpret_cast<uintptr_t>(q) & 1))
+  if ((out_row_stride & 3) || (reinterpret_cast<uintptr_t>(work) & 15) || (reinterpret_cast<uintptr_t>(q) & 1))
     return GK_ERR_INVALID_ARGUMENT;
   if (part_ml && ((reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15)))
     return GK_ERR_INVALID_ARGUMENT;
@@ -430,7 +438,8 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
   p.table_rows = table_rows;
   p.entry_stride = table_entry_stride;
   p.work = work;
-  p.out = static_cast<__nv_bfloat16*>(out);
+  for (int i = 0; i < n_outs; ++i) p.out[i] = static_cast<__nv_bfloat16*>(outs[i]);
+  p.n_out = n_outs;
   p.part_ml = part_ml;
   p.part_o = part_o;
   p.status = status;
@@ -453,17 +462,36 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
   }
 }
 
-extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
-                                          int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
-                                          int head_dim, gk_stream_t stream) {
+extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                  int64_t slots, const int32_t* table, int64_t table_stride,
+                                  int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
+                                  const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
+                                  float* part_ml, float* part_o, float scale, float softcap, int window,
+                                  int q_heads, int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
+  void* const outs[1] = {out};
+  return gk_paged_attn_multi_bf16(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
+                                  page_tokens, table_rows, work, n_work, outs, 1, out_row_stride, part_ml, part_o, scale,
+                                  softcap, window, q_heads, kv_heads, head_dim, status, stream);
+}
+
+extern "C" int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
+                                                int64_t n_combine, void* const* outs, int n_outs,
+                                                int64_t out_row_stride, int q_heads, int head_dim,
+                                                gk_stream_t stream) {
   if (n_combine == 0) return GK_OK;
-  if (!part_ml || !part_o || !combine || !out || n_combine < 0 || n_combine > 0x7fffffffLL || q_heads <= 0)
+  if (!part_ml || !part_o || !combine || !outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS || n_combine < 0 ||
+      n_combine > 0x7fffffffLL || q_heads <= 0)
     return GK_ERR_INVALID_ARGUMENT;
-  if ((reinterpret_cast<uintptr_t>(out) & 7) || (out_row_stride & 3) || (reinterpret_cast<uintptr_t>(combine) & 15) ||
+  gk::OutputList o{};
+  o.n = n_outs;
+  for (int i = 0; i < n_outs; ++i) {
+    if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 7)) return GK_ERR_INVALID_ARGUMENT;
+    o.ptr[i] = static_cast<__nv_bfloat16*>(outs[i]);
+  }
+  if ((out_row_stride & 3) || (reinterpret_cast<uintptr_t>(combine) & 15) ||
       (reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15))
     return GK_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  auto* o = static_cast<__nv_bfloat16*>(out);
   switch (head_dim) {
     case 64: gk::paged_attn_combine_kernel<64><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
     case 128: gk::paged_attn_combine_kernel<128><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
@@ -471,6 +499,14 @@ extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* par
     default: return GK_ERR_UNSUPPORTED;
   }
   return gk::check_launch();
+}
+
+extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
+                                          int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
+                                          int head_dim, gk_stream_t stream) {
+  void* const outs[1] = {out};
+  return gk_paged_attn_combine_multi_bf16(part_ml, part_o, combine, n_combine, outs, 1, out_row_stride, q_heads,
+                                          head_dim, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -350,11 +350,13 @@ at::Tensor allocate_paged_kv(int64_t layers, int64_t slots, int64_t heads, int64
 
 int64_t paged_attn_kv_tile(int64_t) { return GK_REFERENCE_KV_TILE; }
 
-at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
-                                at::Tensor& key_pool, at::Tensor& value_pool, const at::Tensor& locations,
-                                const at::Tensor& /*requests*/, const at::Tensor& /*positions*/,
-                                const at::Tensor& plan_tensor, const at::Tensor& /*header*/, int64_t head_dim,
-                                double scale, double softcap, int64_t sliding_window) {
+// Shared body of the attention operators.  With `pushed` empty the result is a fresh tensor;
+// otherwise every tensor of `pushed` (one per tensor-parallel rank, peer-mapped, same shape and
+// strides) receives the rows and nothing is returned.
+at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                           at::Tensor& key_pool, at::Tensor& value_pool, const at::Tensor& locations,
+                           const at::Tensor& plan_tensor, int64_t head_dim, double scale, double softcap,
+                           int64_t sliding_window, const std::vector<at::Tensor>& pushed) {
   const auto& plan = plan_of(plan_tensor);
   const auto device = plan_tensor.device();
   c10::cuda::CUDAGuard guard(device);
@@ -389,7 +391,22 @@ at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, 
   const at::Tensor q = query.stride(1) == 1 ? query : query.contiguous();
   const at::Tensor k = key.stride(1) == 1 ? key : key.contiguous();
   const at::Tensor v = value.stride(1) == 1 ? value : value.contiguous();
-  auto output = at::empty({plan.rows, query.size(1)}, query.options().memory_format(at::MemoryFormat::Contiguous));
+  at::Tensor output;
+  std::vector<void*> outs;
+  int64_t out_stride = query.size(1);
+  if (pushed.empty()) {
+    output = at::empty({plan.rows, query.size(1)}, query.options().memory_format(at::MemoryFormat::Contiguous));
+    outs.push_back(output.data_ptr());
+  } else {
+    TORCH_CHECK(pushed.size() <= GK_MAX_OUTPUTS, "GaudiRT attention: too many gather destinations");
+    out_stride = pushed.front().stride(0);
+    for (const auto& t : pushed) {
+      TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.size(0) == plan.rows &&
+                      t.size(1) == query.size(1) && t.stride(1) == 1 && t.stride(0) == out_stride,
+                  "GaudiRT attention: gather destinations must be BF16 [rows, q_width] column blocks of equal stride");
+      outs.push_back(t.data_ptr());
+    }
+  }
   int32_t* status = device_status(device.index()).data_ptr<int32_t>();
   const gk_stream_t s = stream_of(stream);
   check_status(gk_kv_store_head_major_bf16(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
@@ -397,18 +414,58 @@ at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, 
                                            value_pool.data_ptr(), plan.slots, (int)plan.kv_heads, (int)head_dim, status, s),
                "KV store");
   const int32_t* words = plan.buffer.data_ptr<int32_t>();
-  check_status(gk_paged_attn_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
-                                  plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride, plan.page_tokens,
-                                  plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr, words,
-                                  plan.n_work, output.data_ptr(), output.stride(0), plan.part_ml.data_ptr<float>(),
-                                  plan.part_o.data_ptr<float>(), scale_f, softcap_f, (int)sliding_window,
-                                  (int)plan.query_heads, (int)plan.kv_heads, (int)head_dim, status, s),
+  check_status(gk_paged_attn_multi_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
+                                        plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride,
+                                        plan.page_tokens,
+                                        plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr, words,
+                                        plan.n_work, outs.data(), (int)outs.size(), out_stride,
+                                        plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(), scale_f, softcap_f,
+                                        (int)sliding_window, (int)plan.query_heads, (int)plan.kv_heads, (int)head_dim,
+                                        status, s),
                "paged attention");
-  check_status(gk_paged_attn_combine_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
-                                          words + plan.combine_offset, plan.n_combine, output.data_ptr(), output.stride(0),
-                                          (int)plan.query_heads, (int)head_dim, s),
+  check_status(gk_paged_attn_combine_multi_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
+                                                words + plan.combine_offset, plan.n_combine, outs.data(), (int)outs.size(),
+                                                out_stride, (int)plan.query_heads, (int)head_dim, s),
                "split-KV combine");
   return output;
+}
+
+at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                at::Tensor& key_pool, at::Tensor& value_pool, const at::Tensor& locations,
+                                const at::Tensor& /*requests*/, const at::Tensor& /*positions*/,
+                                const at::Tensor& plan_tensor, const at::Tensor& /*header*/, int64_t head_dim,
+                                double scale, double softcap, int64_t sliding_window) {
+  return paged_attn_impl(query, key, value, key_pool, value_pool, locations, plan_tensor, head_dim, scale, softcap,
+                         sliding_window, {});
+}
+
+// Attention whose epilogue is the tensor-parallel output gather: the rows are stored into every
+// tensor of `outputs` (this rank's column block of each rank's gathered activation).  Not in the
+// reference, which gathers with a separate collective (src/bridge/segmented_runner.cpp:170-191).
+void paged_attn_push(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, at::Tensor& key_pool,
+                     at::Tensor& value_pool, const at::Tensor& locations, const at::Tensor& plan_tensor,
+                     at::TensorList outputs, int64_t head_dim, double scale, double softcap, int64_t sliding_window) {
+  TORCH_CHECK(!outputs.empty(), "GaudiRT attention: gather destinations are required");
+  paged_attn_impl(query, key, value, key_pool, value_pool, locations, plan_tensor, head_dim, scale, softcap,
+                  sliding_window, outputs.vec());
+}
+
+// Completion barrier after the pushes: flags[p] aliases rank p's int32[world] flag array.
+void peer_barrier(at::TensorList flags, int64_t rank, int64_t epoch, int64_t max_cycles) {
+  TORCH_CHECK(!flags.empty() && flags.size() <= GK_MAX_OUTPUTS && rank >= 0 && rank < (int64_t)flags.size(),
+              "GaudiRT: invalid peer barrier arguments");
+  std::vector<int32_t*> ptrs;
+  for (const auto& f : flags) {
+    TORCH_CHECK(f.is_cuda() && f.scalar_type() == at::kInt && f.is_contiguous() && f.numel() >= (int64_t)flags.size(),
+                "GaudiRT: peer barrier flags must be int32 device arrays of at least world entries");
+    ptrs.push_back(f.data_ptr<int32_t>());
+  }
+  const auto device = flags[rank].device();
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_peer_barrier(ptrs.data(), (int)rank, (int)flags.size(), (int32_t)epoch, max_cycles,
+                               device_status(device.index()).data_ptr<int32_t>(),
+                               stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "peer barrier");
 }
 
 at::Tensor paged_attn(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, at::Tensor& key_pool,
@@ -577,6 +634,10 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_paged_attn_validated(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "Tensor locations, Tensor requests, Tensor positions, Tensor mapping, Tensor header, "
         "int head_dim, float scale, float softcap=0.0, int sliding_window=-1) -> Tensor");
+  m.def("_paged_attn_push(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+        "Tensor locations, Tensor plan, Tensor(c!)[] outputs, int head_dim, float scale, float softcap=0.0, "
+        "int sliding_window=-1) -> ()");
+  m.def("_peer_barrier(Tensor(a!)[] flags, int rank, int epoch, int max_cycles) -> ()");
   m.def("rms_norm(Tensor input, Tensor weight, float epsilon, float weight_offset=0.0) -> Tensor");
   m.def("fused_add_rms_norm(Tensor input, Tensor residual, Tensor weight, float epsilon, float weight_offset=0.0) -> (Tensor, Tensor)");
   m.def("rotary_embedding(Tensor query, Tensor key, Tensor cache, "
@@ -594,6 +655,8 @@ TORCH_LIBRARY(gaudirt, m) {
 TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("paged_attn", TORCH_FN(gaudirt_b200::paged_attn));
   m.impl("_paged_attn_validated", TORCH_FN(gaudirt_b200::paged_attn_validated));
+  m.impl("_paged_attn_push", TORCH_FN(gaudirt_b200::paged_attn_push));
+  m.impl("_peer_barrier", TORCH_FN(gaudirt_b200::peer_barrier));
   m.impl("rms_norm", TORCH_FN(gaudirt_b200::rms_norm));
   m.impl("fused_add_rms_norm", TORCH_FN(gaudirt_b200::fused_add_rms_norm));
   m.impl("rotary_embedding", TORCH_FN(gaudirt_b200::rotary_embedding));

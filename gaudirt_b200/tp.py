@@ -1,0 +1,135 @@
+"""Tensor-parallel use of the path: KV heads are sharded over the ranks of one node and the
+attention output is gathered along the last dimension before o_proj.
+
+The reference expresses that gather as the `AllGatherDimLast` collective of its compiled schedule
+(``src/bridge/segmented_runner.cpp:170-191``: an HCCL all-gather into scratch followed by a
+transpose recipe).  Two forms are provided here, one process per GPU, `torch.distributed` (NCCL)
+for the plumbing:
+
+* ``mode="nccl"``  -- `all_gather_into_tensor` over NVLink/NVSwitch plus the rank-major -> last-dim
+  permutation; the baseline.
+* ``mode="push"``  -- the gather is fused into the attention epilogue: every rank's kernels store
+  their ``[rows, cols]`` block straight into column block `rank` of every peer's gathered
+  ``[rows, world*cols]`` buffer (plain peer stores into symmetric memory), followed by one small
+  completion barrier with a bounded wait.  No collective kernel and no transpose run.
+
+Buffers are double-buffered: a buffer is written again only after one full barrier has passed, so a
+peer still reading layer L's activation never sees layer L+1's stores.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class HeadShard:
+    """Which heads a rank owns: rank r of `world` takes KV heads [r*Hkv/W, (r+1)*Hkv/W) and the query
+    heads of those groups (the caller's column-parallel QKV projection already produces them)."""
+    rank: int
+    world: int
+    q_heads: int
+    kv_heads: int
+
+    def __post_init__(self):
+        if self.world <= 0 or not (0 <= self.rank < self.world):
+            raise ValueError("GaudiRT: invalid tensor-parallel rank")
+        if self.kv_heads % self.world or self.q_heads % self.kv_heads:
+            raise ValueError("GaudiRT: KV heads must divide evenly over the tensor-parallel ranks")
+
+    @property
+    def local_kv_heads(self) -> int:
+        return self.kv_heads // self.world
+
+    @property
+    def local_q_heads(self) -> int:
+        return self.q_heads // self.world
+
+    def kv_head_range(self):
+        n = self.local_kv_heads
+        return range(self.rank * n, (self.rank + 1) * n)
+
+    def q_columns(self, head_dim: int) -> slice:
+        n = self.local_q_heads * head_dim
+        return slice(self.rank * n, (self.rank + 1) * n)
+
+    def kv_columns(self, head_dim: int) -> slice:
+        n = self.local_kv_heads * head_dim
+        return slice(self.rank * n, (self.rank + 1) * n)
+
+
+class OutputGather:
+    """`[rows, cols]` per rank -> `[rows, world*cols]`, rank-major along the last dimension."""
+
+    # bound of the completion wait in SM clock cycles (~1 s at 2 GHz); expiry sets a status bit
+    WAIT_CYCLES = 2_000_000_000
+
+    def __init__(self, rows: int, cols: int, device, group=None, mode: str = "push", depth: int = 2):
+        if mode not in ("push", "nccl"):
+            raise ValueError("GaudiRT: gather mode must be 'push' or 'nccl'")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.rows, self.cols, self.mode, self.depth = rows, cols, mode, depth
+        self.device = torch.device(device)
+        self._turn = 0
+        self._epoch = 0
+        if mode == "nccl" or self.world == 1:
+            self.mode = "nccl"
+            self._staging = torch.empty(self.world, rows, cols, dtype=torch.bfloat16, device=self.device)
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+        width = self.world * cols
+        self._local = symm_mem.empty(depth, rows, width, dtype=torch.bfloat16, device=self.device)
+        self._flags = symm_mem.empty(max(self.world, 8), dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        self._buf_handle = symm_mem.rendezvous(self._local, self.group)
+        self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
+        block = slice(self.rank * cols, (self.rank + 1) * cols)
+        self._peers = []            # [depth][peer] -> my column block of that peer's buffer
+        for d in range(depth):
+            per = []
+            for p in range(self.world):
+                buf = self._local if p == self.rank else self._buf_handle.get_buffer(
+                    p, (depth, rows, width), torch.bfloat16)
+                per.append(buf[d][:, block])
+            self._peers.append(per)
+        self._peer_flags = [self._flags if p == self.rank else
+                            self._flag_handle.get_buffer(p, (self._flags.numel(),), torch.int32)
+                            for p in range(self.world)]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)          # every rank's flags are zero before anyone signals
+
+    def destinations(self):
+        """Tensors the attention epilogue of this step must write (push mode)."""
+        return self._peers[self._turn % self.depth]
+
+    def attention(self, query, key, value, key_pool, value_pool, metadata, head_dim, scale, softcap=0.0,
+                  sliding_window=-1):
+        """Paged attention on this rank's heads followed by the gather; returns `[rows, world*cols]`."""
+        q_heads, kv_heads = query.size(1) // head_dim, key_pool.size(1)
+        if self.mode == "nccl":
+            out = torch.ops.gaudirt.paged_attn(query, key, value, key_pool, value_pool, metadata, head_dim, scale,
+                                               softcap, sliding_window)
+            return self.gather(out)
+        plan = (metadata.attention_plan_for(q_heads, kv_heads, head_dim, sliding_window) if sliding_window > 0
+                else metadata.attention_plan(q_heads, kv_heads, head_dim))
+        torch.ops.gaudirt._paged_attn_push(query, key, value, key_pool, value_pool, metadata.row_locations(), plan,
+                                           self.destinations(), head_dim, scale, softcap, sliding_window)
+        return self.finish()
+
+    def gather(self, out):
+        """Baseline: NCCL all-gather + permutation of an already computed `[rows, cols]` block."""
+        if self.world == 1:
+            return out
+        dist.all_gather_into_tensor(self._staging.view(self.world * self.rows, self.cols), out, group=self.group)
+        return self._staging.permute(1, 0, 2).reshape(self.rows, self.world * self.cols)
+
+    def finish(self):
+        """Push mode: signal + bounded wait, then hand out the gathered buffer of this step."""
+        self._epoch += 1
+        torch.ops.gaudirt._peer_barrier(self._peer_flags, self.rank, self._epoch, self.WAIT_CYCLES)
+        gathered = self._local[self._turn % self.depth]
+        self._turn += 1
+        return gathered

@@ -156,6 +156,35 @@ GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o,
                                int64_t n_combine, void* out, int64_t out_row_stride, int q_heads,
                                int head_dim, gk_stream_t stream);
 
+/* ---- tensor-parallel output gather fused into the attention epilogue ----------------------
+ * Replaces AllGatherDimLast after attention (src/bridge/segmented_runner.cpp:170-191,
+ * src/bridge/communicator.cpp:56-116: hcclAllGather into scratch + a transpose recipe): with KV
+ * heads sharded over `world` ranks, rank r's kernels store their [rows, cols] result into
+ * column block r of the gathered [rows, world*cols] activation of EVERY rank, i.e. `outs[p]`
+ * is (peer p's gathered buffer) + r*cols with out_row_stride = world*cols.  Peer buffers are
+ * ordinary peer-mapped device memory (CUDA IPC / symmetric memory); the kernels only issue
+ * plain stores to them.  The multi forms are otherwise identical to the single-output forms. */
+#define GK_MAX_OUTPUTS 8
+GK_API int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                             const void* pool_v, int64_t slots, const int32_t* table,
+                             int64_t table_stride, int64_t table_entry_stride, int page_tokens,
+                             const int32_t* table_rows, const int32_t* work, int64_t n_work,
+                             void* const* outs, int n_outs, int64_t out_row_stride,
+                             float* part_ml, float* part_o, float scale, float softcap,
+                             int window, int q_heads, int kv_heads, int head_dim,
+                             int32_t* status, gk_stream_t stream);
+GK_API int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o,
+                                     const int32_t* combine, int64_t n_combine,
+                                     void* const* outs, int n_outs, int64_t out_row_stride,
+                                     int q_heads, int head_dim, gk_stream_t stream);
+/* Completion barrier that follows the pushes (replaces the wait on the collective,
+ * src/bridge/segmented_runner.cpp:489-506): flags[p] is rank p's int32[world] flag array as
+ * mapped in this process.  Writes `epoch` to slot `rank` of every peer's array, then waits
+ * until all slots of its own array have reached `epoch` (epochs only grow).  The wait gives up
+ * after max_cycles SM clock cycles and sets GK_DEV_WAIT_EXPIRED in *status; it never traps. */
+GK_API int gk_peer_barrier(int32_t* const* flags, int rank, int world, int32_t epoch,
+                    int64_t max_cycles, int32_t* status, gk_stream_t stream);
+
 /* ---- front of a decode layer ---------------------------------------------------------------
  * Replace gk_rms_norm_bf16_v1 / gk_fused_add_rms_norm_bf16_v1 (src/bridge/fx_op_lowering.cpp:450-478,
  * entry checks src/bridge/eager_ops.cpp:1140-1212):
