@@ -1,15 +1,24 @@
 #!/usr/bin/env python
-"""Paged-decode benchmark: tokens/s and KV-read HBM bandwidth at Llama-3-8B geometry.
+"""Paged-decode benchmark: tokens/s and KV-read HBM bandwidth.
 
 One step = one decode step of the whole batch through all layers: per layer one head-major KV
 store of the new token plus paged GQA attention over the whole context, each layer on its own
-KV pool.  Default workload (N = 1): batch 256, every context 4096 tokens, 32 query / 8 KV heads,
-head_dim 128, KV block 128 tokens, pool of batch*32 blocks + 10 % spare, shuffled block tables,
-bf16, 32 layers.  With N > 1 the KV heads are sharded over the ranks (tensor parallel) and the
-attention output is gathered along the last dimension (strong scaling: the batch is fixed).
+KV pool.  The default workload (`--config 2`, the one the headline metric is quoted on) is
+Llama-3-8B geometry: batch 256, every context 4096 tokens, 32 query / 8 KV heads, head_dim 128,
+KV block 128 tokens, pool of batch*32 blocks + 10 % spare, shuffled block tables, bf16, 32 layers.
 
-Inputs are synthetic (seeded); pool contents are N(0,1) bf16.  The pools together are far
-larger than L2 (4.7 GB per layer), so consecutive launches never hit in cache.
+    --config 3   skewed lengths (lognormal, median 2048, sigma 1, clipped to [16, 32768]),
+                 batch 128, 64 query / 8 KV heads, length-aware split-KV schedule
+    --config 5   fused decode layer step: fused_add_rms_norm (hidden 8192, weight_offset 1) ->
+                 rotary (theta 500000) -> KV store -> paged GQA decode, batch 64,
+                 contexts uniform [1024, 16384], 64 query / 8 KV heads
+
+With N > 1 ranks the KV heads are sharded over the ranks (tensor parallel) and the attention
+output is gathered along the last dimension, by default inside the attention epilogue
+(`--gather push`) or with NCCL (`--gather nccl`).  The batch is fixed: strong scaling.
+
+Inputs are synthetic (seeded); pool contents are N(0,1) bf16.  The pools together are far larger
+than L2, so consecutive launches never hit in cache.
 
     python bench.py --gpus 1 --steps 5 --warmup 3
     python bench.py --impl reference          # the CPU restatement of the reference on host cores
@@ -25,6 +34,7 @@ import subprocess
 import sys
 import threading
 import time
+from dataclasses import dataclass
 
 import torch
 
@@ -37,7 +47,47 @@ METRIC = "paged_decode_tokens_per_s"
 # visible K/V rows, so it is scaled to the benchmark launch by its KV bytes.
 TRAFFIC_PER_KV_BYTE = 1.0037
 TRAFFIC_SOURCE = "profiles/paged_attn_kernel_decode_b128_ctx4096_ncu_full.md, scaled by KV bytes"
-GEOM = dict(batch=256, ctx=4096, q_heads=32, kv_heads=8, head_dim=128, block=128, layers=32)
+BLOCK = 128
+HEAD_DIM = 128
+
+
+@dataclass
+class Workload:
+    name: str
+    batch: int
+    q_heads: int
+    kv_heads: int
+    layers: int
+    ctx: torch.Tensor            # [batch] context length after the store
+    front: bool = False          # fused_add_rms_norm + rotary in front of the store
+    hidden: int = 8192
+    theta: float = 500000.0
+
+    @property
+    def describe(self):
+        lo, hi = int(self.ctx.min()), int(self.ctx.max())
+        span = f"ctx {lo}" if lo == hi else f"ctx {lo}..{hi} (mean {float(self.ctx.double().mean()):.0f})"
+        steps = "fused_add_rms_norm + rotary + KV store + attention" if self.front else "KV store + attention"
+        return (f"{self.name}: batch {self.batch}, {span}, {self.q_heads}q/{self.kv_heads}kv heads, head_dim {HEAD_DIM}, "
+                f"block {BLOCK}, {self.layers} layers (independent pools), {steps} per layer")
+
+
+def make_workload(args) -> Workload:
+    from tests import cases
+    if args.config == 2:
+        batch = args.batch or 256
+        return Workload("Llama-3-8B-geometry paged decode", batch, 32, 8, args.layers or 32,
+                        torch.full((batch,), args.ctx or 4096, dtype=torch.int64))
+    if args.config == 3:
+        batch = args.batch or 128
+        return Workload("skewed-length paged decode with split-KV (70B geometry)", batch, 64, 8, args.layers or 8,
+                        cases.lognormal_contexts(batch, 20261103))
+    if args.config == 5:
+        batch = args.batch or 64
+        gen = torch.Generator().manual_seed(20261105)
+        return Workload("fused decode layer step (70B geometry)", batch, 64, 8, args.layers or 16,
+                        torch.randint(1024, 16385, (batch,), generator=gen), front=True)
+    raise SystemExit("--config must be 2, 3 or 5")
 
 
 def parse():
@@ -46,10 +96,12 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--layers", type=int, default=GEOM["layers"], help="for experiments only; 32 is the workload")
-    ap.add_argument("--batch", type=int, default=GEOM["batch"], help="for experiments only")
-    ap.add_argument("--ctx", type=int, default=GEOM["ctx"], help="for experiments only")
-    ap.add_argument("--cpu-seqs", type=int, default=64, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--config", type=int, default=2, help="2 (headline), 3 or 5")
+    ap.add_argument("--gather", default="push", choices=["push", "nccl"], help="output gather when N > 1")
+    ap.add_argument("--layers", type=int, default=0, help="experiments only; 0 = the workload's own count")
+    ap.add_argument("--batch", type=int, default=0, help="experiments only")
+    ap.add_argument("--ctx", type=int, default=0, help="experiments only (config 2)")
+    ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample; 0 = sized for a few seconds")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -99,66 +151,90 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+def workload_config(w: Workload, world: int, gather: str):
+    return {"workload": w.describe,
+            "parallelism": (f"tp{world} (KV heads sharded, attention output gathered along the last dim: {gather})"
+                            if world > 1 else "single GPU"),
+            "cache": "inputs larger than L2: every layer reads its own KV pool"}
+
+
 # --------------------------------------------------------------------------------------------
 # CPU arm: the oracle's restatement of the reference's CPU path on a bounded sample
 # --------------------------------------------------------------------------------------------
-def cpu_case(args, n_seqs):
-    from tests import cases
-    g = GEOM
-    blocks = n_seqs * (args.ctx // g["block"]) + 4
-    return cases.decode_case(n_seqs, g["q_heads"], g["kv_heads"], g["head_dim"], g["block"], blocks,
-                             [args.ctx] * n_seqs, seed=20261102)
+class CpuSample:
+    """A bounded sample of the workload (some sequences of ONE layer) for the host cores."""
+
+    def __init__(self, w: Workload, n_seqs: int):
+        from tests import cases
+        import oracle
+        n_seqs = min(n_seqs, w.batch)
+        pick = torch.linspace(0, w.batch - 1, n_seqs).round().long().unique()
+        self.w, self.ctx = w, w.ctx[pick]
+        blocks = int(((self.ctx + BLOCK - 1) // BLOCK).sum()) + 4
+        self.case = cases.decode_case(len(pick), w.q_heads, w.kv_heads, HEAD_DIM, BLOCK, blocks, self.ctx,
+                                      seed=20261100 + len(pick))
+        self.tokens = int(self.ctx.sum())
+        if w.front:
+            gen = torch.Generator().manual_seed(7)
+            self.x = torch.randn(len(pick), w.hidden, generator=gen).to(torch.bfloat16)
+            self.res = torch.randn(len(pick), w.hidden, generator=gen).to(torch.bfloat16)
+            self.gamma = (0.02 * torch.randn(w.hidden, generator=gen)).to(torch.bfloat16)
+            self.cache = oracle.rotary_cache(int(w.ctx.max()) + 1, HEAD_DIM, w.theta)
+
+    def run(self):
+        """Seconds per context token of one layer (store + attend, and the layer front if any)."""
+        import oracle
+        c, w = self.case, self.w
+        pool = c.pool.clone()
+        t0 = time.perf_counter()
+        q, k = c.q, c.k
+        if w.front:
+            oracle.fused_add_rms_norm(self.x, self.res, self.gamma, 1e-5, 1.0)
+            q = oracle.rotary_embedding(c.q, self.cache, c.positions, HEAD_DIM, HEAD_DIM, True).to(torch.bfloat16)
+            k = oracle.rotary_embedding(c.k, self.cache, c.positions, HEAD_DIM, HEAD_DIM, True).to(torch.bfloat16)
+        oracle.kv_store_head_major(pool, k, c.v, c.locations)
+        kp, vp = oracle.pool_views(pool)
+        oracle.direct_bf16_pv(q, kp, vp, c.requests, c.positions, c.mapping, w.q_heads, w.kv_heads, HEAD_DIM, c.scale)
+        return (time.perf_counter() - t0) / self.tokens
 
 
-def cpu_pass(case):
-    """Store + attend for the sample's sequences of ONE layer on the host cores (all threads):
-    seconds per (sequence, layer)."""
-    import oracle
-    g = GEOM
-    pool = case.pool.clone()
-    t0 = time.perf_counter()
-    oracle.kv_store_head_major(pool, case.k, case.v, case.locations)
-    kp, vp = oracle.pool_views(pool)
-    oracle.direct_bf16_pv(case.q, kp, vp, case.requests, case.positions, case.mapping, g["q_heads"],
-                          g["kv_heads"], g["head_dim"], case.scale)
-    return (time.perf_counter() - t0) / case.q.size(0)
+def cpu_sample_size(w: Workload, requested: int) -> int:
+    if requested:
+        return requested
+    # ~5.5 us per context token and layer on 8 cores: aim at a few seconds per pass
+    per_seq = float(w.ctx.double().mean()) * 6e-6
+    return max(2, min(w.batch, int(3.0 / per_seq)))
+
+
+def cpu_tokens_per_s(w: Workload, sec_per_token: float) -> float:
+    return w.batch / (sec_per_token * float(w.ctx.sum()) * w.layers)
 
 
 def run_reference(args):
-    """`--impl reference`: the reference's CPU implementation of the path (its Python restatement
-    in oracle/, all host threads), each step one bounded sample of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """`--impl reference`: the reference's CPU implementation of the path (its Python restatement in
+    oracle/, all host threads), each step one bounded sample of the workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
+    w = make_workload(args)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    n = args.cpu_seqs
-    case = cpu_case(args, n)
+    sample = CpuSample(w, cpu_sample_size(w, args.cpu_seqs))
     for _ in range(min(args.warmup, 2)):
-        cpu_pass(case)
+        sample.run()
     t0 = time.perf_counter()
-    per = [cpu_pass(case) for _ in range(args.steps)]
+    per = [sample.run() for _ in range(args.steps)]
     wall = time.perf_counter() - t0
-    sec_per_seq_layer = statistics.mean(per)
-    value = 1.0 / (sec_per_seq_layer * args.layers)          # tokens/s of the full workload
-    sample = f"{n} of {args.batch} sequences x 1 of {args.layers} layers per step, scaled linearly"
+    value = cpu_tokens_per_s(w, statistics.mean(per))
+    text = (f"{len(sample.ctx)} of {w.batch} sequences x 1 of {w.layers} layers per step ({sample.tokens} context tokens), "
+            "scaled linearly by context tokens")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_seq_layer * args.batch * args.layers * 1e3,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.batch / value * 1e3,
             "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(args, 1),
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(w, 1, "-"),
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": text},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0, "wall_s": wall}
     print(json.dumps(line), flush=True)
-
-
-def workload_config(args, world):
-    g = GEOM
-    return {"workload": f"Llama-3-8B-geometry paged decode: batch {args.batch}, ctx {args.ctx}, "
-                        f"{g['q_heads']}q/{g['kv_heads']}kv heads, head_dim {g['head_dim']}, block {g['block']}, "
-                        f"{args.layers} layers (independent pools), KV store + attention per layer",
-            "parallelism": f"tp{world} (KV heads sharded, output gathered along the last dim)" if world > 1 else "single GPU",
-            "cache": "inputs larger than L2: 4.7 GB of KV per layer, every layer its own pool"}
 
 
 # --------------------------------------------------------------------------------------------
@@ -167,6 +243,8 @@ def workload_config(args, world):
 def run_b200(args):
     import torch.distributed as dist
     import gaudirt_b200 as rt
+    from gaudirt_b200 import abi, tp
+    from gaudirt_b200 import raw as H
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -177,31 +255,35 @@ def run_b200(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    g = GEOM
-    B, ctx, d, blk, L = args.batch, args.ctx, g["head_dim"], g["block"], args.layers
-    assert g["kv_heads"] % world == 0, "KV heads must divide over the ranks"
-    hq, hkv = g["q_heads"] // world, g["kv_heads"] // world
-    blocks_per_seq = ctx // blk
-    n_blocks = int(B * blocks_per_seq * 1.1)
-    slots = n_blocks * blk
+    w = make_workload(args)
+    shard = tp.HeadShard(rank, world, w.q_heads, w.kv_heads)
+    B, d, L = w.batch, HEAD_DIM, w.layers
+    hq, hkv = shard.local_q_heads, shard.local_kv_heads
 
     # ---- metadata (replicated on every rank): shuffled block tables, new token at ctx-1 -------
-    gen = torch.Generator().manual_seed(20261102)
-    tables = torch.randperm(n_blocks, generator=gen)[: B * blocks_per_seq].reshape(B, blocks_per_seq).to(torch.int32)
-    pos = torch.arange(ctx)
-    mapping = (tables.long()[:, pos // blk] * blk + pos % blk).to(torch.int32).contiguous()
+    need = (w.ctx + BLOCK - 1) // BLOCK
+    n_blocks = int(int(need.sum()) * 1.1) + 1
+    slots = n_blocks * BLOCK
+    gen = torch.Generator().manual_seed(20261100 + args.config)
+    perm = torch.randperm(n_blocks, generator=gen).to(torch.int32)
+    tables = torch.zeros(B, int(need.max()), dtype=torch.int32)
+    cursor = 0
+    for b in range(B):
+        tables[b, : int(need[b])] = perm[cursor:cursor + int(need[b])]
+        cursor += int(need[b])
+    pos = torch.arange(int(need.max()) * BLOCK)
+    mapping = (tables.long()[:, pos // BLOCK] * BLOCK + pos % BLOCK).to(torch.int32).contiguous()
     requests = torch.arange(B, dtype=torch.int32)
-    positions = torch.full((B,), ctx - 1, dtype=torch.int32)
-    locations = mapping[:, ctx - 1].contiguous()
+    positions = (w.ctx - 1).to(torch.int32)
+    locations = mapping[torch.arange(B), positions.long()].contiguous()
     scale = 1.0 / math.sqrt(d)
 
     # ---- pools: layer 0 is drawn N(0,1); the others are that data rotated by a layer-specific
     # offset (same distribution, distinct HBM, seconds instead of minutes to fill) ---------------
     pool = rt._C._allocate_paged_kv(L, slots, hkv, d)
     flat0 = pool[0].view(-1)
-    step_elems = 1 << 28
-    for off in range(0, flat0.numel(), step_elems):
-        flat0[off:off + step_elems].normal_()
+    for off in range(0, flat0.numel(), 1 << 28):
+        flat0[off:off + (1 << 28)].normal_()
     for l in range(1, L):
         shift = (l * 7919 * d) % flat0.numel()
         dst = pool[l].view(-1)
@@ -209,20 +291,33 @@ def run_b200(args):
         dst[flat0.numel() - shift:].copy_(flat0[:shift])
     views = [(pool[l, 0].transpose(0, 1), pool[l, 1].transpose(0, 1)) for l in range(L)]
 
-    hgen = torch.Generator().manual_seed(20261102 + rank)
+    hgen = torch.Generator().manual_seed(20261100 + 10 * args.config + rank)
     host_q = torch.randn(L, B, hq * d, generator=hgen).to(torch.bfloat16).pin_memory()
     host_k = torch.randn(L, B, hkv * d, generator=hgen).to(torch.bfloat16).pin_memory()
     host_v = torch.randn(L, B, hkv * d, generator=hgen).to(torch.bfloat16).pin_memory()
     host_out = torch.empty(L, B, hq * d * world, dtype=torch.bfloat16).pin_memory()
-    dq, dk, dv = host_q.to(dev), host_k.to(dev), host_v.to(dev)
-    gathered = torch.empty(world, B, hq * d, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    host_in = [host_q, host_k, host_v]
+    gamma = cache = None
+    if w.front:
+        fgen = torch.Generator().manual_seed(20261199)      # the hidden state is replicated on every rank
+        host_in += [torch.randn(L, B, w.hidden, generator=fgen).to(torch.bfloat16).pin_memory() for _ in range(2)]
+        gamma = (0.02 * torch.randn(w.hidden, generator=fgen)).to(torch.bfloat16).to(dev)
+        inv = w.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+        ang = torch.arange(mapping.size(1), dtype=torch.float64)[:, None] * inv[None, :]   # covers the whole table
+        cache = torch.cat((ang.cos(), ang.sin()), dim=-1).float().to(torch.bfloat16).to(dev)
+    resident = [h.to(dev) for h in host_in]
 
-    def gather_last(out):
-        """AllGatherDimLast: [B, cols] per rank -> [B, world*cols], rank-major along the last dim."""
-        if world == 1:
-            return out
-        dist.all_gather_into_tensor(gathered.view(world * B, -1), out)
-        return gathered.permute(1, 0, 2).reshape(B, -1)
+    gather = tp.OutputGather(B, hq * d, dev, mode=args.gather) if world > 1 else None
+    lib = abi.lib()
+
+    def layer(l, md, q, k, v, x=None, res=None):
+        """One layer of the step on the current stream; returns the gathered attention output."""
+        if w.front:
+            torch.ops.gaudirt.fused_add_rms_norm(x, res, gamma, 1e-5, 1.0)
+            q, k = torch.ops.gaudirt.rotary_embedding(q, k, cache, md, d, d, True)
+        if gather is not None:
+            return gather.attention(q, k, v, views[l][0], views[l][1], md, d, scale)
+        return torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], md, d, scale)
 
     md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
     md.attention_plan(hq, hkv, d)
@@ -230,15 +325,14 @@ def run_b200(args):
     def resident_step():
         last = None
         for l in range(L):
-            out = torch.ops.gaudirt.paged_attn(dq[l], dk[l], dv[l], views[l][0], views[l][1], md, d, scale)
-            last = gather_last(out)
+            last = layer(l, md, *(t[l] for t in resident))
         return last
 
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
 
     def e2e_step():
-        """The same step from HOST buffers: metadata built from CPU tensors, per layer q/k/v copied
-        in from pinned memory and the layer's result copied back, copies overlapped with compute."""
+        """The same step from HOST buffers: metadata built from CPU tensors, per layer the inputs
+        copied in from pinned memory and the layer's result copied back, copies overlapped with compute."""
         main = torch.cuda.current_stream()
         step_md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
         step_md.attention_plan(hq, hkv, d)
@@ -246,8 +340,7 @@ def run_b200(args):
 
         def stage(l):
             with torch.cuda.stream(copy_in):
-                t = (host_q[l].to(dev, non_blocking=True), host_k[l].to(dev, non_blocking=True),
-                     host_v[l].to(dev, non_blocking=True))
+                t = tuple(h[l].to(dev, non_blocking=True) for h in host_in)
                 ev = torch.cuda.Event()
                 ev.record(copy_in)
             staged[l] = (t, ev)
@@ -256,17 +349,19 @@ def run_b200(args):
         for l in range(L):
             if l + 1 < L:
                 stage(l + 1)
-            (q, k, v), ev = staged.pop(l)
+            t, ev = staged.pop(l)
             main.wait_event(ev)
-            for t in (q, k, v):
-                t.record_stream(main)
-            out = gather_last(torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], step_md, d, scale))
+            for x in t:
+                x.record_stream(main)
+            out = layer(l, step_md, *t)
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(done)
                 out.record_stream(copy_out)
                 host_out[l].copy_(out, non_blocking=True)
+            if gather is not None and gather.mode == "push":
+                main.wait_stream(copy_out)        # the gathered buffer is reused two layers later
         main.wait_stream(copy_out)
 
     def timed(fn, steps):
@@ -296,17 +391,17 @@ def run_b200(args):
     assert status == 0, f"device status {status}"
 
     # ---- dominant kernel alone: CUDA events around every attention launch of one step ---------
-    from gaudirt_b200 import raw as H
-    from gaudirt_b200 import abi
-    seq, page = H.validate(locations, requests, positions, mapping, slots)
+    seq = torch.tensor(md.sequences(), dtype=torch.int32).reshape(-1, 4).numpy()
+    page = md.page_tokens()
     work, combine, entries = H.plan(seq, hq, hkv, d, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
     work_d = torch.from_numpy(work).to(dev)
     table = md.request_mapping()
+    dq = resident[0]
     out = torch.empty(B, hq * d, dtype=torch.bfloat16, device=dev)
     pml, po = torch.empty(max(entries, 1) * 2, device=dev), torch.empty(max(entries, 1) * d, device=dev)
-    lib, s = abi.lib(), H.stream_ptr()
+    s = H.stream_ptr()
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
-    for rep in range(2):
+    for _ in range(2):
         for l in range(L):
             events[l][0].record()
             abi.check(lib.gk_paged_attn_bf16(dq[l].data_ptr(), dq[l].stride(0), pool[l, 0].data_ptr(), pool[l, 1].data_ptr(),
@@ -324,37 +419,41 @@ def run_b200(args):
     ms_per_step = total_ms / args.steps
     tokens_s = B / ms_per_step * 1e3
     e2e_tokens_s = B / (e2e_ms / args.steps) * 1e3
-    kv_bytes = B * ctx * hkv * d * 2 * 2
-    algo_bytes = kv_bytes + 2 * B * hq * d * 2 + B * (ctx // page) * 4 + len(work) * 32
+    kv_bytes = int(w.ctx.sum()) * hkv * d * 2 * 2
+    pages = int(((w.ctx + page - 1) // page).sum())
+    algo_bytes = kv_bytes + 2 * B * hq * d * 2 + pages * 4 + len(work) * 32 + entries * (d + 2) * 4
     peak, which = peaks()
     achieved = algo_bytes / kernel_ms / 1e6
+    mine_per_layer = 2 + (1 if len(combine) else 0) + (1 if gather is not None and gather.mode == "push" else 0) + \
+        (2 if w.front else 0)
+    h2d = sum(h[0].numel() * 2 for h in host_in) * L + (3 * B + mapping.numel() + 1) * 4 + work.nbytes + combine.nbytes
     line = {
         "metric": METRIC, "value": tokens_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args, world),
+        "config": workload_config(w, world, args.gather),
         "kv_read_gbs_whole_step": kv_bytes * L * world / ms_per_step / 1e6,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": f"{which} copy bandwidth", "kernel": "paged_attn_kernel<128,4,3>",
+                     "traffic": TRAFFIC_PER_KV_BYTE * kv_bytes, "traffic_source": TRAFFIC_SOURCE,
+                     "peak_source": f"{which} copy bandwidth", "kernel": "paged_attn_kernel<128,4,3>",
                      "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": algo_bytes,
+                     "work_items": len(work), "split_blocks": len(combine),
                      "frac_of_8TBs_nominal": achieved / 8000.0},
-        "e2e": {"value": e2e_tokens_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": int(L * B * (hq + 2 * hkv) * d * 2 + (3 * B + mapping.numel() + 1) * 4 + work.nbytes),
+        "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(L * B * hq * world * d * 2)},
-        "gpu_launches": args.steps * L * (2 + (1 if len(combine) else 0)),
+        "gpu_launches": args.steps * L * mine_per_layer,
         "clocks": clocks.summary(),
     }
-    line["roofline"]["traffic"] = TRAFFIC_PER_KV_BYTE * kv_bytes
-    line["roofline"]["traffic_source"] = TRAFFIC_SOURCE
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
-        case = cpu_case(args, args.cpu_seqs)
-        cpu_pass(case)
-        sec = min(cpu_pass(case), cpu_pass(case))
-        line["cpu_baseline"] = {"value": 1.0 / (sec * L), "unit": "tokens/s", "cores": cores, "kind": "port",
-                                "sample": f"{args.cpu_seqs} of {B} sequences x 1 of {L} layers (store + direct_bf16_pv), "
-                                          "best of 2 after a warm-up, scaled linearly"}
+        sample = CpuSample(w, cpu_sample_size(w, args.cpu_seqs))
+        sample.run()
+        sec = min(sample.run(), sample.run())
+        line["cpu_baseline"] = {"value": cpu_tokens_per_s(w, sec), "unit": "tokens/s", "cores": cores, "kind": "port",
+                                "sample": f"{len(sample.ctx)} of {B} sequences x 1 of {L} layers ({sample.tokens} context "
+                                          "tokens; store + direct_bf16_pv), best of 2 after a warm-up, scaled linearly "
+                                          "by context tokens"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

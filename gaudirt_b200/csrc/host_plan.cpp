@@ -71,6 +71,9 @@ extern "C" int gk_paged_metadata_validate(const int32_t* locations, const int32_
   std::vector<int32_t> reach(n_requests, -1);
   std::unordered_map<int32_t, std::pair<int32_t, int32_t>> target;   // output slot -> (request, position)
   target.reserve((size_t)rows * 2);
+  // One bit per slot in front of the map: the prefix walk below touches every visible position,
+  // almost none of which is an output slot of this step.
+  std::vector<uint64_t> is_target(static_cast<size_t>(slots / 64 + 1), 0);
   int64_t n_seq = 0;
   for (int64_t i = 0; i < rows; ++i) {
     const int64_t slot = locations[i], request = requests[i], position = positions[i];
@@ -80,6 +83,7 @@ extern "C" int gk_paged_metadata_validate(const int32_t* locations, const int32_
       return metadata_fail("GaudiRT: output slot does not match request-to-token mapping");
     if (!target.emplace((int32_t)slot, std::make_pair((int32_t)request, (int32_t)position)).second)
       return metadata_fail("GaudiRT: duplicate output KV slot");
+    is_target[static_cast<size_t>(slot >> 6)] |= 1ull << (slot & 63);
     const bool continues = i > 0 && requests[i - 1] == request && positions[i - 1] + 1 == position;
     if (continues) {
       ++seq_out[(n_seq - 1) * 4 + 1];
@@ -99,9 +103,11 @@ extern "C" int gk_paged_metadata_validate(const int32_t* locations, const int32_
     for (int32_t position = 0; position <= reach[request]; ++position) {
       const int32_t slot = row[position];
       if (slot < 0) return metadata_fail("GaudiRT: missing KV slot in a visible prefix");
-      const auto hit = target.find(slot);
-      if (hit != target.end() && (hit->second.first != request || hit->second.second != position))
-        return metadata_fail("GaudiRT: output KV slot aliases another visible prefix position");
+      if (is_target[static_cast<size_t>(slot >> 6)] >> (slot & 63) & 1) {
+        const auto hit = target.find(slot);
+        if (hit != target.end() && (hit->second.first != request || hit->second.second != position))
+          return metadata_fail("GaudiRT: output KV slot aliases another visible prefix position");
+      }
       // A break in slot contiguity at `position` only allows pages that end there.
       if (position > 0 && slot != row[position - 1] + 1) page = std::min(page, position & -position);
     }

@@ -326,7 +326,8 @@ struct OutputList {
 };
 
 // Merge the split states of each combine record in split order and write bf16(O / l).
-// One warp per (row, query head) entry; lanes stride over head_dim in float4 steps.
+// blockIdx.x = combine record, blockIdx.y = group of four query heads, one warp per
+// (row, query head) entry; lanes stride over head_dim in float4 steps.
 template <int D>
 __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __restrict__ part_ml,
                                                                 const float* __restrict__ part_o,
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
   const int first_row = rec.x, n_rows = rec.y, base = rec.z, n_splits = rec.w;
   const int entries = n_rows * q_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int e = warp; e < entries; e += 4) {
+  for (int e = blockIdx.y * 4 + warp; e < entries; e += gridDim.y * 4) {
     float mstar = -CUDART_INF_F;
     for (int s = 0; s < n_splits; ++s) {
       const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml) + (int64_t)base + (int64_t)s * entries + e);
@@ -492,10 +493,13 @@ extern "C" int gk_paged_attn_combine_multi_bf16(const float* part_ml, const floa
       (reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15))
     return GK_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // Four entries per CTA; a decode record (one row) is covered in one pass, records with more
+  // rows loop over them.
+  const dim3 grid((unsigned)n_combine, (unsigned)((q_heads + 3) / 4));
   switch (head_dim) {
-    case 64: gk::paged_attn_combine_kernel<64><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
-    case 128: gk::paged_attn_combine_kernel<128><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
-    case 256: gk::paged_attn_combine_kernel<256><<<(unsigned)n_combine, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    case 64: gk::paged_attn_combine_kernel<64><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    case 128: gk::paged_attn_combine_kernel<128><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
+    case 256: gk::paged_attn_combine_kernel<256><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
     default: return GK_ERR_UNSUPPORTED;
   }
   return gk::check_launch();

@@ -33,8 +33,12 @@ def _worker(rank, world, port, result):
         blocks = int(((ctx + 127) // 128).sum()) + 2
         shard = tp.HeadShard(rank, world, q_heads, kv_heads)
         hq, hkv = shard.local_q_heads, shard.local_kv_heads
-        layer_cases = [cases.decode_case(len(ctx), q_heads, kv_heads, d, 128, blocks, ctx, seed=500 + l) for l in range(layers)]
-        base = layer_cases[0]
+        import dataclasses
+        base = cases.decode_case(len(ctx), q_heads, kv_heads, d, 128, blocks, ctx, seed=500)
+        layer_cases = [base]
+        for l in range(1, layers):           # same block tables for every layer, fresh activations and pools
+            other = cases.decode_case(len(ctx), q_heads, kv_heads, d, 128, blocks, ctx, seed=500 + l)
+            layer_cases.append(dataclasses.replace(base, q=other.q, k=other.k, v=other.v, pool=other.pool))
         md = rt.PagedMetadata(base.locations, base.requests, base.positions, base.mapping, base.slots)
         md._set_split_tokens(256)                                  # exercise the split-KV combine as well
         outs = {}
@@ -51,7 +55,7 @@ def _worker(rank, world, port, result):
             outs[mode] = got
         ok = rt._C._take_device_status() == 0
         for c, a, b in zip(layer_cases, outs["nccl"], outs["push"]):
-            ok = ok and a.shape == (len(ctx), q_heads * d) and torch.equal(a.view(torch.int16), b.view(torch.int16))
+            assert a.shape == (len(ctx), q_heads * d) and torch.equal(a.view(torch.int16), b.view(torch.int16)), 'push != nccl'
             ref_pool = c.pool.clone()
             oracle.kv_store_head_major(ref_pool, c.k, c.v, c.locations)
             kp, vp = oracle.pool_views(ref_pool)
