@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <array>
 #include <climits>
+#include <functional>
 #include <cstdint>
 #include <numeric>
 #include <string>
@@ -145,12 +146,87 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
       total_span += blocks.back().hi - lo;
     }
   }
-  // Longest KV range of one work item: aim at four CTAs' worth of work per resident CTA slot
-  // (two CTAs per SM), never below 256 tokens, in multiples of the 64 tokens four warps eat.
+  // How a block's KV range is cut for a given longest-range limit: equal pieces, multiples of the
+  // 64 tokens four warps eat, and no cut for ranges within 25 % of the limit.
+  auto cut = [](int64_t span, int64_t chunk, int64_t& splits, int64_t& per) {
+    splits = 1;
+    per = span;
+    if (span > chunk + chunk / 4) {
+      splits = (span + chunk - 1) / chunk;
+      per = round_up((span + splits - 1) / splits, 64);
+      splits = (span + per - 1) / per;
+    }
+  };
+  // Longest KV range of one work item.  The grid is (work items x KV heads) CTAs, two resident
+  // per SM, handed out longest first by the hardware scheduler; the cost of a candidate limit is
+  // the makespan of that list schedule (a CTA costs its tokens plus a fixed prologue/epilogue)
+  // plus the split-state traffic of the combine.  Candidates: the throughput heuristic (about
+  // four CTAs per resident slot) and the longest range divided by small integers.
   int64_t chunk = split_tokens;
-  if (chunk == 0) {
-    const int64_t want = (int64_t)sm_count * 2 * 4;
+  // The count-only call and the filling call of one plan see the same input: remember the
+  // last choice per thread instead of searching twice.
+  struct Memo { uint64_t key = 0; int64_t chunk = 0; };
+  thread_local Memo memo;
+  uint64_t key = 1469598103934665603ull;
+  auto mix = [&key](uint64_t v) { key = (key ^ v) * 1099511628211ull; };
+  for (const Block& b : blocks) { mix((uint64_t)b.n_rows << 32 | (uint32_t)b.lo); mix((uint32_t)b.hi); }
+  mix(q_heads); mix(kv_heads); mix(head_dim); mix((uint32_t)window); mix(sm_count);
+  if (chunk == 0 && memo.key == key && memo.chunk > 0) {
+    chunk = memo.chunk;
+  } else if (chunk == 0) {
+    const int64_t slots_resident = (int64_t)sm_count * 2;
+    const int64_t want = slots_resident * 4;
     chunk = round_up(std::max<int64_t>(256, (total_span * kv_heads + want - 1) / want), 64);
+    int64_t longest = 0;
+    for (const Block& b : blocks) longest = std::max<int64_t>(longest, b.hi - b.lo);
+    if ((int64_t)blocks.size() * kv_heads < 16 * slots_resident) {
+      constexpr double kCtaOverheadTokens = 150.0;    // ~3.5 us of prologue + merge at 23 ns/token
+      constexpr double kCombineLaunchTokens = 130.0;  // ~3 us
+      auto estimate = [&](int64_t limit) {
+        std::vector<int32_t> pieces;
+        double combine_bytes = 0.0;
+        for (const Block& b : blocks) {
+          int64_t splits, per;
+          cut(b.hi - b.lo, limit, splits, per);
+          for (int64_t i = 0; i < splits; ++i)
+            pieces.push_back((int32_t)(std::min<int64_t>(b.hi, b.lo + (i + 1) * per) - (b.lo + i * per)));
+          if (splits > 1) combine_bytes += 2.0 * splits * b.n_rows * q_heads * (head_dim + 2) * 4;
+        }
+        std::sort(pieces.begin(), pieces.end(), std::greater<int32_t>());
+        std::vector<double> heap((size_t)slots_resident, 0.0);       // min-heap of slot finish times
+        auto later = std::greater<double>();
+        double makespan = 0.0;
+        for (int32_t len : pieces)
+          for (int h = 0; h < kv_heads; ++h) {
+            std::pop_heap(heap.begin(), heap.end(), later);
+            heap.back() += len + kCtaOverheadTokens;
+            makespan = std::max(makespan, heap.back());
+            std::push_heap(heap.begin(), heap.end(), later);
+          }
+        const double token_bytes = 2.0 * head_dim * 2;
+        return makespan + combine_bytes / token_bytes / slots_resident + (combine_bytes > 0 ? kCombineLaunchTokens : 0.0);
+      };
+      double best = estimate(chunk);
+      for (int k : {1, 2, 3, 4, 6, 8, 12, 16}) {
+        const int64_t candidate = round_up((longest + k - 1) / k, 64);
+        if (candidate < 256) break;
+        // finer cuts than ~12 CTAs per resident slot only add overhead: stop searching there
+        int64_t ctas = 0;
+        for (const Block& b : blocks) {
+          int64_t splits, per;
+          cut(b.hi - b.lo, candidate, splits, per);
+          ctas += splits * kv_heads;
+        }
+        if (ctas > 12 * slots_resident) break;
+        const double cost = estimate(candidate);
+        if (cost < best * 0.995) {
+          best = cost;
+          chunk = candidate;
+        }
+      }
+    }
+    memo.key = key;
+    memo.chunk = chunk;
   }
   chunk = std::max<int64_t>(chunk, 16);
 
@@ -160,12 +236,8 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
   int64_t entries = 0;
   for (const Block& b : blocks) {
     const int64_t span = b.hi - b.lo;
-    int64_t splits = 1, per = span;
-    if (span > chunk + chunk / 4) {
-      splits = (span + chunk - 1) / chunk;
-      per = round_up((span + splits - 1) / splits, 64);
-      splits = (span + per - 1) / per;
-    }
+    int64_t splits, per;
+    cut(span, chunk, splits, per);
     int64_t base = -1;
     if (splits > 1) {
       base = entries;
