@@ -271,3 +271,50 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
     std::copy(merges[i].begin(), merges[i].end(), combine_out + i * GK_COMBINE_WORDS);
   return GK_OK;
 }
+
+extern "C" int gk_prefill_plan_build(const int32_t* seq, int64_t n_seq, int q_heads, int kv_heads, int window,
+                                     int min_rows, int32_t* work_out, int64_t work_cap, int64_t* n_work_out,
+                                     int32_t* rest_seq_out, int64_t* n_rest_out) {
+  if (!seq || n_seq <= 0 || !n_work_out || !n_rest_out || min_rows < 0 || (window != -1 && window <= 0))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS)
+    return GK_ERR_UNSUPPORTED;
+  const int group = q_heads / kv_heads;
+  const int tile_rows = GK_PREFILL_TILE_ROWS / group;
+  if (min_rows == 0) min_rows = std::max(2, (32 + group - 1) / group);
+  struct Item { int32_t w[GK_WORK_WORDS]; };
+  std::vector<Item> items;
+  int64_t n_rest = 0;
+  for (int64_t s = 0; s < n_seq; ++s) {
+    const int32_t* r = seq + s * 4;
+    if (r[1] <= 0 || r[2] < 0 || r[0] < 0 || r[3] < 0) return GK_ERR_INVALID_ARGUMENT;
+    if (r[1] < min_rows) {
+      if (rest_seq_out) std::copy(r, r + 4, rest_seq_out + n_rest * 4);
+      ++n_rest;
+      continue;
+    }
+    for (int32_t done = 0; done < r[1]; done += tile_rows) {
+      const int32_t n = std::min<int32_t>(tile_rows, r[1] - done);
+      const int64_t first_pos = (int64_t)r[2] + done;
+      if (first_pos + n > INT32_MAX) return GK_ERR_UNSUPPORTED;
+      Item it{};
+      it.w[0] = r[0] + done;
+      it.w[1] = n;
+      it.w[2] = (int32_t)first_pos;
+      it.w[3] = r[3];
+      it.w[4] = window > 0 ? (int32_t)std::max<int64_t>(0, first_pos - window + 1) : 0;
+      it.w[5] = (int32_t)(first_pos + n);
+      it.w[6] = -1;
+      it.w[7] = 1;
+      items.push_back(it);
+    }
+  }
+  *n_work_out = (int64_t)items.size();
+  *n_rest_out = n_rest;
+  if (!work_out) return GK_OK;
+  if (work_cap < (int64_t)items.size()) return GK_ERR_CAPACITY;
+  std::stable_sort(items.begin(), items.end(),
+                   [](const Item& a, const Item& b) { return a.w[5] - a.w[4] > b.w[5] - b.w[4]; });
+  for (size_t i = 0; i < items.size(); ++i) std::copy(items[i].w, items[i].w + GK_WORK_WORDS, work_out + i * GK_WORK_WORDS);
+  return GK_OK;
+}

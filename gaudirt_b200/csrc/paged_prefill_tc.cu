@@ -1,0 +1,447 @@
+// Chunked-prefill paged attention on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// A work record here is a query tile of one sequence: up to 128/G consecutive rows whose G query
+// heads of one KV head are packed into the 128 rows of a UMMA tile, against the KV range
+// [kv_begin, kv_end) of the pool (prefix + the rows themselves, causal inside the chunk).
+// Q.K^T (128 x 128 x d) and P.V (128 x d x 128) are real dense contractions, so they run as
+// tcgen05.mma.kind::f16 with fp32 accumulators in tensor memory:
+//
+//   warps 0-3  softmax: one thread per packed row (= TMEM lane); reads S with tcgen05.ld, keeps
+//              the online (m, l), rescales O in TMEM when the maximum moves, writes P (bf16,
+//              the reference's rounding point) to shared memory, and finally normalises O
+//   warps 4-5  loaders: K and V rows of a 128-token tile -> shared memory with 16-byte cp.async,
+//              slots resolved from the table (any page size), two-stage ring
+//   warp 6     one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_j V_j, signalling
+//              completion through tcgen05.commit -> mbarrier
+//
+// Shared-memory operand tiles are [128 rows x 128 bf16] as two panels of [128 x 64] with the
+// 128-byte swizzle (16-byte chunk c of row r at chunk c ^ (r & 7)); the same bytes serve K as a
+// K-major operand and V as an MN-major operand.  S is double-buffered in TMEM so that Q K_{j+1}^T
+// runs under softmax_j.  Every mbarrier wait is bounded: on expiry the CTA raises
+// GK_DEV_WAIT_EXPIRED, drains its copies, frees its TMEM and returns.
+#include "gk_common.cuh"
+
+#include <math_constants.h>
+
+namespace gk {
+namespace {
+
+constexpr int kTile = 128;             // packed query rows per CTA, KV tokens per tile, head_dim
+constexpr int kPanelBytes = kTile * 128;
+constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
+constexpr int kSoftmaxThreads = 128, kLoaderThreads = 64, kThreads = 224;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kSpinLimit = 1 << 22;
+
+struct PrefillParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* pool_k;
+  const __nv_bfloat16* pool_v;
+  const int32_t* table;
+  const int32_t* table_rows;
+  const int32_t* work;
+  __nv_bfloat16* out;
+  int32_t* status;
+  int64_t q_stride, out_stride, slots, table_stride, entry_stride;
+  float scale, softcap;
+  int window, page_shift, q_heads, kv_heads, group;
+};
+
+struct Shared {
+  uint64_t kv_full[2], kv_empty[2], s_full[2], p_full, pv_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  return (c >> 3) * kPanelBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+
+// SWIZZLE_128B shared-memory matrix descriptor (version 1).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((saddr >> 4) & 0x3fff) | (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16 |
+         (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32 | (uint64_t)1 << 46 | (uint64_t)2 << 61;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait; returns false (and raises the CTA's abort flag) when it gives up.
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, Shared* sh) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
+                 : "=r"(ok)
+                 : "r"(addr), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+    if ((i & 1023) == 1023 && *reinterpret_cast<volatile int*>(&sh->abort)) return false;
+  }
+  atomicExch(&sh->abort, 1);
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 128.
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);   // A, B K-major
+constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
+
+__global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // swizzle atoms need 1 KiB alignment
+  uint8_t* s_q = tiles;
+  uint8_t* s_p = tiles + kTileBytes;
+  uint8_t* s_kv = tiles + 2 * kTileBytes;              // stage s: K at s*64 KiB, V right after it
+  Shared* sh = reinterpret_cast<Shared*>(tiles + 6 * kTileBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
+  const int4 w0 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item);
+  const int4 w1 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item + 1);
+  const int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, table_row = w0.w;
+  const int kv_begin = w1.x, kv_end = w1.y;
+  const int G = p.group;
+  const int mv = n_rows * G;                            // packed rows in use (<= 128)
+  const int n_tiles = (kv_end - kv_begin + kTile - 1) / kTile;
+
+  if (tid == 0) {
+    bar_init(&sh->kv_full[0], kLoaderThreads);
+    bar_init(&sh->kv_full[1], kLoaderThreads);
+    bar_init(&sh->kv_empty[0], 1);
+    bar_init(&sh->kv_empty[1], 1);
+    bar_init(&sh->s_full[0], 1);
+    bar_init(&sh->s_full[1], 1);
+    bar_init(&sh->p_full, kSoftmaxThreads);
+    bar_init(&sh->pv_done, 1);
+    sh->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  // Q tile: packed row pr = (row pr / G, query head pr % G) of this KV head; unused rows are zero.
+  for (int i = tid; i < kTile * 16; i += kThreads) {
+    const int pr = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (pr < mv) {
+      const int r = pr / G, g = pr - r * G;
+      const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * kTile + c * 8;
+      if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        v = __ldg(reinterpret_cast<const uint4*>(src));
+      } else {
+        const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
+        unsigned short e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = __ldg(s16 + k);
+        v = *reinterpret_cast<const uint4*>(e);
+      }
+    }
+    *reinterpret_cast<uint4*>(s_q + tile_off(pr, c)) = v;
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tmem_o = tmem + 256;
+
+  if (warp < 4) {
+    // ================================ softmax ============================================
+    const int pr = tid;                                          // packed row == TMEM lane
+    const int lim = pr < mv ? first_pos + pr / G : 0x7fffffff;   // last visible key of this row
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const bool capped = p.softcap > 0.f;
+    const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
+    const float cap_in = capped ? p.scale / p.softcap : 0.f;
+    float m = -CUDART_INF_F, l = 0.f;
+    bool alive = true;
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int st = j & 1;
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], (j >> 1) & 1, sh));
+      if (!alive) break;
+      tc_fence_after();
+      const uint32_t s_addr = tmem + st * kTile + lane_base;
+      const int tok0 = kv_begin + j * kTile;
+      const bool ragged = tok0 + kTile > kv_end || tok0 + kTile > first_pos + 1 ||
+                          (p.window > 0 && tok0 <= first_pos + n_rows - 1 - p.window);
+      auto score = [&](uint32_t raw, int tok) -> float {
+        float s = __uint_as_float(raw);
+        if (capped) s = p.softcap * tanhf(s * cap_in);
+        s *= to_log2;
+        if (ragged) {
+          const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
+          if (!seen) s = -CUDART_INF_F;
+        }
+        return s;
+      };
+      // pass 1: row maximum of this tile
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + cb * 32, r);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, score(r[e], tok0 + cb * 32 + e));
+      }
+      const float m_new = fmaxf(m, mx);
+      const float mu = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float alpha = fast_exp2(m - mu);
+      m = m_new;
+      // O may only be touched (and P overwritten) once the previous P.V has completed.
+      if (j > 0) {
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done, (j - 1) & 1, sh));
+        if (!alive) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int cb = 0; cb < 4; ++cb) {
+            uint32_t r[32];
+            tmem_ld32(tmem_o + lane_base + cb * 32, r);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st32(tmem_o + lane_base + cb * 32, r);
+          }
+        }
+      }
+      // pass 2: probabilities, rounded to bf16 for the second product; l from the fp32 values
+      float sum = 0.f;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + cb * 32, r);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = c * 8 + e * 2;
+            const float a = fast_exp2(score(r[col], tok0 + cb * 32 + col) - mu);
+            const float b = fast_exp2(score(r[col + 1], tok0 + cb * 32 + col + 1) - mu);
+            sum += a + b;
+            packed[e] = pack_bf16(a, b);
+          }
+          *reinterpret_cast<uint4*>(s_p + tile_off(pr, cb * 4 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+      l = l * alpha + sum;
+      fence_async_smem();
+      tc_fence_before();
+      bar_arrive(&sh->p_full);
+    }
+    // epilogue: O / l -> bf16 rows of the output
+    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done, (n_tiles - 1) & 1, sh));
+    if (alive) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int r_q = pr / G, g = pr - r_q * G;
+      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(tmem_o + lane_base + cb * 32, r);
+        if (pr < mv) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[c * 8 + 0]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + cb * 32 + c * 8) = v;
+          }
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ================================ K/V loaders =========================================
+    const int lt = tid - kSoftmaxThreads;                        // 0..63
+    const int lwarp = lt >> 5;
+    const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * kTile;
+    const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * kTile;
+    const int32_t* trow = p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
+    const int page_mask = (1 << p.page_shift) - 1;
+    bool alive = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      // Tile j-1 must be announced before waiting for stage `st` to drain: the P.V that frees it
+      // is only issued after Q.K^T of tile j-1.
+      if (j >= 1) {
+        cp_async_wait<0>();
+        fence_async_smem();
+        bar_arrive(&sh->kv_full[(j - 1) & 1]);
+      }
+      if (j >= 2) {
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->kv_empty[st], ((j >> 1) - 1) & 1, sh));
+        if (!alive) break;
+      }
+      const uint32_t dst_k = smem_u32(s_kv) + st * 2 * kTileBytes, dst_v = dst_k + kTileBytes;
+      // each loader warp stages 64 rows, 32 at a time: lanes resolve one slot each, then the
+      // warp copies two 256-byte rows per instruction (16 lanes x 16 bytes each)
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int row0 = lwarp * 64 + half * 32;
+        const int tok = kv_begin + j * kTile + row0 + lane;
+        int slot = -1;
+        if (tok < kv_end) {
+          slot = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
+          if ((unsigned)slot >= (unsigned)p.slots) {
+            if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
+            slot = -1;
+          }
+        }
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int rr = 2 * i + (lane >> 4), c = lane & 15;
+          const int s = __shfl_sync(0xffffffffu, slot, rr);
+          const int64_t src = (int64_t)(s < 0 ? 0 : s) * kTile + c * 8;
+          const int bytes = s < 0 ? 0 : 16;
+          const uint32_t off = tile_off(row0 + rr, c);
+          cp_async_16(dst_k + off, kbase + src, bytes);
+          cp_async_16(dst_v + off, vbase + src, bytes);
+        }
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+    if (alive) {
+      fence_async_smem();
+      bar_arrive(&sh->kv_full[(n_tiles - 1) & 1]);
+    }
+  } else if (lane == 0) {
+    // ================================ MMA issue ===========================================
+    const uint32_t q_addr = smem_u32(s_q), p_addr = smem_u32(s_p), kv_addr = smem_u32(s_kv);
+    bool alive = true;
+    auto issue_pv = [&](int i) {
+      if (!bar_wait(&sh->p_full, i & 1, sh)) return false;
+      tc_fence_after();
+      const uint32_t v_addr = kv_addr + (i & 1) * 2 * kTileBytes + kTileBytes;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step
+        const uint64_t da = umma_desc(p_addr + (k >> 2) * kPanelBytes + (k & 3) * 32, 16, 1024);
+        const uint64_t db = umma_desc(v_addr + k * 2048, kPanelBytes, 1024);
+        umma_bf16(tmem_o, da, db, kIdescPV, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&sh->kv_empty[i & 1]);
+      umma_commit(&sh->pv_done);
+      return true;
+    };
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int st = j & 1;
+      alive = bar_wait(&sh->kv_full[st], (j >> 1) & 1, sh);
+      if (!alive) break;
+      tc_fence_after();
+      const uint32_t k_addr = kv_addr + st * 2 * kTileBytes;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {                    // 16 elements of head_dim per step
+        const uint32_t koff = (k >> 2) * kPanelBytes + (k & 3) * 32;
+        umma_bf16(tmem + st * kTile, umma_desc(q_addr + koff, 16, 1024), umma_desc(k_addr + koff, 16, 1024), kIdescQK,
+                  k > 0 ? 1u : 0u);
+      }
+      umma_commit(&sh->s_full[st]);
+      if (j > 0) alive = issue_pv(j - 1);
+    }
+    if (alive) issue_pv(n_tiles - 1);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && sh->abort && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
+}
+
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
+
+}  // namespace
+}  // namespace gk
+
+extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                        int64_t slots, const int32_t* table, int64_t table_stride,
+                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
+                                        const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
+                                        float scale, float softcap, int window, int q_heads, int kv_heads, int head_dim,
+                                        int32_t* status, gk_stream_t stream) {
+  if (n_work == 0) return GK_OK;
+  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 ||
+      table_entry_stride <= 0 || page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
+      !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
+    return GK_ERR_INVALID_ARGUMENT;
+  if (head_dim != 128 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS ||
+      n_work * kv_heads > 0x7fffffffLL)
+    return GK_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(out) |
+        reinterpret_cast<uintptr_t>(work)) & 15) || (out_row_stride & 7) || (reinterpret_cast<uintptr_t>(q) & 1))
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::PrefillParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.pool_k = static_cast<const __nv_bfloat16*>(pool_k);
+  p.pool_v = static_cast<const __nv_bfloat16*>(pool_v);
+  p.table = table;
+  p.table_rows = table_rows;
+  p.work = work;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.q_stride = q_row_stride;
+  p.out_stride = out_row_stride;
+  p.slots = slots;
+  p.table_stride = table_stride;
+  p.entry_stride = table_entry_stride;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.window = window;
+  p.page_shift = __builtin_ctz((unsigned)page_tokens);
+  p.q_heads = q_heads;
+  p.kv_heads = kv_heads;
+  p.group = q_heads / kv_heads;
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return gk::check_launch();
+  if (device < 0 || device >= 64 || !configured[device]) {
+    if (cudaFuncSetAttribute(gk::paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gk::kSmemBytes) !=
+        cudaSuccess)
+      return gk::check_launch();
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  gk::paged_prefill_tc_kernel<<<(unsigned)(n_work * kv_heads), gk::kThreads, gk::kSmemBytes,
+                                reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return gk::check_launch();
+}

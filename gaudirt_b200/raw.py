@@ -81,3 +81,33 @@ def paged_attn(query, pool_layer, table, page_tokens, work, combine, entries, q_
         abi.check(st, "gk_paged_attn_combine_bf16")
     torch.cuda.current_stream().synchronize()
     return out
+
+
+def prefill_plan(seq, q_heads, kv_heads, window=-1, min_rows=0):
+    """Tensor-core work records for the multi-row sequences, and the sequences left for `plan`."""
+    seq = np.ascontiguousarray(seq, dtype=np.int32).reshape(-1, 4)
+    n_work, n_rest = C.c_int64(0), C.c_int64(0)
+    lib = abi.lib()
+    abi.check(lib.gk_prefill_plan_build(_ptr(seq), len(seq), q_heads, kv_heads, window, min_rows, None, 0,
+                                        C.byref(n_work), None, C.byref(n_rest)), "gk_prefill_plan_build(count)")
+    work = np.zeros((max(n_work.value, 1), 8), dtype=np.int32)
+    rest = np.zeros((max(n_rest.value, 1), 4), dtype=np.int32)
+    abi.check(lib.gk_prefill_plan_build(_ptr(seq), len(seq), q_heads, kv_heads, window, min_rows, _ptr(work), len(work),
+                                        C.byref(n_work), _ptr(rest), C.byref(n_rest)), "gk_prefill_plan_build")
+    return work[: n_work.value].copy(), rest[: n_rest.value].copy()
+
+
+def paged_prefill_tc(query, pool_layer, table, page_tokens, work, out, q_heads, scale, softcap=0.0, window=-1,
+                     status=None, entry_stride=1, table_rows=None):
+    """Launch the tensor-core prefill kernel for prepared work records, writing rows of `out`."""
+    _, kv_heads, slots, d = pool_layer.shape
+    work_d = torch.from_numpy(np.ascontiguousarray(work)).to(query.device)
+    st = abi.lib().gk_paged_prefill_tc_bf16(
+        query.data_ptr(), query.stride(0), pool_layer[0].data_ptr(), pool_layer[1].data_ptr(), slots,
+        table.data_ptr(), table.stride(0), entry_stride, page_tokens,
+        table_rows.data_ptr() if table_rows is not None else None, work_d.data_ptr(), len(work), out.data_ptr(),
+        out.stride(0), scale, softcap, window, q_heads, kv_heads, d,
+        status.data_ptr() if status is not None else None, stream_ptr())
+    abi.check(st, "gk_paged_prefill_tc_bf16")
+    torch.cuda.current_stream().synchronize()
+    return out
