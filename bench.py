@@ -9,6 +9,9 @@ KV block 128 tokens, pool of batch*32 blocks + 10 % spare, shuffled block tables
 
     --config 3   skewed lengths (lognormal, median 2048, sigma 1, clipped to [16, 32768]),
                  batch 128, 64 query / 8 KV heads, length-aware split-KV schedule
+    --config 4   chunked prefill on the tensor-core (tcgen05) kernel: 16 sequences, each a new
+                 512-token chunk on a paged prefix of uniform [0, 8192] tokens, 32 query / 8 KV heads,
+                 N(0, 0.5) data, causal inside the chunk, KV store of all new tokens first
     --config 5   fused decode layer step: fused_add_rms_norm (hidden 8192, weight_offset 1) ->
                  rotary (theta 500000) -> KV store -> paged GQA decode, batch 64,
                  contexts uniform [1024, 16384], 64 query / 8 KV heads
@@ -62,12 +65,26 @@ class Workload:
     front: bool = False          # fused_add_rms_norm + rotary in front of the store
     hidden: int = 8192
     theta: float = 500000.0
+    chunk: int = 1               # new rows per sequence (1 = decode)
+    std: float = 1.0
+
+    @property
+    def rows(self):
+        return self.batch * self.chunk
+
+    @property
+    def visible_total(self):
+        """Sum over all rows of the keys the row attends to."""
+        prefix = self.ctx - self.chunk
+        return int((prefix * self.chunk).sum()) + self.batch * self.chunk * (self.chunk + 1) // 2
 
     @property
     def describe(self):
         lo, hi = int(self.ctx.min()), int(self.ctx.max())
         span = f"ctx {lo}" if lo == hi else f"ctx {lo}..{hi} (mean {float(self.ctx.double().mean()):.0f})"
         steps = "fused_add_rms_norm + rotary + KV store + attention" if self.front else "KV store + attention"
+        if self.chunk > 1:
+            span = f"{self.chunk} new rows each on " + span.replace("ctx", "contexts (after the store)")
         return (f"{self.name}: batch {self.batch}, {span}, {self.q_heads}q/{self.kv_heads}kv heads, head_dim {HEAD_DIM}, "
                 f"block {BLOCK}, {self.layers} layers (independent pools), {steps} per layer")
 
@@ -82,12 +99,18 @@ def make_workload(args) -> Workload:
         batch = args.batch or 128
         return Workload("skewed-length paged decode with split-KV (70B geometry)", batch, 64, 8, args.layers or 8,
                         cases.lognormal_contexts(batch, 20261103))
+    if args.config == 4:
+        batch = args.batch or 16
+        gen = torch.Generator().manual_seed(20261104)
+        prefix = torch.randint(0, 8193, (batch,), generator=gen)
+        return Workload("chunked prefill onto a paged prefix (tensor-core path)", batch, 32, 8, args.layers or 8,
+                        prefix + 512, chunk=512, std=0.5)
     if args.config == 5:
         batch = args.batch or 64
         gen = torch.Generator().manual_seed(20261105)
         return Workload("fused decode layer step (70B geometry)", batch, 64, 8, args.layers or 16,
                         torch.randint(1024, 16385, (batch,), generator=gen), front=True)
-    raise SystemExit("--config must be 2, 3 or 5")
+    raise SystemExit("--config must be 2, 3, 4 or 5")
 
 
 def parse():
@@ -96,7 +119,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", type=int, default=2, help="2 (headline), 3 or 5")
+    ap.add_argument("--config", type=int, default=2, help="2 (headline), 3, 4 or 5")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"], help="output gather when N > 1")
     ap.add_argument("--layers", type=int, default=0, help="experiments only; 0 = the workload's own count")
     ap.add_argument("--batch", type=int, default=0, help="experiments only")
@@ -112,6 +135,14 @@ def peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -170,10 +201,18 @@ class CpuSample:
         n_seqs = min(n_seqs, w.batch)
         pick = torch.linspace(0, w.batch - 1, n_seqs).round().long().unique()
         self.w, self.ctx = w, w.ctx[pick]
-        blocks = int(((self.ctx + BLOCK - 1) // BLOCK).sum()) + 4
-        self.case = cases.decode_case(len(pick), w.q_heads, w.kv_heads, HEAD_DIM, BLOCK, blocks, self.ctx,
-                                      seed=20261100 + len(pick))
-        self.tokens = int(self.ctx.sum())
+        if w.chunk > 1:
+            # chunked prefill: whole chunks are stored, every `stride`-th row of them attends
+            self.case = cases.chunk_case(self.ctx - w.chunk, w.chunk, w.q_heads, w.kv_heads, HEAD_DIM, BLOCK,
+                                         seed=20261100 + len(pick), std=w.std)
+            stride = max(1, w.chunk // 16)
+            self.rows = torch.arange(0, len(pick) * w.chunk, stride)
+        else:
+            blocks = int(((self.ctx + BLOCK - 1) // BLOCK).sum()) + 4
+            self.case = cases.decode_case(len(pick), w.q_heads, w.kv_heads, HEAD_DIM, BLOCK, blocks, self.ctx,
+                                          seed=20261100 + len(pick))
+            self.rows = torch.arange(len(pick))
+        self.tokens = int((self.case.positions[self.rows] + 1).sum())       # keys visited by the sampled rows
         if w.front:
             gen = torch.Generator().manual_seed(7)
             self.x = torch.randn(len(pick), w.hidden, generator=gen).to(torch.bfloat16)
@@ -182,7 +221,7 @@ class CpuSample:
             self.cache = oracle.rotary_cache(int(w.ctx.max()) + 1, HEAD_DIM, w.theta)
 
     def run(self):
-        """Seconds per context token of one layer (store + attend, and the layer front if any)."""
+        """Seconds per visited key of one layer (store + attend, and the layer front if any)."""
         import oracle
         c, w = self.case, self.w
         pool = c.pool.clone()
@@ -194,20 +233,27 @@ class CpuSample:
             k = oracle.rotary_embedding(c.k, self.cache, c.positions, HEAD_DIM, HEAD_DIM, True).to(torch.bfloat16)
         oracle.kv_store_head_major(pool, k, c.v, c.locations)
         kp, vp = oracle.pool_views(pool)
-        oracle.direct_bf16_pv(q, kp, vp, c.requests, c.positions, c.mapping, w.q_heads, w.kv_heads, HEAD_DIM, c.scale)
+        args = (q[self.rows], kp, vp, c.requests[self.rows], c.positions[self.rows], c.mapping, w.q_heads, w.kv_heads,
+                HEAD_DIM, c.scale)
+        if w.chunk > 1:
+            oracle.tiled_bf16_pv(*args, kv_tile=oracle.KV_TILE)
+        else:
+            oracle.direct_bf16_pv(*args)
         return (time.perf_counter() - t0) / self.tokens
 
 
 def cpu_sample_size(w: Workload, requested: int) -> int:
     if requested:
         return requested
-    # ~5.5 us per context token and layer on 8 cores: aim at a few seconds per pass
+    # ~5.5 us per visited key and layer on 8 cores: aim at a few seconds per pass
+    if w.chunk > 1:
+        return 2
     per_seq = float(w.ctx.double().mean()) * 6e-6
     return max(2, min(w.batch, int(3.0 / per_seq)))
 
 
-def cpu_tokens_per_s(w: Workload, sec_per_token: float) -> float:
-    return w.batch / (sec_per_token * float(w.ctx.sum()) * w.layers)
+def cpu_tokens_per_s(w: Workload, sec_per_key: float) -> float:
+    return w.rows / (sec_per_key * float(w.visible_total) * w.layers)
 
 
 def run_reference(args):
@@ -225,10 +271,10 @@ def run_reference(args):
     per = [sample.run() for _ in range(args.steps)]
     wall = time.perf_counter() - t0
     value = cpu_tokens_per_s(w, statistics.mean(per))
-    text = (f"{len(sample.ctx)} of {w.batch} sequences x 1 of {w.layers} layers per step ({sample.tokens} context tokens), "
-            "scaled linearly by context tokens")
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.batch / value * 1e3,
+    text = (f"{len(sample.rows)} rows of {len(sample.ctx)} of {w.batch} sequences x 1 of {w.layers} layers per step "
+            f"({sample.tokens} visited keys), scaled linearly by visited keys")
+    line = {"impl": "reference", "metric": METRIC if w.chunk == 1 else "paged_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.rows / value * 1e3,
             "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(w, 1, "-"),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": text},
@@ -257,7 +303,7 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
     w = make_workload(args)
     shard = tp.HeadShard(rank, world, w.q_heads, w.kv_heads)
-    B, d, L = w.batch, HEAD_DIM, w.layers
+    B, d, L, R = w.batch, HEAD_DIM, w.layers, w.rows
     hq, hkv = shard.local_q_heads, shard.local_kv_heads
 
     # ---- metadata (replicated on every rank): shuffled block tables, new token at ctx-1 -------
@@ -273,9 +319,9 @@ def run_b200(args):
         cursor += int(need[b])
     pos = torch.arange(int(need.max()) * BLOCK)
     mapping = (tables.long()[:, pos // BLOCK] * BLOCK + pos % BLOCK).to(torch.int32).contiguous()
-    requests = torch.arange(B, dtype=torch.int32)
-    positions = (w.ctx - 1).to(torch.int32)
-    locations = mapping[torch.arange(B), positions.long()].contiguous()
+    requests = torch.arange(B, dtype=torch.int32).repeat_interleave(w.chunk)
+    positions = ((w.ctx - w.chunk)[:, None] + torch.arange(w.chunk)[None, :]).reshape(-1).to(torch.int32)
+    locations = mapping[requests.long(), positions.long()].contiguous()
     scale = 1.0 / math.sqrt(d)
 
     # ---- pools: layer 0 is drawn N(0,1); the others are that data rotated by a layer-specific
@@ -283,7 +329,7 @@ def run_b200(args):
     pool = rt._C._allocate_paged_kv(L, slots, hkv, d)
     flat0 = pool[0].view(-1)
     for off in range(0, flat0.numel(), 1 << 28):
-        flat0[off:off + (1 << 28)].normal_()
+        flat0[off:off + (1 << 28)].normal_(0.0, w.std)
     for l in range(1, L):
         shift = (l * 7919 * d) % flat0.numel()
         dst = pool[l].view(-1)
@@ -292,22 +338,22 @@ def run_b200(args):
     views = [(pool[l, 0].transpose(0, 1), pool[l, 1].transpose(0, 1)) for l in range(L)]
 
     hgen = torch.Generator().manual_seed(20261100 + 10 * args.config + rank)
-    host_q = torch.randn(L, B, hq * d, generator=hgen).to(torch.bfloat16).pin_memory()
-    host_k = torch.randn(L, B, hkv * d, generator=hgen).to(torch.bfloat16).pin_memory()
-    host_v = torch.randn(L, B, hkv * d, generator=hgen).to(torch.bfloat16).pin_memory()
-    host_out = torch.empty(L, B, hq * d * world, dtype=torch.bfloat16).pin_memory()
+    host_q = (torch.randn(L, R, hq * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
+    host_k = (torch.randn(L, R, hkv * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
+    host_v = (torch.randn(L, R, hkv * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
+    host_out = torch.empty(L, R, hq * d * world, dtype=torch.bfloat16).pin_memory()
     host_in = [host_q, host_k, host_v]
     gamma = cache = None
     if w.front:
         fgen = torch.Generator().manual_seed(20261199)      # the hidden state is replicated on every rank
-        host_in += [torch.randn(L, B, w.hidden, generator=fgen).to(torch.bfloat16).pin_memory() for _ in range(2)]
+        host_in += [torch.randn(L, R, w.hidden, generator=fgen).to(torch.bfloat16).pin_memory() for _ in range(2)]
         gamma = (0.02 * torch.randn(w.hidden, generator=fgen)).to(torch.bfloat16).to(dev)
         inv = w.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
         ang = torch.arange(mapping.size(1), dtype=torch.float64)[:, None] * inv[None, :]   # covers the whole table
         cache = torch.cat((ang.cos(), ang.sin()), dim=-1).float().to(torch.bfloat16).to(dev)
     resident = [h.to(dev) for h in host_in]
 
-    gather = tp.OutputGather(B, hq * d, dev, mode=args.gather) if world > 1 else None
+    gather = tp.OutputGather(R, hq * d, dev, mode=args.gather) if world > 1 else None
     lib = abi.lib()
 
     def layer(l, md, q, k, v, x=None, res=None):
@@ -393,21 +439,36 @@ def run_b200(args):
     # ---- dominant kernel alone: CUDA events around every attention launch of one step ---------
     seq = torch.tensor(md.sequences(), dtype=torch.int32).reshape(-1, 4).numpy()
     page = md.page_tokens()
-    work, combine, entries = H.plan(seq, hq, hkv, d, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
-    work_d = torch.from_numpy(work).to(dev)
     table = md.request_mapping()
     dq = resident[0]
-    out = torch.empty(B, hq * d, dtype=torch.bfloat16, device=dev)
-    pml, po = torch.empty(max(entries, 1) * 2, device=dev), torch.empty(max(entries, 1) * d, device=dev)
+    out = torch.empty(R, hq * d, dtype=torch.bfloat16, device=dev)
     s = H.stream_ptr()
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
-    for _ in range(2):
-        for l in range(L):
-            events[l][0].record()
+    if w.chunk > 1:
+        work, rest = H.prefill_plan(seq, hq, hkv)
+        assert len(rest) == 0
+        combine, entries = [], 0
+        work_d = torch.from_numpy(work).to(dev)
+
+        def launch(l):
+            abi.check(lib.gk_paged_prefill_tc_bf16(dq[l].data_ptr(), dq[l].stride(0), pool[l, 0].data_ptr(), pool[l, 1].data_ptr(),
+                                                   slots, table.data_ptr(), table.stride(0), page, page, None, work_d.data_ptr(),
+                                                   len(work), out.data_ptr(), out.stride(0), scale, 0.0, -1, hq, hkv, d,
+                                                   None, s), "gk_paged_prefill_tc_bf16")
+    else:
+        work, combine, entries = H.plan(seq, hq, hkv, d, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
+        work_d = torch.from_numpy(work).to(dev)
+        pml, po = torch.empty(max(entries, 1) * 2, device=dev), torch.empty(max(entries, 1) * d, device=dev)
+
+        def launch(l):
             abi.check(lib.gk_paged_attn_bf16(dq[l].data_ptr(), dq[l].stride(0), pool[l, 0].data_ptr(), pool[l, 1].data_ptr(),
                                              slots, table.data_ptr(), table.stride(0), page, page, None, work_d.data_ptr(),
                                              len(work), out.data_ptr(), out.stride(0), pml.data_ptr(), po.data_ptr(), scale,
                                              0.0, -1, hq, hkv, d, None, s), "gk_paged_attn_bf16")
+    for _ in range(2):
+        for l in range(L):
+            events[l][0].record()
+            launch(l)
             events[l][1].record()
         torch.cuda.synchronize()
     kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
@@ -417,30 +478,44 @@ def run_b200(args):
             dist.destroy_process_group()
         return
     ms_per_step = total_ms / args.steps
-    tokens_s = B / ms_per_step * 1e3
-    e2e_tokens_s = B / (e2e_ms / args.steps) * 1e3
+    tokens_s = R / ms_per_step * 1e3
+    e2e_tokens_s = R / (e2e_ms / args.steps) * 1e3
     kv_bytes = int(w.ctx.sum()) * hkv * d * 2 * 2
-    pages = int(((w.ctx + page - 1) // page).sum())
-    algo_bytes = kv_bytes + 2 * B * hq * d * 2 + pages * 4 + len(work) * 32 + entries * (d + 2) * 4
     peak, which = peaks()
-    achieved = algo_bytes / kernel_ms / 1e6
-    mine_per_layer = 2 + (1 if len(combine) else 0) + (1 if gather is not None and gather.mode == "push" else 0) + \
-        (2 if w.front else 0)
-    h2d = sum(h[0].numel() * 2 for h in host_in) * L + (3 * B + mapping.numel() + 1) * 4 + work.nbytes + combine.nbytes
+    if w.chunk > 1:
+        flops = 4.0 * d * hq * w.visible_total
+        achieved = flops / kernel_ms / 1e9
+        tpeak, twhich = tensor_peak()
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
+                    "traffic": None, "peak_source": f"{twhich} cuBLAS bf16 burst throughput",
+                    "kernel": "paged_prefill_tc_kernel (tcgen05)", "kernel_ms": kernel_ms,
+                    "algorithmic_flops_per_launch": flops, "work_items": len(work),
+                    "frac_of_2250_nominal": achieved / 2250.0}
+        mine_per_layer = 2
+    else:
+        pages = int(((w.ctx + page - 1) // page).sum())
+        algo_bytes = kv_bytes + 2 * B * hq * d * 2 + pages * 4 + len(work) * 32 + entries * (d + 2) * 4
+        achieved = algo_bytes / kernel_ms / 1e6
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": TRAFFIC_PER_KV_BYTE * kv_bytes, "traffic_source": TRAFFIC_SOURCE,
+                    "peak_source": f"{which} copy bandwidth", "kernel": "paged_attn_kernel<128,4,3>",
+                    "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": algo_bytes,
+                    "work_items": len(work), "split_blocks": len(combine),
+                    "frac_of_8TBs_nominal": achieved / 8000.0}
+        mine_per_layer = 2 + (1 if len(combine) else 0) + (1 if gather is not None and gather.mode == "push" else 0) + \
+            (2 if w.front else 0)
+    h2d = sum(h[0].numel() * 2 for h in host_in) * L + (3 * R + mapping.numel() + 1) * 4 + work.nbytes + \
+        (combine.nbytes if len(combine) else 0)
     line = {
-        "metric": METRIC, "value": tokens_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if w.chunk == 1 else "paged_prefill_tokens_per_s", "value": tokens_s, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(w, world, args.gather),
         "kv_read_gbs_whole_step": kv_bytes * L * world / ms_per_step / 1e6,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": TRAFFIC_PER_KV_BYTE * kv_bytes, "traffic_source": TRAFFIC_SOURCE,
-                     "peak_source": f"{which} copy bandwidth", "kernel": "paged_attn_kernel<128,4,3>",
-                     "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": algo_bytes,
-                     "work_items": len(work), "split_blocks": len(combine),
-                     "frac_of_8TBs_nominal": achieved / 8000.0},
+        "roofline": roofline,
         "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(L * B * hq * world * d * 2)},
+                "d2h_bytes_per_step": int(L * R * hq * world * d * 2)},
         "gpu_launches": args.steps * L * mine_per_layer,
         "clocks": clocks.summary(),
     }
@@ -451,9 +526,10 @@ def run_b200(args):
         sample.run()
         sec = min(sample.run(), sample.run())
         line["cpu_baseline"] = {"value": cpu_tokens_per_s(w, sec), "unit": "tokens/s", "cores": cores, "kind": "port",
-                                "sample": f"{len(sample.ctx)} of {B} sequences x 1 of {L} layers ({sample.tokens} context "
-                                          "tokens; store + direct_bf16_pv), best of 2 after a warm-up, scaled linearly "
-                                          "by context tokens"}
+                                "sample": f"{len(sample.rows)} rows of {len(sample.ctx)} of {B} sequences x 1 of {L} layers "
+                                          f"({sample.tokens} visited keys; store + "
+                                          f"{'tiled_bf16_pv(512)' if w.chunk > 1 else 'direct_bf16_pv'}), best of 2 after a "
+                                          "warm-up, scaled linearly by visited keys"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

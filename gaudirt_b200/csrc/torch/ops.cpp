@@ -61,6 +61,7 @@ struct AttentionPlan {
   c10::DeviceIndex device = -1;
   int64_t rows = 0, slots = 0, query_heads = 0, kv_heads = 0, head_dim = 0, sliding_window = -1;
   int64_t n_work = 0, n_combine = 0, combine_offset = 0, table_stride = 0, entry_stride = 1;
+  int64_t n_prefill = 0, prefill_offset = 0;   // query tiles for the tensor-core prefill kernel
   int page_tokens = 1;
 };
 
@@ -278,19 +279,36 @@ class PagedMetadata : public torch::CustomClassHolder {
     c10::cuda::CUDAGuard guard(device);
     const int sm_count = at::cuda::getDeviceProperties(device.index())->multiProcessorCount;
     const int64_t n_seq = static_cast<int64_t>(sequences_.size() / 4);
-    int64_t n_work = 0, n_combine = 0, entries = 0;
     const int window = static_cast<int>(sliding_window);
-    check_status(gk_attention_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, (int)head_dim, window,
-                                         sm_count, split_tokens_, nullptr, 0, &n_work, nullptr, 0, &n_combine, &entries),
-                 "attention plan");
+    // Multi-row sequences go to the tensor-core prefill kernel (head_dim 128 only), the rest --
+    // decode rows and very short chunks -- to the split-KV decode kernel.
+    int64_t n_prefill = 0, n_rest = n_seq;
+    std::vector<int32_t> rest(sequences_);
+    const bool tensor_core = head_dim == 128 && prefill_min_rows_ >= 0;
+    if (tensor_core)
+      check_status(gk_prefill_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, window,
+                                         prefill_min_rows_, nullptr, 0, &n_prefill, rest.data(), &n_rest),
+                   "prefill plan");
+    int64_t n_work = 0, n_combine = 0, entries = 0;
+    if (n_rest > 0)
+      check_status(gk_attention_plan_build(rest.data(), n_rest, (int)query_heads, (int)kv_heads, (int)head_dim, window,
+                                           sm_count, split_tokens_, nullptr, 0, &n_work, nullptr, 0, &n_combine, &entries),
+                   "attention plan");
     const int64_t combine_offset = n_work * GK_WORK_WORDS;
-    const int64_t words = std::max<int64_t>(4, combine_offset + n_combine * GK_COMBINE_WORDS);
+    const int64_t prefill_offset = combine_offset + n_combine * GK_COMBINE_WORDS;
+    const int64_t words = std::max<int64_t>(4, prefill_offset + n_prefill * GK_WORK_WORDS);
     auto staging = at::empty({words}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
     int32_t* host = staging.data_ptr<int32_t>();
-    check_status(gk_attention_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, (int)head_dim, window,
-                                         sm_count, split_tokens_, host, n_work, &n_work, host + combine_offset,
-                                         n_combine, &n_combine, &entries),
-                 "attention plan");
+    if (n_rest > 0)
+      check_status(gk_attention_plan_build(rest.data(), n_rest, (int)query_heads, (int)kv_heads, (int)head_dim, window,
+                                           sm_count, split_tokens_, host, n_work, &n_work, host + combine_offset,
+                                           n_combine, &n_combine, &entries),
+                   "attention plan");
+    if (n_prefill > 0)
+      check_status(gk_prefill_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, window,
+                                         prefill_min_rows_, host + prefill_offset, n_prefill, &n_prefill, rest.data(),
+                                         &n_rest),
+                   "prefill plan");
     auto plan = std::make_unique<AttentionPlan>();
     plan->buffer = staging.to(device, /*non_blocking=*/true);
     const auto f32 = at::TensorOptions().dtype(at::kFloat).device(device);
@@ -312,6 +330,8 @@ class PagedMetadata : public torch::CustomClassHolder {
     plan->n_work = n_work;
     plan->n_combine = n_combine;
     plan->combine_offset = combine_offset;
+    plan->n_prefill = n_prefill;
+    plan->prefill_offset = prefill_offset;
     auto tensor = wrap_plan(std::move(plan));
     plans_.emplace_back(sliding_window, tensor);
     return tensor;
@@ -330,8 +350,15 @@ class PagedMetadata : public torch::CustomClassHolder {
     split_tokens_ = static_cast<int>(tokens);
   }
 
+  // Fewest rows of a sequence that are sent to the tensor-core prefill kernel (0 = the library's
+  // default, -1 = never).  Not part of the reference surface: a test and tuning hook.
+  void set_prefill_min_rows(int64_t rows) {
+    TORCH_CHECK(rows >= -1 && rows <= INT32_MAX, "GaudiRT attention: invalid prefill threshold");
+    prefill_min_rows_ = static_cast<int>(rows);
+  }
+
   int64_t rows_ = 0, slots_ = 0, request_count_ = 0, context_ = 0, vocabulary_ = 0, page_tokens_ = 1;
-  int split_tokens_ = 0;
+  int split_tokens_ = 0, prefill_min_rows_ = 0;
   at::Tensor locations_, requests_, positions_, mapping_, header_, batch_requests_, token_ids_, last_token_indices_;
   std::vector<int32_t> sequences_;   // {first_row, n_rows, first_position, table_row} per sequence
   std::vector<std::pair<int64_t, at::Tensor>> plans_;
@@ -427,6 +454,23 @@ at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const
                                                 words + plan.combine_offset, plan.n_combine, outs.data(), (int)outs.size(),
                                                 out_stride, (int)plan.query_heads, (int)head_dim, s),
                "split-KV combine");
+  if (plan.n_prefill > 0) {
+    // Query tiles of multi-row sequences: tcgen05 kernel, one destination.  With several gather
+    // destinations the rows are staged once and copied to each of them.
+    at::Tensor staged = pushed.empty() ? output : at::empty({plan.rows, query.size(1)}, query.options());
+    check_status(gk_paged_prefill_tc_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
+                                          plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride,
+                                          plan.page_tokens,
+                                          plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr,
+                                          words + plan.prefill_offset, plan.n_prefill, staged.data_ptr(), staged.stride(0),
+                                          scale_f, softcap_f, (int)sliding_window, (int)plan.query_heads,
+                                          (int)plan.kv_heads, (int)head_dim, status, s),
+                 "tensor-core prefill");
+    if (!pushed.empty()) {
+      TORCH_CHECK(plan.n_work == 0, "GaudiRT attention: mixed prefill and decode rows are not supported with gather destinations");
+      for (const auto& t : pushed) const_cast<at::Tensor&>(t).copy_(staged, /*non_blocking=*/true);
+    }
+  }
   return output;
 }
 
@@ -627,7 +671,8 @@ TORCH_LIBRARY(gaudirt, m) {
       .def("last_token_indices", &PagedMetadata::last_token_indices)
       .def("token_ids", &PagedMetadata::token_ids)
       .def("vocabulary", &PagedMetadata::vocabulary)
-      .def("_set_split_tokens", &PagedMetadata::set_split_tokens);
+      .def("_set_split_tokens", &PagedMetadata::set_split_tokens)
+      .def("_set_prefill_min_rows", &PagedMetadata::set_prefill_min_rows);
   m.def("paged_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, float scale, "
         "float softcap=0.0, int sliding_window=-1) -> Tensor");

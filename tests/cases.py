@@ -68,3 +68,47 @@ def lognormal_contexts(batch, seed, median=2048, sigma=1.0, lo=16, hi=32768):
     gen = torch.Generator().manual_seed(seed)
     z = torch.randn(batch, generator=gen, dtype=torch.float64)
     return torch.clamp(torch.round(torch.exp(math.log(median) + sigma * z)), lo, hi).to(torch.int64)
+
+
+@dataclass
+class ChunkCase:
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    slots: int
+    mapping: torch.Tensor        # [seqs, context] int32
+    requests: torch.Tensor       # [rows] int64
+    positions: torch.Tensor      # [rows] int64
+    locations: torch.Tensor      # [rows] int32
+    q: torch.Tensor
+    k: torch.Tensor
+    v: torch.Tensor
+    pool: torch.Tensor
+    scale: float
+
+
+def chunk_case(prefixes, chunk, q_heads, kv_heads, head_dim, block, seed, std=1.0) -> ChunkCase:
+    """Chunked prefill: every sequence appends `chunk` new rows to a prefix already in the pool."""
+    gen = torch.Generator().manual_seed(seed)
+    prefixes = torch.as_tensor(prefixes, dtype=torch.int64)
+    n = len(prefixes)
+    need = (prefixes + chunk + block - 1) // block
+    n_blocks = int(int(need.sum()) * 1.1) + 1
+    perm = torch.randperm(n_blocks, generator=gen).to(torch.int32)
+    tables = torch.zeros(n, int(need.max()), dtype=torch.int32)
+    cursor = 0
+    for b in range(n):
+        tables[b, : int(need[b])] = perm[cursor:cursor + int(need[b])]
+        cursor += int(need[b])
+    pos = torch.arange(int(need.max()) * block)
+    mapping = (tables.long()[:, pos // block] * block + pos % block).to(torch.int32).contiguous()
+    requests = torch.arange(n).repeat_interleave(chunk)
+    positions = (prefixes[:, None] + torch.arange(chunk)[None, :]).reshape(-1)
+    locations = mapping[requests, positions].contiguous()
+    rows = n * chunk
+    mk = lambda *shape: (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+    q, k, v = mk(rows, q_heads * head_dim), mk(rows, kv_heads * head_dim), mk(rows, kv_heads * head_dim)
+    pool = mk(2, kv_heads, n_blocks * block, head_dim)
+    scale = torch.tensor(1.0 / math.sqrt(head_dim), dtype=torch.float32).item()
+    return ChunkCase(q_heads, kv_heads, head_dim, n_blocks * block, mapping, requests, positions, locations, q, k, v,
+                     pool, scale)

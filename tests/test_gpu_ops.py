@@ -254,3 +254,33 @@ def test_sequential_decode_steps_keep_state(rt):
                                          heads, kv_heads, d, d ** -0.5)
         oracle.fp32_softmax_gate(out.cpu().double(), ref)
     assert torch.equal(bits(key_pool.cpu()), bits(kc)) and torch.equal(bits(value_pool.cpu()), bits(vc))
+
+
+def test_chunked_prefill_goes_to_the_tensor_core_kernel_and_matches_the_generic_path(rt):
+    """Mixed step: two prefill chunks on paged prefixes plus decode rows, head_dim 128.  The default
+    plan sends the chunks to the tcgen05 kernel; with the threshold disabled the same rows run on
+    the generic kernel.  Both satisfy the oracle gates."""
+    from tests import cases
+    c = cases.chunk_case([300, 0, 1500], 96, 16, 4, 128, 128, seed=31, std=0.5)
+    # turn the last sequence into a single decode row
+    keep = torch.cat([torch.arange(0, 192), torch.arange(192 + 95, 192 + 96)])
+    requests, positions, locations = c.requests[keep], c.positions[keep], c.locations[keep].contiguous()
+    q, k, v = c.q[keep], c.k[keep], c.v[keep]
+    # the dropped rows' positions must already be in the pool for the decode row: store them first
+    pool_ref = c.pool.clone()
+    oracle.kv_store_head_major(pool_ref, c.k, c.v, c.locations)
+    outs = []
+    for min_rows in (0, -1):
+        combined = rt._C._allocate_paged_kv(1, c.slots, 4, 128)
+        combined[0].copy_(pool_ref)
+        kp, vp = combined[0, 0].transpose(0, 1), combined[0, 1].transpose(0, 1)
+        md = rt.PagedMetadata(locations, requests, positions, c.mapping, c.slots)
+        assert md.sequences() == [0, 96, 300, 0, 96, 96, 0, 1, 192, 1, 1595, 2]
+        md._set_prefill_min_rows(min_rows)
+        out = torch.ops.gaudirt.paged_attn(q.to(DEV), k.to(DEV), v.to(DEV), kp, vp, md, 128, c.scale)
+        assert torch.equal(bits(combined[0].cpu()), bits(pool_ref))
+        kpc, vpc = oracle.pool_views(pool_ref)
+        gates(out, (q, kpc, vpc, requests, positions, c.mapping, 16, 4, 128, c.scale))
+        outs.append(out.cpu().double())
+    assert rt._C._take_device_status() == 0
+    assert float((outs[0] - outs[1]).abs().max()) <= 2e-2
