@@ -6,19 +6,23 @@
 // Q.K^T (128 x 128 x d) and P.V (128 x d x 128) are real dense contractions, so they run as
 // tcgen05.mma.kind::f16 with fp32 accumulators in tensor memory:
 //
-//   warps 0-3  softmax: one thread per packed row (= TMEM lane); reads S with tcgen05.ld, keeps
-//              the online (m, l), rescales O in TMEM when the maximum moves, writes P (bf16,
-//              the reference's rounding point) to shared memory, and finally normalises O
-//   warps 4-5  loaders: K and V rows of a 128-token tile -> shared memory with 16-byte cp.async,
-//              slots resolved from the table (any page size), two-stage ring
-//   warp 6     one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_j V_j, signalling
+//   warps 0-7  softmax, two warpgroups: thread (wg, row) owns columns [64 wg, 64 wg + 64) of
+//              packed row `row` (= TMEM lane).  It reads S with tcgen05.ld, the two halves of a
+//              row exchange their maxima through shared memory, O is rescaled in TMEM only when
+//              the running maximum moved by more than 2^8, P (bf16, the reference's rounding
+//              point) goes to shared memory, and at the end O is normalised and written out
+//   warps 8-9  loaders: K and V rows of a 128-token tile -> shared memory with 16-byte cp.async,
+//              slots resolved from the table (any page size); completion is signalled
+//              asynchronously (cp.async.mbarrier.arrive), the loaders never wait for their copies
+//   warp 10    one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_{j-1} V_{j-1}, signalling
 //              completion through tcgen05.commit -> mbarrier
 //
 // Shared-memory operand tiles are [128 rows x 128 bf16] as two panels of [128 x 64] with the
 // 128-byte swizzle (16-byte chunk c of row r at chunk c ^ (r & 7)); the same bytes serve K as a
-// K-major operand and V as an MN-major operand.  S is double-buffered in TMEM so that Q K_{j+1}^T
-// runs under softmax_j.  Every mbarrier wait is bounded: on expiry the CTA raises
-// GK_DEV_WAIT_EXPIRED, drains its copies, frees its TMEM and returns.
+// K-major operand and V as an MN-major operand.  S and P are double-buffered, K and V have two
+// stages each, so Q K_{j+1}^T and the loads run under softmax_j and P_j V_j under softmax_{j+1}.
+// Every mbarrier wait is bounded: on expiry the CTA raises GK_DEV_WAIT_EXPIRED, drains its
+// copies, frees its TMEM and returns.
 #include "gk_common.cuh"
 
 #include <math_constants.h>
@@ -29,7 +33,7 @@ namespace {
 constexpr int kTile = 128;             // packed query rows per CTA, KV tokens per tile, head_dim
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
-constexpr int kSoftmaxThreads = 128, kLoaderThreads = 64, kThreads = 224;
+constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 352;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSpinLimit = 1 << 22;
 
@@ -48,9 +52,10 @@ struct PrefillParams {
 };
 
 struct Shared {
-  uint64_t kv_full[2], kv_empty[2], s_full[2], p_full, pv_done;
+  uint64_t k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], swap[3];   // swap: row-half exchanges
   uint32_t tmem_base;
   int abort;
+  float exchange[2][2][kTile];     // [tile parity][warpgroup][row]: row maxima, finally row sums
 };
 
 __device__ __forceinline__ uint32_t tile_off(int r, int c) {
@@ -75,6 +80,10 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+// Arrive once all cp.async of the calling thread issued so far have landed (counted arrival).
+__device__ __forceinline__ void bar_arrive_on_copies(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -109,6 +118,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
@@ -126,14 +146,18 @@ constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) |
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
 
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* tiles = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // swizzle atoms need 1 KiB alignment
+  extern __shared__ __align__(1024) uint8_t tiles[];     // swizzle atoms need 1 KiB alignment
   uint8_t* s_q = tiles;
-  uint8_t* s_p = tiles + kTileBytes;
-  uint8_t* s_kv = tiles + 2 * kTileBytes;              // stage s: K at s*64 KiB, V right after it
-  Shared* sh = reinterpret_cast<Shared*>(tiles + 6 * kTileBytes);
+  uint8_t* s_p = tiles + kTileBytes;                     // two P buffers
+  uint8_t* s_k = tiles + 3 * kTileBytes;                 // two K stages
+  uint8_t* s_v = tiles + 5 * kTileBytes;                 // two V stages
+  Shared* sh = reinterpret_cast<Shared*>(tiles + 7 * kTileBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (smem_u32(tiles) & 1023) {                          // cannot build valid descriptors: report, leave
+    if (tid == 0 && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
+    return;
+  }
   const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
   const int4 w0 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item);
   const int4 w1 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item + 1);
@@ -144,14 +168,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   const int n_tiles = (kv_end - kv_begin + kTile - 1) / kTile;
 
   if (tid == 0) {
-    bar_init(&sh->kv_full[0], kLoaderThreads);
-    bar_init(&sh->kv_full[1], kLoaderThreads);
-    bar_init(&sh->kv_empty[0], 1);
-    bar_init(&sh->kv_empty[1], 1);
-    bar_init(&sh->s_full[0], 1);
-    bar_init(&sh->s_full[1], 1);
-    bar_init(&sh->p_full, kSoftmaxThreads);
-    bar_init(&sh->pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      bar_init(&sh->k_full[i], kLoaderThreads);
+      bar_init(&sh->v_full[i], kLoaderThreads);
+      bar_init(&sh->s_full[i], 1);
+      bar_init(&sh->p_full[i], kSoftmaxThreads);
+      bar_init(&sh->pv_done[i], 1);
+    }
+    for (int i = 0; i < 3; ++i) bar_init(&sh->swap[i], kSoftmaxThreads);
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -185,100 +209,125 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   const uint32_t tmem = sh->tmem_base;
   const uint32_t tmem_o = tmem + 256;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // ================================ softmax ============================================
-    const int pr = tid;                                          // packed row == TMEM lane
+    const int wg = warp >> 2;                                    // which 64 columns of the row
+    const int pr = tid & 127;                                    // packed row == TMEM lane
     const int lim = pr < mv ? first_pos + pr / G : 0x7fffffff;   // last visible key of this row
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const bool capped = p.softcap > 0.f;
     const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
-    float m = -CUDART_INF_F, l = 0.f;
+    float m = -CUDART_INF_F, l = 0.f;                            // m: exponent reference of this row
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j & 1;
       alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], (j >> 1) & 1, sh));
       if (!alive) break;
       tc_fence_after();
-      const uint32_t s_addr = tmem + st * kTile + lane_base;
-      const int tok0 = kv_begin + j * kTile;
-      const bool ragged = tok0 + kTile > kv_end || tok0 + kTile > first_pos + 1 ||
-                          (p.window > 0 && tok0 <= first_pos + n_rows - 1 - p.window);
-      auto score = [&](uint32_t raw, int tok) -> float {
-        float s = __uint_as_float(raw);
-        if (capped) s = p.softcap * tanhf(s * cap_in);
-        s *= to_log2;
-        if (ragged) {
-          const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
-          if (!seen) s = -CUDART_INF_F;
-        }
-        return s;
-      };
-      // pass 1: row maximum of this tile
-      float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + cb * 32, r);
+      const uint32_t s_addr = tmem + st * kTile + wg * 64 + lane_base;
+      const int tok0 = kv_begin + j * kTile + wg * 64;
+      float sc[64];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32_nowait(s_addr, r0);
+        tmem_ld32_nowait(s_addr + 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, score(r[e], tok0 + cb * 32 + e));
+        for (int e = 0; e < 32; ++e) {
+          sc[e] = __uint_as_float(r0[e]);
+          sc[32 + e] = __uint_as_float(r1[e]);
+        }
       }
-      const float m_new = fmaxf(m, mx);
-      const float mu = m_new == -CUDART_INF_F ? 0.f : m_new;
-      const float alpha = fast_exp2(m - mu);
-      m = m_new;
-      // O may only be touched (and P overwritten) once the previous P.V has completed.
-      if (j > 0) {
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done, (j - 1) & 1, sh));
+      if (capped) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) sc[e] = p.softcap * tanhf(sc[e] * cap_in);
+      }
+      const int tile_end = kv_begin + (j + 1) * kTile;
+      const bool ragged = tile_end > kv_end || tile_end > first_pos + 1 ||
+                          (p.window > 0 && kv_begin + j * kTile <= first_pos + n_rows - 1 - p.window);
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int e = 0; e < 64; ++e) {
+        float v = sc[e] * to_log2;
+        if (ragged) {
+          const int tok = tok0 + e;
+          const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
+          if (!seen) v = -CUDART_INF_F;
+        }
+        sc[e] = v;
+        mx = fmaxf(mx, v);
+      }
+      // the two halves of a row meet through an mbarrier (a bounded wait, unlike bar.sync)
+      sh->exchange[st][wg][pr] = mx;
+      bar_arrive(&sh->swap[st]);
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[st], (j >> 1) & 1, sh));
+      if (!alive) break;
+      mx = fmaxf(mx, sh->exchange[st][wg ^ 1][pr]);
+      // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
+      // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
+      float alpha = 1.f;
+      if (mx > m + 8.f || m == -CUDART_INF_F) {
+        if (mx > m) {
+          alpha = fast_exp2(m - mx);                               // 0 on the first finite maximum
+          m = mx;
+        }
+      }
+      const float mu = m == -CUDART_INF_F ? 0.f : m;
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st ^ 1], ((j - 1) >> 1) & 1, sh));
         if (!alive) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-          for (int cb = 0; cb < 4; ++cb) {
-            uint32_t r[32];
-            tmem_ld32(tmem_o + lane_base + cb * 32, r);
+        for (int cb = 0; cb < 2; ++cb) {
+          uint32_t r[32];
+          tmem_ld32(tmem_o + lane_base + wg * 64 + cb * 32, r);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-            tmem_st32(tmem_o + lane_base + cb * 32, r);
-          }
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+          tmem_st32(tmem_o + lane_base + wg * 64 + cb * 32, r);
         }
+        tc_fence_before();
       }
-      // pass 2: probabilities, rounded to bf16 for the second product; l from the fp32 values
+      if (j >= 2) {                                                // P[st] was last read by P.V of tile j-2
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
+        if (!alive) break;
+      }
+      // probabilities, rounded to bf16 for the second product; l from the fp32 values
       float sum = 0.f;
-#pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + cb * 32, r);
+      uint8_t* p_tile = s_p + st * kTileBytes;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t packed[4];
+      for (int c = 0; c < 8; ++c) {
+        uint32_t packed[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = c * 8 + e * 2;
-            const float a = fast_exp2(score(r[col], tok0 + cb * 32 + col) - mu);
-            const float b = fast_exp2(score(r[col + 1], tok0 + cb * 32 + col + 1) - mu);
-            sum += a + b;
-            packed[e] = pack_bf16(a, b);
-          }
-          *reinterpret_cast<uint4*>(s_p + tile_off(pr, cb * 4 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        for (int e = 0; e < 4; ++e) {
+          const float a = fast_exp2(sc[c * 8 + 2 * e] - mu);
+          const float b = fast_exp2(sc[c * 8 + 2 * e + 1] - mu);
+          sum += a + b;
+          packed[e] = pack_bf16(a, b);
         }
+        *reinterpret_cast<uint4*>(p_tile + tile_off(pr, wg * 8 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       l = l * alpha + sum;
       fence_async_smem();
       tc_fence_before();
-      bar_arrive(&sh->p_full);
+      bar_arrive(&sh->p_full[st]);
     }
     // epilogue: O / l -> bf16 rows of the output
-    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done, (n_tiles - 1) & 1, sh));
+    const int last = n_tiles - 1;
+    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[last & 1], (last >> 1) & 1, sh));
+    sh->exchange[n_tiles & 1][wg][pr] = l;
+    bar_arrive(&sh->swap[2]);
+    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[2], 0, sh));
+    l += sh->exchange[n_tiles & 1][wg ^ 1][pr];
     if (alive) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int r_q = pr / G, g = pr - r_q * G;
-      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile;
+      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile + wg * 64;
 #pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
+      for (int cb = 0; cb < 2; ++cb) {
         uint32_t r[32];
-        tmem_ld32(tmem_o + lane_base + cb * 32, r);
+        tmem_ld32(tmem_o + lane_base + wg * 64 + cb * 32, r);
         if (pr < mv) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -292,10 +341,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ================================ K/V loaders =========================================
-    const int lt = tid - kSoftmaxThreads;                        // 0..63
-    const int lwarp = lt >> 5;
+    const int lwarp = warp - 8;
     const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * kTile;
     const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * kTile;
     const int32_t* trow = p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
@@ -303,74 +351,74 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     bool alive = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
-      // Tile j-1 must be announced before waiting for stage `st` to drain: the P.V that frees it
-      // is only issued after Q.K^T of tile j-1.
-      if (j >= 1) {
-        cp_async_wait<0>();
-        fence_async_smem();
-        bar_arrive(&sh->kv_full[(j - 1) & 1]);
-      }
-      if (j >= 2) {
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->kv_empty[st], ((j >> 1) - 1) & 1, sh));
-        if (!alive) break;
-      }
-      const uint32_t dst_k = smem_u32(s_kv) + st * 2 * kTileBytes, dst_v = dst_k + kTileBytes;
       // each loader warp stages 64 rows, 32 at a time: lanes resolve one slot each, then the
       // warp copies two 256-byte rows per instruction (16 lanes x 16 bytes each)
-#pragma unroll 1
+      int slot[2];
+#pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int row0 = lwarp * 64 + half * 32;
-        const int tok = kv_begin + j * kTile + row0 + lane;
-        int slot = -1;
+        const int tok = kv_begin + j * kTile + lwarp * 64 + half * 32 + lane;
+        slot[half] = -1;
         if (tok < kv_end) {
-          slot = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
-          if ((unsigned)slot >= (unsigned)p.slots) {
+          slot[half] = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
+          if ((unsigned)slot[half] >= (unsigned)p.slots) {
             if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
-            slot = -1;
+            slot[half] = -1;
           }
         }
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int rr = 2 * i + (lane >> 4), c = lane & 15;
-          const int s = __shfl_sync(0xffffffffu, slot, rr);
-          const int64_t src = (int64_t)(s < 0 ? 0 : s) * kTile + c * 8;
-          const int bytes = s < 0 ? 0 : 16;
-          const uint32_t off = tile_off(row0 + rr, c);
-          cp_async_16(dst_k + off, kbase + src, bytes);
-          cp_async_16(dst_v + off, vbase + src, bytes);
-        }
       }
-      cp_async_commit();
+      auto stage_rows = [&](const __nv_bfloat16* base, uint32_t dst) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rr = 2 * i + (lane >> 4), c = lane & 15;
+            const int s = __shfl_sync(0xffffffffu, slot[half], rr);
+            cp_async_16(dst + tile_off(lwarp * 64 + half * 32 + rr, c), base + (int64_t)(s < 0 ? 0 : s) * kTile + c * 8,
+                        s < 0 ? 0 : 16);
+          }
+        }
+      };
+      if (j >= 2) {                          // K stage: free once Q.K^T of tile j-2 has completed
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], ((j - 2) >> 1) & 1, sh));
+        if (!alive) break;
+      }
+      stage_rows(kbase, smem_u32(s_k) + st * kTileBytes);
+      bar_arrive_on_copies(&sh->k_full[st]);
+      if (j >= 2) {                          // V stage: free once P.V of tile j-2 has completed
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
+        if (!alive) break;
+      }
+      stage_rows(vbase, smem_u32(s_v) + st * kTileBytes);
+      bar_arrive_on_copies(&sh->v_full[st]);
     }
-    cp_async_wait<0>();
-    if (alive) {
-      fence_async_smem();
-      bar_arrive(&sh->kv_full[(n_tiles - 1) & 1]);
-    }
-  } else if (lane == 0) {
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
+  } else if (warp == 10 && lane == 0) {
     // ================================ MMA issue ===========================================
-    const uint32_t q_addr = smem_u32(s_q), p_addr = smem_u32(s_p), kv_addr = smem_u32(s_kv);
+    const uint32_t q_addr = smem_u32(s_q), p_addr = smem_u32(s_p), k_base = smem_u32(s_k), v_base = smem_u32(s_v);
     bool alive = true;
     auto issue_pv = [&](int i) {
-      if (!bar_wait(&sh->p_full, i & 1, sh)) return false;
+      const int st = i & 1;
+      if (!bar_wait(&sh->p_full[st], (i >> 1) & 1, sh)) return false;
+      if (!bar_wait(&sh->v_full[st], (i >> 1) & 1, sh)) return false;
+      fence_async_smem();
       tc_fence_after();
-      const uint32_t v_addr = kv_addr + (i & 1) * 2 * kTileBytes + kTileBytes;
+      const uint32_t v_addr = v_base + st * kTileBytes, pa = p_addr + st * kTileBytes;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {                    // 16 tokens per step
-        const uint64_t da = umma_desc(p_addr + (k >> 2) * kPanelBytes + (k & 3) * 32, 16, 1024);
+        const uint64_t da = umma_desc(pa + (k >> 2) * kPanelBytes + (k & 3) * 32, 16, 1024);
         const uint64_t db = umma_desc(v_addr + k * 2048, kPanelBytes, 1024);
         umma_bf16(tmem_o, da, db, kIdescPV, (i > 0 || k > 0) ? 1u : 0u);
       }
-      umma_commit(&sh->kv_empty[i & 1]);
-      umma_commit(&sh->pv_done);
+      umma_commit(&sh->pv_done[st]);
       return true;
     };
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j & 1;
-      alive = bar_wait(&sh->kv_full[st], (j >> 1) & 1, sh);
+      alive = bar_wait(&sh->k_full[st], (j >> 1) & 1, sh);
       if (!alive) break;
+      fence_async_smem();
       tc_fence_after();
-      const uint32_t k_addr = kv_addr + st * 2 * kTileBytes;
+      const uint32_t k_addr = k_base + st * kTileBytes;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {                    // 16 elements of head_dim per step
         const uint32_t koff = (k >> 2) * kPanelBytes + (k & 3) * 32;
@@ -389,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
 }
 
-constexpr int kSmemBytes = 6 * kTileBytes + 1024 + 256;
+constexpr int kSmemBytes = 7 * kTileBytes + 3072;   // 227 KiB: the whole opt-in shared memory of an SM
 
 }  // namespace
 }  // namespace gk
