@@ -239,25 +239,33 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           sc[32 + e] = __uint_as_float(r1[e]);
         }
       }
-      if (capped) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) sc[e] = p.softcap * tanhf(sc[e] * cap_in);
-      }
       const int tile_end = kv_begin + (j + 1) * kTile;
       const bool ragged = tile_end > kv_end || tile_end > first_pos + 1 ||
                           (p.window > 0 && kv_begin + j * kTile <= first_pos + n_rows - 1 - p.window);
-      float mx = -CUDART_INF_F;
+      // After this block sc[] holds raw scores and `mult` the factor that takes them to log2
+      // units; the uncommon cases (softcap, tiles that need masking) rewrite sc[] in place.
+      float mult = to_log2;
+      if (capped || ragged) {
 #pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        float v = sc[e] * to_log2;
-        if (ragged) {
+        for (int e = 0; e < 64; ++e) {
+          float v = sc[e];
+          if (capped) v = p.softcap * tanhf(v * cap_in);
+          v *= to_log2;
           const int tok = tok0 + e;
           const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
-          if (!seen) v = -CUDART_INF_F;
+          sc[e] = seen ? v : -CUDART_INF_F;
         }
-        sc[e] = v;
-        mx = fmaxf(mx, v);
+        mult = 1.f;
       }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int e = 0; e < 64; e += 4) {
+        mx4[0] = fmaxf(mx4[0], sc[e]);
+        mx4[1] = fmaxf(mx4[1], sc[e + 1]);
+        mx4[2] = fmaxf(mx4[2], sc[e + 2]);
+        mx4[3] = fmaxf(mx4[3], sc[e + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;     // mult > 0
       // the two halves of a row meet through an mbarrier (a bounded wait, unlike bar.sync)
       sh->exchange[st][wg][pr] = mx;
       bar_arrive(&sh->swap[st]);
@@ -293,21 +301,22 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         if (!alive) break;
       }
       // probabilities, rounded to bf16 for the second product; l from the fp32 values
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* p_tile = s_p + st * kTileBytes;
+      const float neg_mu = -mu;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t packed[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float a = fast_exp2(sc[c * 8 + 2 * e] - mu);
-          const float b = fast_exp2(sc[c * 8 + 2 * e + 1] - mu);
-          sum += a + b;
+          const float a = fast_exp2(fmaf(sc[c * 8 + 2 * e], mult, neg_mu));
+          const float b = fast_exp2(fmaf(sc[c * 8 + 2 * e + 1], mult, neg_mu));
+          sum4[e] += a + b;
           packed[e] = pack_bf16(a, b);
         }
         *reinterpret_cast<uint4*>(p_tile + tile_off(pr, wg * 8 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      l = l * alpha + sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       fence_async_smem();
       tc_fence_before();
       bar_arrive(&sh->p_full[st]);
