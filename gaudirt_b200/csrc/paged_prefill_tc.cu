@@ -11,10 +11,10 @@
 //              row exchange their maxima through shared memory, O is rescaled in TMEM only when
 //              the running maximum moved by more than 2^8, P (bf16, the reference's rounding
 //              point) goes to shared memory, and at the end O is normalised and written out
-//   warps 8-9  loaders: K and V rows of a 128-token tile -> shared memory with 16-byte cp.async,
+//   warps 8-11 loaders (8-9 for K, 10-11 for V): rows of a 128-token tile -> shared memory with 16-byte cp.async,
 //              slots resolved from the table (any page size); completion is signalled
 //              asynchronously (cp.async.mbarrier.arrive), the loaders never wait for their copies
-//   warp 10    one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_{j-1} V_{j-1}, signalling
+//   warp 12    one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_{j-1} V_{j-1}, signalling
 //              completion through tcgen05.commit -> mbarrier
 //
 // Shared-memory operand tiles are [128 rows x 128 bf16] as two panels of [128 x 64] with the
@@ -33,7 +33,7 @@ namespace {
 constexpr int kTile = 128;             // packed query rows per CTA, KV tokens per tile, head_dim
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
-constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 352;
+constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V; 4 warpgroups
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSpinLimit = 1 << 22;
 
@@ -209,6 +209,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   const uint32_t tmem = sh->tmem_base;
   const uint32_t tmem_o = tmem + 256;
 
+  // Registers move from the loader/MMA warpgroups (which need few) to the softmax warpgroups.
+  if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;\n");
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+  }
   if (warp < 8) {
     // ================================ softmax ============================================
     const int wg = warp >> 2;                                    // which 64 columns of the row
@@ -350,9 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         }
       }
     }
-  } else if (warp < 10) {
+  } else if (warp < 12) {
     // ================================ K/V loaders =========================================
-    const int lwarp = warp - 8;
+    const bool is_v = warp >= 10;
+    const int lwarp = (warp - 8) & 1;
     const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * kTile;
     const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * kTile;
     const int32_t* trow = p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
@@ -387,21 +394,24 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           }
         }
       };
-      if (j >= 2) {                          // K stage: free once Q.K^T of tile j-2 has completed
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], ((j - 2) >> 1) & 1, sh));
-        if (!alive) break;
+      if (!is_v) {
+        if (j >= 2) {                        // K stage: free once Q.K^T of tile j-2 has completed
+          alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], ((j - 2) >> 1) & 1, sh));
+          if (!alive) break;
+        }
+        stage_rows(kbase, smem_u32(s_k) + st * kTileBytes);
+        bar_arrive_on_copies(&sh->k_full[st]);
+      } else {
+        if (j >= 2) {                        // V stage: free once P.V of tile j-2 has completed
+          alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
+          if (!alive) break;
+        }
+        stage_rows(vbase, smem_u32(s_v) + st * kTileBytes);
+        bar_arrive_on_copies(&sh->v_full[st]);
       }
-      stage_rows(kbase, smem_u32(s_k) + st * kTileBytes);
-      bar_arrive_on_copies(&sh->k_full[st]);
-      if (j >= 2) {                          // V stage: free once P.V of tile j-2 has completed
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
-        if (!alive) break;
-      }
-      stage_rows(vbase, smem_u32(s_v) + st * kTileBytes);
-      bar_arrive_on_copies(&sh->v_full[st]);
     }
     asm volatile("cp.async.wait_all;\n" ::: "memory");
-  } else if (warp == 10 && lane == 0) {
+  } else if (warp == 12 && lane == 0) {
     // ================================ MMA issue ===========================================
     const uint32_t q_addr = smem_u32(s_q), p_addr = smem_u32(s_p), k_base = smem_u32(s_k), v_base = smem_u32(s_v);
     bool alive = true;

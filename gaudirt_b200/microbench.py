@@ -1,0 +1,81 @@
+"""Kernel-level timings of the small kernels of the path against the HBM roofline.
+
+    python -m gaudirt_b200.microbench
+
+Times `kv_store`, `fused_add_rms_norm`, `rotary_embedding` and the split-KV combine alone with CUDA
+events (inputs larger than L2 are cycled so no launch re-reads cached data) and prints algorithmic
+bytes / time next to the measured copy bandwidth from MEASURED_PEAKS.json when that file exists."""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+
+def _time(fn, sets, iters=20):
+    for i in range(3):
+        fn(*sets[i % len(sets)])
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fn(*sets[i % len(sets)])
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main():
+    import gaudirt_b200 as rt
+    from gaudirt_b200 import raw as H
+    dev = "cuda:0"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    peak = 6650.0
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peak = float(json.load(open(path))["hbm_gbs"])
+    rows = []
+
+    # KV store, chunked-prefill size: 8192 rows x 8 KV heads x 128
+    kv_heads, d, slots, n = 8, 128, 1 << 20, 8192
+    sets = []
+    for i in range(6):
+        pool = torch.zeros(2, kv_heads, slots, d, dtype=torch.bfloat16, device=dev)
+        k = torch.randn(n, kv_heads * d, device=dev).to(torch.bfloat16)
+        loc = torch.randperm(slots, device=dev)[:n].to(torch.int32)
+        sets.append((pool, k, k.clone(), loc))
+    ms = _time(lambda pool, k, v, loc: H.kv_store(pool, k, v, loc), sets)
+    rows.append(("kv_store_kernel<8>  8192 rows x 8 heads x 128", 2 * 2 * n * kv_heads * d * 2, ms))
+    del sets
+
+    # fused_add_rms_norm, 8192 rows x hidden 8192
+    sets = []
+    for i in range(4):
+        x = torch.randn(8192, 8192, device=dev).to(torch.bfloat16)
+        sets.append((x, x.clone(), torch.ones(8192, dtype=torch.bfloat16, device=dev)))
+    ms = _time(lambda x, r, w: torch.ops.gaudirt.fused_add_rms_norm(x, r, w, 1e-5, 1.0), sets)
+    rows.append(("rms_norm_kernel<8,fused>  8192 x 8192", 4 * 8192 * 8192 * 2, ms))
+    ms = _time(lambda x, r, w: torch.ops.gaudirt.fused_add_rms_norm(x[:64], r[:64], w, 1e-5, 1.0), sets)
+    rows.append(("rms_norm_kernel<8,fused>  64 x 8192 (decode step)", 4 * 64 * 8192 * 2, ms))
+    del sets
+
+    # rotary, 8192 rows, 32 q heads + 8 k heads x 128
+    sets = []
+    cache = torch.randn(16384, 128, device=dev).to(torch.bfloat16)
+    for i in range(4):
+        q = torch.randn(8192, 32 * 128, device=dev).to(torch.bfloat16)
+        k = torch.randn(8192, 8 * 128, device=dev).to(torch.bfloat16)
+        pos = torch.randint(0, 16384, (8192,), device=dev, dtype=torch.int32)
+        sets.append((q, k, pos))
+    ms = _time(lambda q, k, pos: torch.ops.gaudirt.rotary_embedding_positions(q, k, cache, pos, 128, 128, True), sets)
+    rows.append(("rotary_kernel  8192 rows x (32+8) heads x 128", 2 * 8192 * 40 * 128 * 2, ms))
+
+    print(f"{'kernel / case':58s} {'ms':>8s} {'GB/s':>9s} {'of measured copy peak':>22s}")
+    for name, nbytes, ms in rows:
+        gbs = nbytes / ms / 1e6
+        print(f"{name:58s} {ms:8.4f} {gbs:9.1f} {gbs / peak:22.3f}")
+
+
+if __name__ == "__main__":
+    main()
