@@ -11,9 +11,13 @@
 //              row exchange their maxima through shared memory, O is rescaled in TMEM only when
 //              the running maximum moved by more than 2^8, P (bf16, the reference's rounding
 //              point) goes to shared memory, and at the end O is normalised and written out
-//   warps 8-11 loaders (8-9 for K, 10-11 for V): rows of a 128-token tile -> shared memory with 16-byte cp.async,
-//              slots resolved from the table (any page size); completion is signalled
-//              asynchronously (cp.async.mbarrier.arrive), the loaders never wait for their copies
+//   warps 8-11 loaders (8-9 for K, 10-11 for V) of a 128-token tile.  A tile made of whole,
+//              slot-contiguous pages of >= 8 tokens is fetched by TMA: one elected thread issues
+//              cp.async.bulk.tensor (2-D boxes of 64 columns x page rows, 128-byte swizzle, no
+//              multicast) per page and panel, completion by transaction bytes on the mbarrier.
+//              Any other tile (ragged tail, token-granular tables, window offsets) is gathered
+//              row by row with 16-byte cp.async, completion by cp.async.mbarrier.arrive.  The
+//              loaders never wait for their copies
 //   warp 12    one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_{j-1} V_{j-1}, signalling
 //              completion through tcgen05.commit -> mbarrier
 //
@@ -25,6 +29,8 @@
 // copies, frees its TMEM and returns.
 #include "gk_common.cuh"
 
+#include <cuda.h>
+#include <string.h>
 #include <math_constants.h>
 
 namespace gk {
@@ -49,6 +55,7 @@ struct PrefillParams {
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group;
+  int tma_rows;          // rows of a TMA box (= page_tokens), 0 = TMA path off
 };
 
 struct Shared {
@@ -84,6 +91,16 @@ __device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
 // Arrive once all cp.async of the calling thread issued so far have landed (counted arrival).
 __device__ __forceinline__ void bar_arrive_on_copies(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One 2-D TMA box (64 columns x box rows of the [kv_heads*slots, 128] pool view) into shared memory.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
 }
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -145,7 +162,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);   // A, B K-major
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
 
-__global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p,
+                                                                       const __grid_constant__ CUtensorMap map_k,
+                                                                       const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t tiles[];     // swizzle atoms need 1 KiB alignment
   uint8_t* s_q = tiles;
   uint8_t* s_p = tiles + kTileBytes;                     // two P buffers
@@ -211,9 +230,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
 
   // Registers move from the loader/MMA warpgroups (which need few) to the softmax warpgroups.
   if (warp < 8) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;\n");
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n");
   }
   if (warp < 8) {
     // ================================ softmax ============================================
@@ -394,20 +413,37 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           }
         }
       };
-      if (!is_v) {
-        if (j >= 2) {                        // K stage: free once Q.K^T of tile j-2 has completed
-          alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], ((j - 2) >> 1) & 1, sh));
-          if (!alive) break;
+      // This warp's 64 rows go by TMA when they are whole, in-range boxes of tma_rows slot-contiguous
+      // tokens; the two warps of a tile decide independently (every thread arrives once either way).
+      const int tok_first = kv_begin + j * kTile + lwarp * 64;
+      bool by_tma = p.tma_rows > 0 && (tok_first & (p.tma_rows - 1)) == 0 && tok_first + 64 <= kv_end;
+      by_tma = __all_sync(0xffffffffu, by_tma && slot[0] >= 0 && slot[1] >= 0);
+      uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
+      if (j >= 2) {   // stage free: K once Q.K^T of tile j-2 completed, V once P.V of tile j-2 completed
+        uint64_t* freed = is_v ? &sh->pv_done[st] : &sh->s_full[st];
+        alive = __all_sync(0xffffffffu, bar_wait(freed, ((j - 2) >> 1) & 1, sh));
+        if (!alive) break;
+      }
+      const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
+      if (by_tma) {
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        const int head_row = head * (int)p.slots;
+        if (lane == 0) bar_arrive_expect_tx(full, 64 * 256);
+        else bar_arrive(full);
+        __syncwarp();
+        // the lane that holds the first row of a box issues its two panels
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = half * 32 + lane;                       // row within this warp's 64
+          if ((row & (p.tma_rows - 1)) == 0) {
+            const uint32_t at = dst + (lwarp * 64 + row) * 128;
+            tma_load_box(at, map, 0, head_row + slot[half], full);
+            tma_load_box(at + kPanelBytes, map, 64, head_row + slot[half], full);
+          }
         }
-        stage_rows(kbase, smem_u32(s_k) + st * kTileBytes);
-        bar_arrive_on_copies(&sh->k_full[st]);
       } else {
-        if (j >= 2) {                        // V stage: free once P.V of tile j-2 has completed
-          alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
-          if (!alive) break;
-        }
-        stage_rows(vbase, smem_u32(s_v) + st * kTileBytes);
-        bar_arrive_on_copies(&sh->v_full[st]);
+        stage_rows(is_v ? vbase : kbase, dst);
+        bar_arrive_on_copies(full);
       }
     }
     asm volatile("cp.async.wait_all;\n" ::: "memory");
@@ -454,6 +490,38 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   __syncthreads();
   if (tid == 0 && sh->abort && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      sym = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// 2-D view [kv_heads*slots rows, 128 bf16] of one pool half; boxes of 64 columns x box_rows rows.
+bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kTile, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kTile * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 constexpr int kSmemBytes = 7 * kTileBytes + 3072;   // 227 KiB: the whole opt-in shared memory of an SM
@@ -508,7 +576,16 @@ extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, con
       return gk::check_launch();
     if (device >= 0 && device < 64) configured[device] = true;
   }
+  // TMA boxes need slot-contiguous pages of at least 8 tokens and 32-bit row coordinates.
+  alignas(64) CUtensorMap map_k, map_v;
+  memset(&map_k, 0, sizeof(map_k));
+  memset(&map_v, 0, sizeof(map_v));
+  const int box_rows = page_tokens < 64 ? page_tokens : 64;
+  const int64_t pool_rows = (int64_t)kv_heads * slots;
+  if (page_tokens >= 8 && pool_rows < 0x7fffffffLL && gk::make_pool_map(&map_k, pool_k, pool_rows, box_rows) &&
+      gk::make_pool_map(&map_v, pool_v, pool_rows, box_rows))
+    p.tma_rows = box_rows;
   gk::paged_prefill_tc_kernel<<<(unsigned)(n_work * kv_heads), gk::kThreads, gk::kSmemBytes,
-                                reinterpret_cast<cudaStream_t>(stream)>>>(p);
+                                reinterpret_cast<cudaStream_t>(stream)>>>(p, map_k, map_v);
   return gk::check_launch();
 }
