@@ -40,8 +40,11 @@ constexpr int kTile = 128;             // packed query rows per CTA, KV tokens p
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
 constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V; 4 warpgroups
+constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
+constexpr int kSoftmaxRegs = 176, kOtherRegs = 80;
+static_assert(kSoftmaxThreads * kSoftmaxRegs + (kThreads - kSoftmaxThreads) * kOtherRegs <= kThreads * kLaunchRegs,
+              "register budgets exceed the pool the launch allocates");
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kSpinLimit = 1 << 22;
 
 struct PrefillParams {
   const __nv_bfloat16* q;
@@ -105,7 +108,11 @@ __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* ma
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait; returns false (and raises the CTA's abort flag) when it gives up.
+// Bounded wait; returns false (and raises the CTA's abort flag) when it gives up.  The loaders,
+// whose waits are long and off the critical path, give try_wait a suspend-time hint so that they
+// sleep in hardware instead of spinning through issue slots the softmax warps need.
+constexpr int kSpinLimit = 1 << 22;
+constexpr int kPatientHintNs = 1000, kPatientLimit = 1 << 20;
 __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, Shared* sh) {
   const uint32_t addr = smem_u32(bar);
   for (int i = 0; i < kSpinLimit; ++i) {
@@ -116,6 +123,20 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, Shared*
                  : "memory");
     if (ok) return true;
     if ((i & 1023) == 1023 && *reinterpret_cast<volatile int*>(&sh->abort)) return false;
+  }
+  atomicExch(&sh->abort, 1);
+  return false;
+}
+__device__ __forceinline__ bool bar_wait_patient(uint64_t* bar, uint32_t parity, Shared* sh) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < kPatientLimit; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\nselp.b32 %0, 1, 0, P1;\n}\n"
+                 : "=r"(ok)
+                 : "r"(addr), "r"(parity), "r"(kPatientHintNs)
+                 : "memory");
+    if (ok) return true;
+    if (*reinterpret_cast<volatile int*>(&sh->abort)) return false;
   }
   atomicExch(&sh->abort, 1);
   return false;
@@ -229,10 +250,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   const uint32_t tmem_o = tmem + 256;
 
   // Registers move from the loader/MMA warpgroups (which need few) to the softmax warpgroups.
+  // setmaxnreg.inc blocks until the CTA's register pool can satisfy it, and the pool is what the
+  // launch allocated (kThreads x kLaunchRegs): the two budgets must fit in it or the softmax warps
+  // would never start (checked at compile time and again on the host before every launch).
   if (warp < 8) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;\n");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kSoftmaxRegs));
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kOtherRegs));
   }
   if (warp < 8) {
     // ================================ softmax ============================================
@@ -421,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
       if (j >= 2) {   // stage free: K once Q.K^T of tile j-2 completed, V once P.V of tile j-2 completed
         uint64_t* freed = is_v ? &sh->pv_done[st] : &sh->s_full[st];
-        alive = __all_sync(0xffffffffu, bar_wait(freed, ((j - 2) >> 1) & 1, sh));
+        alive = __all_sync(0xffffffffu, bar_wait_patient(freed, ((j - 2) >> 1) & 1, sh));
         if (!alive) break;
       }
       const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
@@ -575,6 +599,18 @@ extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, con
         cudaSuccess)
       return gk::check_launch();
     if (device >= 0 && device < 64) configured[device] = true;
+  }
+  {
+    // Never launch if the register pool of this build cannot satisfy the budgets (the kernel would hang).
+    static int launch_regs = -1;
+    if (launch_regs < 0) {
+      cudaFuncAttributes attr;
+      if (cudaFuncGetAttributes(&attr, gk::paged_prefill_tc_kernel) != cudaSuccess) return gk::check_launch();
+      launch_regs = attr.numRegs;
+    }
+    if (launch_regs * gk::kThreads <
+        gk::kSoftmaxThreads * gk::kSoftmaxRegs + (gk::kThreads - gk::kSoftmaxThreads) * gk::kOtherRegs)
+      return GK_ERR_UNSUPPORTED;
   }
   // TMA boxes need slot-contiguous pages of at least 8 tokens and 32-bit row coordinates.
   alignas(64) CUtensorMap map_k, map_v;
