@@ -126,6 +126,8 @@ def parse():
     ap.add_argument("--ctx", type=int, default=0, help="experiments only (config 2)")
     ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample; 0 = sized for a few seconds")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
     return ap.parse_args()
 
 
@@ -302,7 +304,8 @@ def run_b200(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     w = make_workload(args)
-    shard = tp.HeadShard(rank, world, w.q_heads, w.kv_heads)
+    shard = tp.HeadShard(rank, world, w.q_heads, w.kv_heads) if args.shard_of == 1 or world > 1 else \
+        tp.HeadShard(0, args.shard_of, w.q_heads, w.kv_heads)
     B, d, L, R = w.batch, HEAD_DIM, w.layers, w.rows
     hq, hkv = shard.local_q_heads, shard.local_kv_heads
 

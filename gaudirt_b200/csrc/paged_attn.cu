@@ -339,10 +339,17 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
   const int entries = n_rows * q_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = blockIdx.y * 4 + warp; e < entries; e += gridDim.y * 4) {
+    // (m, l) of up to 32 splits at a time, one per lane: the reference maximum and the weights come
+    // from warp reductions, then the O rows (independent loads) are accumulated in split order.
     float mstar = -CUDART_INF_F;
-    for (int s = 0; s < n_splits; ++s) {
-      const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml) + (int64_t)base + (int64_t)s * entries + e);
-      if (ml.y > 0.f) mstar = fmaxf(mstar, ml.x);
+    for (int s0 = 0; s0 < n_splits; s0 += 32) {
+      const int sidx = s0 + lane;
+      float2 ml = make_float2(-CUDART_INF_F, 0.f);
+      if (sidx < n_splits) ml = __ldg(reinterpret_cast<const float2*>(part_ml) + (int64_t)base + (int64_t)sidx * entries + e);
+      float mine = ml.y > 0.f ? ml.x : -CUDART_INF_F;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mine = fmaxf(mine, __shfl_xor_sync(0xffffffffu, mine, o));
+      mstar = fmaxf(mstar, mine);
     }
     constexpr int kVec = D / 128 > 0 ? D / 128 : 1;              // float4 per lane
     float4 acc[kVec];
@@ -350,20 +357,29 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
     for (int v = 0; v < kVec; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     float lsum = 0.f;
     const bool active = lane * 4 < D;
-    for (int s = 0; s < n_splits; ++s) {
-      const int64_t entry = (int64_t)base + (int64_t)s * entries + e;
-      const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml) + entry);
-      if (!(ml.y > 0.f)) continue;
-      const float wgt = fast_exp2(ml.x - mstar);
-      lsum += wgt * ml.y;
-      if (active) {
+    for (int s0 = 0; s0 < n_splits; s0 += 32) {
+      const int sidx = s0 + lane;
+      float2 ml = make_float2(-CUDART_INF_F, 0.f);
+      if (sidx < n_splits) ml = __ldg(reinterpret_cast<const float2*>(part_ml) + (int64_t)base + (int64_t)sidx * entries + e);
+      const float wgt_mine = ml.y > 0.f ? fast_exp2(ml.x - mstar) : 0.f;
+      float part = wgt_mine * ml.y;
 #pragma unroll
-        for (int v = 0; v < kVec; ++v) {
-          const float4 x = __ldg(reinterpret_cast<const float4*>(part_o + entry * D) + v * 32 + lane);
-          acc[v].x += wgt * x.x;
-          acc[v].y += wgt * x.y;
-          acc[v].z += wgt * x.z;
-          acc[v].w += wgt * x.w;
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      lsum += part;
+      const int n_here = n_splits - s0 < 32 ? n_splits - s0 : 32;
+#pragma unroll 4
+      for (int s = 0; s < n_here; ++s) {
+        const float wgt = __shfl_sync(0xffffffffu, wgt_mine, s);
+        if (active) {
+          const int64_t entry = (int64_t)base + (int64_t)(s0 + s) * entries + e;
+#pragma unroll
+          for (int v = 0; v < kVec; ++v) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(part_o + entry * D) + v * 32 + lane);
+            acc[v].x += wgt * x.x;
+            acc[v].y += wgt * x.y;
+            acc[v].z += wgt * x.z;
+            acc[v].w += wgt * x.w;
+          }
         }
       }
     }
