@@ -126,6 +126,7 @@ def parse():
     ap.add_argument("--ctx", type=int, default=0, help="experiments only (config 2)")
     ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample; 0 = sized for a few seconds")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--combine", default="auto", choices=["auto", "fused", "separate"], help="experiments only")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
     return ap.parse_args()
@@ -369,6 +370,7 @@ def run_b200(args):
         return torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], md, d, scale)
 
     md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+    md._set_fused_combine({"auto": -1, "separate": 0, "fused": 1}[args.combine])
     md.attention_plan(hq, hkv, d)
 
     def resident_step():

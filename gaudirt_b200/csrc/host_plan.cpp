@@ -238,6 +238,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
     const int64_t span = b.hi - b.lo;
     int64_t splits, per;
     cut(span, chunk, splits, per);
+    if (splits > 0x7fff) return GK_ERR_CAPACITY;     // the split index shares a record word with the count
     int64_t base = -1;
     if (splits > 1) {
       base = entries;
@@ -254,7 +255,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
       it.w[4] = (int32_t)(b.lo + s * per);
       it.w[5] = (int32_t)std::min<int64_t>(b.hi, b.lo + (s + 1) * per);
       it.w[6] = base < 0 ? -1 : (int32_t)(base + s * b.n_rows * q_heads);
-      it.w[7] = (int32_t)splits;
+      it.w[7] = (int32_t)(splits | (s << 16));     // low half: splits of the block, high half: which one
       items.push_back(it);
     }
   }

@@ -32,6 +32,7 @@ struct AttnParams {
   float* part_ml;
   float* part_o;
   int32_t* status;
+  int32_t* counters;                     // optional: per (first_row, kv_head) arrival counts for the fused combine
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group, n_out;
@@ -62,6 +63,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
   const int4 w1 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item + 1);
   const int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, table_row = w0.w;
   const int kv_begin = w1.x, kv_end = w1.y, partial_base = w1.z;
+  const int n_splits = w1.w & 0xffff, split_index = (w1.w >> 16) & 0x7fff;
   const int G = p.group;
   const int mv = n_rows * G;                                    // packed rows in use (<= 16)
 
@@ -318,6 +320,57 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       if (c4 == 0) *reinterpret_cast<float2*>(p.part_ml + entry * 2) = make_float2(mstar, lsum);
     }
   }
+
+  // ---- fused combine: the CTA that completes a block's last split merges all of them ---------
+  // Arrival order decides only WHO merges; the merge itself runs over the splits in split order, so
+  // the result does not depend on scheduling.  The counter returns to zero for the next launch.
+  if (partial_base >= 0 && p.counters != nullptr) {
+    __shared__ int is_last;
+    __threadfence();                                   // this CTA's split state before its arrival
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* counter = p.counters + (int64_t)first_row * p.kv_heads + head;
+      const int seen = atomicAdd(counter, 1);
+      is_last = seen == n_splits - 1;
+      if (is_last) *counter = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();                                 // the other CTAs' split state after their arrivals
+      const int stride = n_rows * p.q_heads;           // entries per split
+      const int64_t base = (int64_t)partial_base - (int64_t)split_index * stride;
+      for (int idx = threadIdx.x; idx < mv * (D / 4); idx += WARPS * 32) {
+        const int prow = idx / (D / 4), c4 = idx - prow * (D / 4);
+        const int r = prow / G, gq = prow - r * G;
+        const int64_t e0 = base + (int64_t)r * p.q_heads + head * G + gq;
+        float mstar = -CUDART_INF_F;
+        for (int s = 0; s < n_splits; ++s) {
+          const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + e0 + (int64_t)s * stride);
+          if (ml.y > 0.f) mstar = fmaxf(mstar, ml.x);
+        }
+        float lsum = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) {
+          const int64_t entry = e0 + (int64_t)s * stride;
+          const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + entry);
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + entry * D) + c4);
+          const float wgt = ml.y > 0.f ? fast_exp2(ml.x - mstar) : 0.f;
+          lsum += wgt * ml.y;
+          acc.x += wgt * v.x;
+          acc.y += wgt * v.y;
+          acc.z += wgt * v.z;
+          acc.w += wgt * v.w;
+        }
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        const int64_t at = (int64_t)(first_row + r) * p.out_stride + (int64_t)(head * G + gq) * D + c4 * 4;
+        for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint2*>(p.out[dst] + at) = packed;
+      }
+    }
+  }
 }
 
 struct OutputList {
@@ -426,9 +479,9 @@ extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, con
                                         int64_t slots, const int32_t* table, int64_t table_stride,
                                         int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
                                         const int32_t* work, int64_t n_work, void* const* outs, int n_outs,
-                                        int64_t out_row_stride, float* part_ml, float* part_o, float scale,
-                                        float softcap, int window, int q_heads, int kv_heads, int head_dim,
-                                        int32_t* status, gk_stream_t stream) {
+                                        int64_t out_row_stride, float* part_ml, float* part_o,
+                                        int32_t* split_counters, float scale, float softcap, int window, int q_heads,
+                                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
   if (n_work == 0) return GK_OK;
   if (!outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS) return GK_ERR_INVALID_ARGUMENT;
   for (int i = 0; i < n_outs; ++i)
@@ -460,6 +513,7 @@ extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, con
   p.part_ml = part_ml;
   p.part_o = part_o;
   p.status = status;
+  p.counters = split_counters;
   p.q_stride = q_row_stride;
   p.out_stride = out_row_stride;
   p.slots = slots;
@@ -487,8 +541,8 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
                                   int q_heads, int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
   void* const outs[1] = {out};
   return gk_paged_attn_multi_bf16(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
-                                  page_tokens, table_rows, work, n_work, outs, 1, out_row_stride, part_ml, part_o, scale,
-                                  softcap, window, q_heads, kv_heads, head_dim, status, stream);
+                                  page_tokens, table_rows, work, n_work, outs, 1, out_row_stride, part_ml, part_o, nullptr,
+                                  scale, softcap, window, q_heads, kv_heads, head_dim, status, stream);
 }
 
 extern "C" int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o, const int32_t* combine,

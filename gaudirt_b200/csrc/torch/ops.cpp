@@ -54,6 +54,7 @@ struct AttentionPlan {
   at::Tensor buffer;      // int32 device words: work records, then combine records
   at::Tensor part_ml;     // fp32 split state (m, l) per partial entry
   at::Tensor part_o;      // fp32 split state O per partial entry
+  at::Tensor counters;    // int32 [rows * kv_heads] arrival counts of the fused combine (zero between launches)
   at::Tensor table;       // int32 slot table the work records index
   at::Tensor table_rows;  // optional int32 row indirection (device-resident request ids)
   void* address = nullptr;
@@ -314,6 +315,13 @@ class PagedMetadata : public torch::CustomClassHolder {
     const auto f32 = at::TensorOptions().dtype(at::kFloat).device(device);
     plan->part_ml = at::empty({std::max<int64_t>(entries, 1) * 2}, f32);
     plan->part_o = at::empty({std::max<int64_t>(entries, 1) * head_dim}, f32);
+    // Fused combine (the last split of a block to finish merges it inside the attention kernel) pays
+    // when only a few blocks are split: it saves a launch whose grid would be tiny.  With many split
+    // blocks the merges are better spread over the whole GPU by the separate combine kernel
+    // (measured: 2-5 % faster fused at 4-23 split blocks, 2-9 % slower at 64-256).
+    const bool fuse = fused_combine_ > 0 || (fused_combine_ < 0 && n_combine * 4 <= sm_count);
+    if (n_combine > 0 && fuse)
+      plan->counters = at::zeros({rows_ * kv_heads}, at::TensorOptions().dtype(at::kInt).device(device));
     plan->table = mapping_;
     plan->table_rows = batch_requests_;
     plan->table_stride = mapping_.stride(0);
@@ -358,7 +366,12 @@ class PagedMetadata : public torch::CustomClassHolder {
   }
 
   int64_t rows_ = 0, slots_ = 0, request_count_ = 0, context_ = 0, vocabulary_ = 0, page_tokens_ = 1;
-  int split_tokens_ = 0, prefill_min_rows_ = 0;
+  // -1: decide from the schedule, 0: separate combine kernel, 1: combine fused into attention.
+  void set_fused_combine(int64_t mode) {
+    TORCH_CHECK(mode >= -1 && mode <= 1, "GaudiRT attention: invalid combine mode");
+    fused_combine_ = static_cast<int>(mode);
+  }
+  int split_tokens_ = 0, prefill_min_rows_ = 0, fused_combine_ = -1;
   at::Tensor locations_, requests_, positions_, mapping_, header_, batch_requests_, token_ids_, last_token_indices_;
   std::vector<int32_t> sequences_;   // {first_row, n_rows, first_position, table_row} per sequence
   std::vector<std::pair<int64_t, at::Tensor>> plans_;
@@ -446,14 +459,16 @@ at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const
                                         plan.page_tokens,
                                         plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr, words,
                                         plan.n_work, outs.data(), (int)outs.size(), out_stride,
-                                        plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(), scale_f, softcap_f,
-                                        (int)sliding_window, (int)plan.query_heads, (int)plan.kv_heads, (int)head_dim,
-                                        status, s),
+                                        plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
+                                        plan.counters.defined() ? plan.counters.data_ptr<int32_t>() : nullptr, scale_f,
+                                        softcap_f, (int)sliding_window, (int)plan.query_heads, (int)plan.kv_heads,
+                                        (int)head_dim, status, s),
                "paged attention");
-  check_status(gk_paged_attn_combine_multi_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
-                                                words + plan.combine_offset, plan.n_combine, outs.data(), (int)outs.size(),
-                                                out_stride, (int)plan.query_heads, (int)head_dim, s),
-               "split-KV combine");
+  if (!plan.counters.defined())     // otherwise the combine ran inside: the last split to finish merged its block
+    check_status(gk_paged_attn_combine_multi_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
+                                                  words + plan.combine_offset, plan.n_combine, outs.data(),
+                                                  (int)outs.size(), out_stride, (int)plan.query_heads, (int)head_dim, s),
+                 "split-KV combine");
   if (plan.n_prefill > 0) {
     // Query tiles of multi-row sequences: tcgen05 kernel, one destination.  With several gather
     // destinations the rows are staged once and copied to each of them.
@@ -672,7 +687,8 @@ TORCH_LIBRARY(gaudirt, m) {
       .def("token_ids", &PagedMetadata::token_ids)
       .def("vocabulary", &PagedMetadata::vocabulary)
       .def("_set_split_tokens", &PagedMetadata::set_split_tokens)
-      .def("_set_prefill_min_rows", &PagedMetadata::set_prefill_min_rows);
+      .def("_set_prefill_min_rows", &PagedMetadata::set_prefill_min_rows)
+      .def("_set_fused_combine", &PagedMetadata::set_fused_combine);
   m.def("paged_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, float scale, "
         "float softcap=0.0, int sliding_window=-1) -> Tensor");

@@ -58,8 +58,9 @@ def kv_store(pool_layer, key, value, locations, status=None):
 
 
 def paged_attn(query, pool_layer, table, page_tokens, work, combine, entries, q_heads, scale,
-               softcap=0.0, window=-1, status=None, entry_stride=1, table_rows=None):
-    """Launch attention (+ combine) for a prepared schedule; returns the bf16 output tensor."""
+               softcap=0.0, window=-1, status=None, entry_stride=1, table_rows=None, fused_combine=False):
+    """Launch attention (+ combine) for a prepared schedule; returns the bf16 output tensor.  With
+    `fused_combine` the attention kernel merges the splits itself (no combine launch)."""
     _, kv_heads, slots, d = pool_layer.shape
     dev = query.device
     out = torch.empty((query.size(0), q_heads * d), dtype=torch.bfloat16, device=dev)
@@ -67,6 +68,19 @@ def paged_attn(query, pool_layer, table, page_tokens, work, combine, entries, q_
     part_ml = torch.empty(max(entries, 1) * 2, dtype=torch.float32, device=dev)
     part_o = torch.empty(max(entries, 1) * d, dtype=torch.float32, device=dev)
     lib = abi.lib()
+    if fused_combine:
+        counters = torch.zeros(query.size(0) * kv_heads, dtype=torch.int32, device=dev)
+        outs = (C.c_void_p * 1)(out.data_ptr())
+        st = lib.gk_paged_attn_multi_bf16(
+            query.data_ptr(), query.stride(0), pool_layer[0].data_ptr(), pool_layer[1].data_ptr(), slots,
+            table.data_ptr(), table.stride(0), entry_stride, page_tokens,
+            table_rows.data_ptr() if table_rows is not None else None, work_d.data_ptr(), work.shape[0], outs, 1,
+            out.stride(0), part_ml.data_ptr(), part_o.data_ptr(), counters.data_ptr(), scale, softcap, window, q_heads,
+            kv_heads, d, status.data_ptr() if status is not None else None, stream_ptr())
+        abi.check(st, "gk_paged_attn_multi_bf16")
+        torch.cuda.current_stream().synchronize()
+        assert int(counters.abs().sum()) == 0, "split counters must return to zero"
+        return out
     st = lib.gk_paged_attn_bf16(
         query.data_ptr(), query.stride(0), pool_layer[0].data_ptr(), pool_layer[1].data_ptr(), slots,
         table.data_ptr(), table.stride(0), entry_stride, page_tokens,

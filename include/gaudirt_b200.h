@@ -106,7 +106,8 @@ GK_API const char* gk_metadata_error(void);
  *   window    sliding window (-1 = none): keys below position-window+1 are never scheduled.
  *   split_tokens  0 = choose from sm_count; otherwise the longest KV range of one work item.
  *   work_out  [work_cap*GK_WORK_WORDS] {first_row, n_rows, first_position, table_row,
- *             kv_begin, kv_end, partial_base (-1 = writes the output itself), n_splits},
+ *             kv_begin, kv_end, partial_base (-1 = writes the output itself),
+ *             n_splits | split_index << 16},
  *             longest first.  combine_out [combine_cap*GK_COMBINE_WORDS] {first_row, n_rows,
  *             partial_base, n_splits} for every query block cut into more than one range.
  *   partial_entries_out  number of (row, query head) entries of fp32 split state needed.
@@ -188,16 +189,20 @@ GK_API int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, const v
  * column block r of the gathered [rows, world*cols] activation of EVERY rank, i.e. `outs[p]`
  * is (peer p's gathered buffer) + r*cols with out_row_stride = world*cols.  Peer buffers are
  * ordinary peer-mapped device memory (CUDA IPC / symmetric memory); the kernels only issue
- * plain stores to them.  The multi forms are otherwise identical to the single-output forms. */
+ * plain stores to them.  The multi forms are otherwise identical to the single-output forms,
+ * except for split_counters: when not NULL it is an int32 array [rows * kv_heads], all zero, and
+ * the attention kernel then also performs the combine -- the CTA that completes the last split of
+ * a query block merges all of the block's splits in split order (the result does not depend on
+ * which CTA that is) and leaves the counter at zero again; no combine launch is needed. */
 #define GK_MAX_OUTPUTS 8
 GK_API int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
                              const void* pool_v, int64_t slots, const int32_t* table,
                              int64_t table_stride, int64_t table_entry_stride, int page_tokens,
                              const int32_t* table_rows, const int32_t* work, int64_t n_work,
                              void* const* outs, int n_outs, int64_t out_row_stride,
-                             float* part_ml, float* part_o, float scale, float softcap,
-                             int window, int q_heads, int kv_heads, int head_dim,
-                             int32_t* status, gk_stream_t stream);
+                             float* part_ml, float* part_o, int32_t* split_counters,
+                             float scale, float softcap, int window, int q_heads, int kv_heads,
+                             int head_dim, int32_t* status, gk_stream_t stream);
 GK_API int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o,
                                      const int32_t* combine, int64_t n_combine,
                                      void* const* outs, int n_outs, int64_t out_row_stride,

@@ -70,9 +70,9 @@ def test_page_detection():
 def _coverage(work, combine, seq, q_heads, window):
     """Every (row, key) pair that must be attended is covered exactly once."""
     spans = {}
-    for first_row, n_rows, first_pos, table_row, lo, hi, base, splits in work:
+    for first_row, n_rows, first_pos, table_row, lo, hi, base, word in work:
         assert 0 < n_rows and lo < hi <= first_pos + n_rows
-        spans.setdefault((first_row, n_rows, first_pos, table_row), []).append((lo, hi, base, splits))
+        spans.setdefault((first_row, n_rows, first_pos, table_row), []).append((lo, hi, base, word & 0xffff, word >> 16))
     merged = {(r, n): (b, s) for r, n, b, s in combine}
     rows_seen = set()
     for (first_row, n_rows, first_pos, _), parts in spans.items():
@@ -87,6 +87,7 @@ def _coverage(work, combine, seq, q_heads, window):
             base, splits = merged[(first_row, n_rows)]
             assert splits == len(parts)
             assert [p[2] for p in parts] == [base + i * n_rows * q_heads for i in range(splits)]
+            assert [p[4] for p in parts] == list(range(splits)) and all(p[3] == splits for p in parts)
         for r in range(first_row, first_row + n_rows):
             assert r not in rows_seen
             rows_seen.add(r)

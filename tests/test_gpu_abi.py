@@ -77,7 +77,7 @@ def test_kv_store_skips_out_of_range_slots_and_reports():
 # ------------------------------------------------------------------------------------------
 # decode
 # ------------------------------------------------------------------------------------------
-def run_decode(case, page_tokens, split_tokens=0, softcap=0.0, window=-1):
+def run_decode(case, page_tokens, split_tokens=0, softcap=0.0, window=-1, fused_combine=False):
     pool = case.pool.to(DEV)
     H.kv_store(pool, case.k.to(DEV), case.v.to(DEV), case.locations.to(DEV))
     seq, detected = H.validate(case.locations, case.requests, case.positions, case.mapping, case.slots)
@@ -90,7 +90,7 @@ def run_decode(case, page_tokens, split_tokens=0, softcap=0.0, window=-1):
         table = (case.mapping[:, ::page_tokens]).contiguous().to(DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = H.paged_attn(case.q.to(DEV), pool, table, page_tokens, work, combine, entries, case.q_heads,
-                       case.scale, softcap, window, status)
+                       case.scale, softcap, window, status, fused_combine=fused_combine)
     assert int(status.item()) == 0
     return out, pool, len(combine)
 
@@ -127,6 +127,11 @@ def test_config1_split_kv_combine(split):
     oracle_gates(out, args)
     again, _, _ = run_decode(case, page_tokens=128, split_tokens=split)
     assert torch.equal(bits(out.cpu()), bits(again.cpu())), "split-KV combine must be deterministic"
+    # the combine fused into the attention kernel (last split to finish merges) gives the same bits
+    # as the separate combine kernel, run after run
+    for _ in range(3):
+        fused, _, _ = run_decode(case, page_tokens=128, split_tokens=split, fused_combine=True)
+        assert torch.equal(bits(out.cpu()), bits(fused.cpu()))
 
 
 @pytest.mark.parametrize("q_heads,kv_heads,d", [(8, 8, 64), (4, 2, 64), (9, 3, 64), (16, 8, 128), (56, 8, 128),
