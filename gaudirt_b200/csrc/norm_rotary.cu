@@ -2,25 +2,42 @@
 //
 // Both are HBM-bound elementwise/row kernels.  Every bf16 boundary of the reference (the updated
 // residual, the normalised output, each rotated element) is rounded ONCE from an exactly computed
-// value: the arithmetic between boundaries runs in fp64, and fp64 -> bf16 goes through a
-// round-to-odd fp32 so that no double rounding can occur.  That reproduces the reference's
-// binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35, tests/rotary_runtime_smoke.py:28-40)
-// bit for bit wherever fp64 itself is exact, at no cost: the kernels stay memory-bound.
+// value.  The norm's arithmetic between boundaries runs in fp64 with exact, integer-only
+// conversions from and to bf16; a rotation is evaluated in fp32 with directed roundings that
+// recover the exact result's rounding (round-to-odd), so no double rounding can occur.  That
+// reproduces the reference's binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35,
+// tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact.
 #include "gk_common.cuh"
 
 namespace gk {
 namespace {
 
-// Correctly rounded binary64 -> bf16 (nearest, ties to even).
+// Correctly rounded binary64 -> bf16 (nearest, ties to even) through a round-to-odd fp32.  (Integer
+// versions of these two conversions were measured slower than the hardware conversions.)
 __device__ __forceinline__ unsigned short bf16_from_double(double v) {
   float f = __double2float_rz(v);
-  if ((double)f != v) {                                       // inexact: force the sticky (odd) bit
-    f = __uint_as_float(__float_as_uint(f) | 1u);
-  }
+  if ((double)f != v) f = __uint_as_float(__float_as_uint(f) | 1u);      // inexact: sticky (odd) bit
   return __bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
 __device__ __forceinline__ double bf16_to_double(unsigned short b) {
   return (double)__uint_as_float((uint32_t)b << 16);
+}
+
+// bf16(x*c - y*s) resp. bf16(x*c + y*s), rounded once from the exact value, in fp32: the first
+// product of two bf16 values is exact, the fused multiply-add is evaluated toward zero and toward
+// +inf; if the two differ the result is inexact and the truncated one gets a sticky bit
+// (round-to-odd), which makes the final rounding to bf16 the rounding of the exact value.
+__device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned short c, unsigned short y,
+                                                      unsigned short s, bool subtract) {
+  const float xf = __uint_as_float((uint32_t)x << 16), cf = __uint_as_float((uint32_t)c << 16);
+  float yf = __uint_as_float((uint32_t)y << 16);
+  const float sf = __uint_as_float((uint32_t)s << 16);
+  if (subtract) yf = -yf;
+  const float first = xf * cf;                                  // exact
+  const float toward_zero = __fmaf_rz(yf, sf, first), upward = __fmaf_ru(yf, sf, first);
+  float r = toward_zero;
+  if (toward_zero != upward) r = __uint_as_float(__float_as_uint(toward_zero) | 1u);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(r));
 }
 
 __device__ __forceinline__ double block_sum(double v, double* shared) {
@@ -143,10 +160,8 @@ __device__ __forceinline__ unsigned short rotate_element(const unsigned short* h
     i = e >> 1;
     partner = e ^ 1;
   }
-  const double self = bf16_to_double(__ldg(head + e)), other = bf16_to_double(__ldg(head + partner));
-  const double c = bf16_to_double(__ldg(table + i)), s = bf16_to_double(__ldg(table + half + i));
   // first of a pair: a*cos - b*sin ; second: b*cos + a*sin   (self is a resp. b)
-  return bf16_from_double(first ? self * c - other * s : self * c + other * s);
+  return rotate_pair(__ldg(head + e), __ldg(table + i), __ldg(head + partner), __ldg(table + half + i), first);
 }
 
 // One thread per element of q, k (and v when the store is fused).
@@ -196,7 +211,103 @@ __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
   }
 }
 
+// Vector form: one thread per 16-byte chunk (8 elements) of q, k (and v when the store is fused).
+// Needs 16-byte aligned rows, head_dim % 8 == 0 and whole chunks on each side of a rotation
+// (rotary_dim % 16 == 0 for neox pairs, % 8 == 0 for interleaved pairs).
+template <bool STORE>
+__global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
+  const int chunks = p.head_dim >> 3;
+  const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
+  const int per_row = heads * chunks;
+  const int64_t total = p.rows * (int64_t)per_row;
+  const int half = p.rotary_dim >> 1;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = idx / per_row;
+    const int rem = (int)(idx - row * per_row);
+    const int head = rem / chunks, ch = rem - head * chunks;
+    const int kh = head - p.q_heads;
+    if (STORE && kh >= p.k_heads) {                              // V: straight to its slot
+      const int vh = kh - p.k_heads;
+      const int slot = __ldg(p.locations + row);
+      if ((unsigned)slot < (unsigned)p.slots)
+        *reinterpret_cast<uint4*>(p.pool_v + ((int64_t)vh * p.slots + slot) * p.head_dim + ch * 8) =
+            __ldg(reinterpret_cast<const uint4*>(p.v + row * p.v_stride + (int64_t)vh * p.head_dim + ch * 8));
+      continue;
+    }
+    int pos = __ldg(p.positions + row);
+    int rotary_dim = p.rotary_dim;
+    if ((unsigned)pos >= (unsigned)p.cache_rows) {                // position outside the table: pass through, report
+      if (p.status && rem == 0) atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+      pos = 0;
+      rotary_dim = 0;
+    }
+    const unsigned short* table = p.cache + (int64_t)pos * p.rotary_dim;
+    const bool is_q = head < p.q_heads;
+    const unsigned short* src = is_q ? p.q + row * p.q_stride + (int64_t)head * p.head_dim
+                                     : p.k + row * p.k_stride + (int64_t)kh * p.head_dim;
+    uint4 self4 = __ldg(reinterpret_cast<const uint4*>(src + ch * 8));
+    const unsigned short* self = reinterpret_cast<const unsigned short*>(&self4);
+    unsigned short out[8];
+    if (ch * 8 >= rotary_dim) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) out[e] = self[e];
+    } else if (p.is_neox) {
+      const bool first = ch * 8 < half;
+      const int i0 = first ? ch * 8 : ch * 8 - half;
+      uint4 other4 = __ldg(reinterpret_cast<const uint4*>(src + (first ? ch * 8 + half : ch * 8 - half)));
+      uint4 cos4 = __ldg(reinterpret_cast<const uint4*>(table + i0)), sin4 = __ldg(reinterpret_cast<const uint4*>(table + half + i0));
+      const unsigned short* other = reinterpret_cast<const unsigned short*>(&other4);
+      const unsigned short* c = reinterpret_cast<const unsigned short*>(&cos4);
+      const unsigned short* sn = reinterpret_cast<const unsigned short*>(&sin4);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) out[e] = rotate_pair(self[e], c[e], other[e], sn[e], first);
+    } else {
+      uint2 cos2 = __ldg(reinterpret_cast<const uint2*>(table + ch * 4)), sin2 = __ldg(reinterpret_cast<const uint2*>(table + half + ch * 4));
+      const unsigned short* c = reinterpret_cast<const unsigned short*>(&cos2);
+      const unsigned short* sn = reinterpret_cast<const unsigned short*>(&sin2);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        out[2 * k] = rotate_pair(self[2 * k], c[k], self[2 * k + 1], sn[k], true);
+        out[2 * k + 1] = rotate_pair(self[2 * k + 1], c[k], self[2 * k], sn[k], false);
+      }
+    }
+    const uint4 packed = *reinterpret_cast<const uint4*>(out);
+    if (is_q) {
+      *reinterpret_cast<uint4*>(p.q_out + row * (int64_t)p.q_heads * p.head_dim + (int64_t)head * p.head_dim + ch * 8) = packed;
+    } else {
+      if (p.k_out) *reinterpret_cast<uint4*>(p.k_out + row * (int64_t)p.k_heads * p.head_dim + (int64_t)kh * p.head_dim + ch * 8) = packed;
+      if (STORE) {
+        const int slot = __ldg(p.locations + row);
+        if ((unsigned)slot < (unsigned)p.slots) {
+          *reinterpret_cast<uint4*>(p.pool_k + ((int64_t)kh * p.slots + slot) * p.head_dim + ch * 8) = packed;
+        } else if (p.status && ch == 0 && kh == 0) {
+          atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+        }
+      }
+    }
+  }
+}
+
+bool rotary_vectorisable(const RotaryParams& p, bool store) {
+  uintptr_t bits = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.cache) |
+                   reinterpret_cast<uintptr_t>(p.q_out) | reinterpret_cast<uintptr_t>(p.k_out);
+  if (store) bits |= reinterpret_cast<uintptr_t>(p.v) | reinterpret_cast<uintptr_t>(p.pool_k) | reinterpret_cast<uintptr_t>(p.pool_v);
+  const int64_t strides = p.q_stride | p.k_stride | (store ? p.v_stride : 0);
+  return !(bits & 15) && !(strides & 7) && p.head_dim % 8 == 0 && p.rotary_dim % (p.is_neox ? 16 : 8) == 0;
+}
+
 int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
+  if (rotary_vectorisable(p, store)) {
+    const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
+    const int64_t total = p.rows * heads * (p.head_dim / 8);
+    const int64_t want = (total + 255) / 256;
+    const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    if (store)
+      rotary_vec_kernel<true><<<blocks, 256, 0, stream>>>(p);
+    else
+      rotary_vec_kernel<false><<<blocks, 256, 0, stream>>>(p);
+    return check_launch();
+  }
   const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
   const int64_t total = p.rows * heads * p.head_dim;
   const int64_t want = (total + 255) / 256;
