@@ -5,8 +5,9 @@ makes them) and exposes the reference's Python-visible names for this path:
 
 * ``torch.ops.gaudirt.paged_attn`` / ``_paged_attn_validated`` and
   ``torch.classes.gaudirt.PagedMetadata`` (reference: ``src/bridge/generic_private_use1.cpp:430-489``);
-* ``gaudirt_b200._C._allocate_paged_kv`` / ``_C._paged_attn_kv_tile`` (reference: the ``gaudirt._C``
-  bindings of the same names);
+* ``gaudirt_b200._C._allocate_paged_kv`` / ``_C._paged_attn_kv_tile`` / ``_C._allocate_paged_slots`` /
+  ``_C._release_paged_slots`` (reference: the ``gaudirt._C`` bindings of the same names) and
+  ``torch.ops.gaudirt._advance_decode_lengths``;
 * fake-tensor registrations with the reference's shape contracts (``python/gaudirt/__init__.py:136-153``).
 
 There is no CPU or pure-PyTorch fallback: a missing library is an import error.
@@ -20,7 +21,7 @@ import torch
 
 from . import abi, build
 
-__all__ = ["abi", "build", "_C", "PagedMetadata", "synchronize"]
+__all__ = ["abi", "build", "_C", "PagedMetadata", "synchronize", "validated_last_token_indices"]
 
 if not os.path.exists(build.OPS_SO):
     raise ImportError(f"{build.OPS_SO} is missing: run `python gaudirt_b200/build.py` (needs nvcc and g++)")
@@ -34,7 +35,23 @@ _C = types.SimpleNamespace(
         layers, slots, heads, head_dim),
     _paged_attn_kv_tile=lambda rows: int(torch.ops.gaudirt._paged_attn_kv_tile(rows)),
     _take_device_status=lambda: int(torch.ops.gaudirt._take_device_status()),
+    _allocate_paged_slots=lambda last_slots, free_pages, prefixes, lengths, page_size:
+        torch.ops.gaudirt._allocate_paged_slots(last_slots, free_pages, prefixes, lengths, page_size),
+    _allocate_paged_slots_into=lambda last_slots, free_pages, prefixes, lengths, page_size, mapping, batch_requests:
+        torch.ops.gaudirt._allocate_paged_slots_into(last_slots, free_pages, prefixes, lengths, page_size, mapping,
+                                                     batch_requests),
+    _release_paged_slots=lambda slots, page_size, max_pages:
+        torch.ops.gaudirt._release_paged_slots(slots, page_size, max_pages),
 )
+
+
+def validated_last_token_indices(metadata) -> torch.Tensor:
+    """Row index of the last token of every sequence of a device-validated batch (int32), tagged with
+    the row count it was validated for (reference: ``python/gaudirt/__init__.py``, used by
+    ``tests/paged_device_metadata_smoke.py:85-89``)."""
+    indices = metadata.last_token_indices()
+    indices._gaudirt_validated_rows = metadata.rows()
+    return indices
 
 
 def synchronize() -> None:

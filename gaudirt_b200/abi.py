@@ -38,6 +38,14 @@ PROTOTYPES = {
     "gk_rotary_bf16": (i32, [vp, vp, i64, i64, vp, i64, vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]),
     "gk_rotary_kv_store_bf16": (i32, [vp, vp, vp, i64, i64, i64, vp, i64, vp, vp, i64, i64, i64, i32, i32, i32,
                                       vp, vp, vp, vp, i64, vp, vp]),
+    "gk_paged_slots_layout": (i32, [vp, vp, i64, i64, i64, vp, i64p, i64p]),
+    "gk_paged_slots_allocate": (i32, [vp, vp, vp, i64, i64, i64, vp, vp, i64, i64, i64, vp, vp, vp, vp]),
+    "gk_paged_slots_release_workspace_bytes": (i32, [i64, i64, C.POINTER(C.c_uint64)]),
+    "gk_paged_slots_release": (i32, [vp, i64, i64, i64, vp, vp, vp, vp]),
+    "gk_advance_decode_lengths": (i32, [vp, vp, i64, vp, vp, vp]),
+    "gk_paged_metadata_device_workspace_bytes": (i32, [i64, C.POINTER(C.c_uint64)]),
+    "gk_paged_metadata_device_validate": (i32, [vp, vp, vp, vp, i32, i64, vp, i64, i64, i64, i64, vp, i64, i64, vp,
+                                                vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
     "gk_paged_attn_static_scratch_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, i64,
                                                 vp, i64, f32, f32, i32, i32, i32, i32, vp, vp]),
 }

@@ -118,6 +118,36 @@ extern "C" int gk_paged_metadata_validate(const int32_t* locations, const int32_
   return GK_OK;
 }
 
+// Host half of slot allocation (src/bridge/paged_slot_allocator.cpp:95-128): the argument checks
+// and one {prefix, length, first token, first fresh page} record per request.
+extern "C" int gk_paged_slots_layout(const int64_t* prefixes, const int64_t* lengths, int64_t n_requests,
+                                     int64_t page_size, int64_t free_page_count, int32_t* records_out,
+                                     int64_t* total_out, int64_t* pages_out) {
+  if (!prefixes || !lengths || !total_out || !pages_out) return GK_ERR_INVALID_ARGUMENT;
+  if (page_size < 1 || page_size > INT32_MAX || n_requests <= 0 || n_requests > (int64_t{1} << 30))
+    return metadata_fail("GaudiRT paged allocator: unsupported page size or request count");
+  int64_t total = 0, pages = 0;
+  for (int64_t i = 0; i < n_requests; ++i) {
+    const int64_t prefix = prefixes[i], length = lengths[i];
+    if (prefix < 0 || length < 0 || prefix > INT32_MAX || length > INT32_MAX || prefix + length > INT32_MAX)
+      return metadata_fail("GaudiRT paged allocator: invalid request lengths");
+    if (records_out && total <= INT32_MAX && pages <= INT32_MAX) {
+      int32_t* r = records_out + i * 4;
+      r[0] = (int32_t)prefix;
+      r[1] = (int32_t)length;
+      r[2] = (int32_t)total;
+      r[3] = (int32_t)pages;
+    }
+    total += length;
+    pages += (prefix + length + page_size - 1) / page_size - (prefix + page_size - 1) / page_size;
+  }
+  if (total <= 0 || total > (int64_t{1} << 30) || pages > (int64_t{1} << 30) || pages > free_page_count)
+    return metadata_fail("GaudiRT paged allocator: invalid token count or insufficient free pages");
+  *total_out = total;
+  *pages_out = pages;
+  return GK_OK;
+}
+
 extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_heads, int kv_heads, int head_dim,
                                        int window, int sm_count, int split_tokens, int32_t* work_out,
                                        int64_t work_cap, int64_t* n_work_out, int32_t* combine_out,

@@ -45,6 +45,9 @@ at::Tensor& device_status(c10::DeviceIndex device) {
   return words[device];
 }
 
+// Clears `bits` of the device status word, in stream order: for errors that were raised on the host.
+void clear_status_bits(c10::DeviceIndex device, int bits) { device_status(device).bitwise_and_(~bits); }
+
 // ---------------------------------------------------------------------------------------------
 // attention plan carried by its device tensor (as in src/bridge/attention_plan.cpp:132-140,
 // 319-322: the tensor's storage context owns the host-side schedule, so the tensor's lifetime
@@ -154,54 +157,102 @@ class PagedMetadata : public torch::CustomClassHolder {
     header_ = all.narrow(0, words - 1, 1);
   }
 
-  // Device-input constructor (src/bridge/paged_metadata.cpp:176-324): `batch_requests[batch]`
+  // Device-input constructor (src/bridge/paged_metadata.cpp:176-430): `batch_requests[batch]`
   // indexes a persistent device table `mapping[max_requests, max_context]`; `prefixes` and
-  // `lengths` are the host lists of cached length and new-token count per sequence.
+  // `lengths` are the host lists of cached length and new-token count per sequence.  The index
+  // vectors never visit the host: one validation pass on the device narrows them to int32,
+  // expands request ids to rows and checks every row and visible table entry.  With
+  // `scheduler_owned` the table is vouched for by the scheduler (not re-checked) and a rejection
+  // only sets GK_DEV_BAD_METADATA in the device status word, so nothing synchronises; otherwise
+  // the 16-byte verdict is read back and a rejection raises here.
   PagedMetadata(const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
                 const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
-                const at::Tensor& token_ids, int64_t vocabulary) {
-    for (const auto& t : {locations, batch_requests, positions, mapping})
-      TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong),
-                  "GaudiRT: device paged metadata must be contiguous CUDA int32 or int64");
-    TORCH_CHECK(locations.dim() == 1 && batch_requests.dim() == 1 && positions.dim() == 1 && mapping.dim() == 2 &&
-                    locations.size(0) == positions.size(0) && !prefixes.empty() && prefixes.size() == lengths.size() &&
-                    batch_requests.size(0) == static_cast<int64_t>(prefixes.size()),
-                "GaudiRT: invalid paged metadata ranks or row counts");
-    TORCH_CHECK(slots > 0 && slots <= INT32_MAX && mapping.numel() <= INT32_MAX && mapping.numel() > 0,
-                "GaudiRT: paged metadata dimensions outside supported range");
-    int64_t row = 0;
-    for (size_t i = 0; i < prefixes.size(); ++i) {
-      TORCH_CHECK(prefixes[i] >= 0 && lengths[i] > 0 && prefixes[i] + lengths[i] <= mapping.size(1),
-                  "GaudiRT: paged metadata index is out of range");
-      sequences_.insert(sequences_.end(), {static_cast<int32_t>(row), static_cast<int32_t>(lengths[i]),
-                                           static_cast<int32_t>(prefixes[i]), static_cast<int32_t>(i)});
-      row += lengths[i];
+                const at::Tensor& token_ids, int64_t vocabulary, bool scheduler_owned) {
+    for (const auto& t : {locations, batch_requests, positions})
+      TORCH_CHECK(t.is_cuda() && t.dim() == 1 && (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong),
+                  "GaudiRT device metadata: expected CUDA int32 or int64 vectors");
+    TORCH_CHECK(mapping.is_cuda() && mapping.scalar_type() == at::kInt && mapping.dim() == 2 && mapping.is_contiguous(),
+                "GaudiRT device metadata: expected a contiguous CUDA int32 request map");
+    const bool has_tokens = token_ids.defined() && token_ids.numel() > 0;
+    const int64_t m = locations.numel(), batch = batch_requests.numel();
+    TORCH_CHECK((has_tokens && token_ids.is_cuda() && token_ids.dim() == 1 && token_ids.numel() == m &&
+                 (token_ids.scalar_type() == at::kInt || token_ids.scalar_type() == at::kLong) && vocabulary > 0 &&
+                 vocabulary <= INT32_MAX) || (!has_tokens && vocabulary == 0),
+                "GaudiRT device metadata: invalid token IDs or vocabulary size");
+    TORCH_CHECK(m > 0 && m <= INT32_MAX && positions.numel() == m && batch > 0 && batch <= m &&
+                    static_cast<int64_t>(prefixes.size()) == batch && static_cast<int64_t>(lengths.size()) == batch &&
+                    slots > 0 && slots <= INT32_MAX && mapping.numel() > 0 && mapping.numel() <= INT32_MAX,
+                "GaudiRT device metadata: dimensions outside supported range");
+    const int64_t context = mapping.size(1);
+    const auto device = locations.device();
+    c10::cuda::CUDAGuard guard(device);
+    // Per-sequence records and last-row indices are host knowledge: one pinned buffer, one copy.
+    auto staging = at::empty({batch * 4}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+    int32_t* records = staging.data_ptr<int32_t>();
+    int64_t cursor = 0;
+    for (int64_t i = 0; i < batch; ++i) {
+      const int64_t prefix = prefixes[i], length = lengths[i];
+      TORCH_CHECK(prefix >= 0 && prefix < context && length > 0 && length <= context - prefix && length <= m - cursor,
+                  "GaudiRT device metadata: invalid sequence lengths");
+      const int32_t record[4] = {static_cast<int32_t>(cursor), static_cast<int32_t>(length),
+                                 static_cast<int32_t>(prefix), static_cast<int32_t>(i)};
+      std::memcpy(records + 4 * i, record, sizeof(record));
+      sequences_.insert(sequences_.end(), record, record + 4);
+      cursor += length;
     }
-    TORCH_CHECK(row == locations.size(0), "GaudiRT: invalid paged metadata ranks or row counts");
-    rows_ = row;
+    TORCH_CHECK(cursor == m, "GaudiRT device metadata: sequence lengths do not cover token rows");
+    rows_ = m;
     slots_ = slots;
     request_count_ = mapping.size(0);
-    context_ = mapping.size(1);
-    locations_ = locations.to(at::kInt);
-    positions_ = positions.to(at::kInt);
-    mapping_ = mapping.to(at::kInt);
-    batch_requests_ = batch_requests.to(at::kInt);
-    if (static_cast<int64_t>(prefixes.size()) == rows_) {
-      requests_ = batch_requests_;
-    } else {
-      auto repeats = at::tensor(lengths, at::TensorOptions().dtype(at::kLong)).to(locations.device(), true);
-      requests_ = at::repeat_interleave(batch_requests_, repeats, 0, rows_);
-    }
-    header_ = at::full({1}, rows_, locations_.options());
-    if (token_ids.defined() && token_ids.numel()) {
-      TORCH_CHECK(token_ids.is_cuda() && token_ids.dim() == 1 && token_ids.size(0) == rows_ && vocabulary > 0,
-                  "GaudiRT: invalid token metadata");
-      token_ids_ = token_ids.to(at::kInt);
+    context_ = context;
+    mapping_ = mapping;
+    const auto i32 = at::TensorOptions().dtype(at::kInt).device(device);
+    auto seq_device = staging.to(device, /*non_blocking=*/true);
+    // Strided views (a column of a scheduler's packed buffer) are packed first, like the
+    // reference's staged copy (src/bridge/paged_metadata.cpp:362-381).
+    const at::Tensor loc = locations.contiguous(), req = batch_requests.contiguous(), pos = positions.contiguous();
+    const at::Tensor tok = has_tokens ? token_ids.contiguous() : at::Tensor();
+    // locations | requests | positions | tokens | row status | token status | last rows | batch ids
+    const int64_t lanes = 4 + (has_tokens ? 2 : 0);
+    auto out = at::empty({lanes * m + 2 * batch}, i32);
+    locations_ = out.narrow(0, 0, m);
+    requests_ = out.narrow(0, m, m);
+    positions_ = out.narrow(0, 2 * m, m);
+    auto row_status = out.narrow(0, 3 * m, m);
+    at::Tensor token_status;
+    if (has_tokens) {
+      token_ids_ = out.narrow(0, 4 * m, m);
+      token_status = out.narrow(0, 5 * m, m);
       vocabulary_ = vocabulary;
-      std::vector<int64_t> last;
-      int64_t end = 0;
-      for (auto n : lengths) last.push_back((end += n) - 1);
-      last_token_indices_ = at::tensor(last, at::TensorOptions().dtype(at::kInt)).to(locations.device(), true);
+    }
+    last_token_indices_ = out.narrow(0, lanes * m, batch);
+    batch_requests_ = req.scalar_type() == at::kInt ? req : req.to(at::kInt);
+    header_ = at::full({1}, rows_, i32);
+    uint64_t workspace_bytes = 0;
+    check_status(gk_paged_metadata_device_workspace_bytes(slots, &workspace_bytes), "device metadata");
+    auto workspace = at::empty({static_cast<int64_t>(workspace_bytes)}, at::TensorOptions().dtype(at::kByte).device(device));
+    auto verdict = at::empty({2}, at::TensorOptions().dtype(at::kLong).device(device));
+    const int wide = (loc.scalar_type() == at::kLong ? 1 : 0) | (req.scalar_type() == at::kLong ? 2 : 0) |
+                     (pos.scalar_type() == at::kLong ? 4 : 0) | (has_tokens && tok.scalar_type() == at::kLong ? 8 : 0);
+    const auto stream = at::cuda::getCurrentCUDAStream(device.index());
+    check_status(gk_paged_metadata_device_validate(
+                     loc.data_ptr(), req.data_ptr(), pos.data_ptr(), has_tokens ? tok.data_ptr() : nullptr, wide,
+                     vocabulary, scheduler_owned ? nullptr : mapping.data_ptr<int32_t>(), mapping.size(0), context,
+                     mapping.stride(0), slots, seq_device.data_ptr<int32_t>(), batch, m, workspace.data_ptr(),
+                     locations_.data_ptr<int32_t>(), requests_.data_ptr<int32_t>(), positions_.data_ptr<int32_t>(),
+                     has_tokens ? token_ids_.data_ptr<int32_t>() : nullptr, last_token_indices_.data_ptr<int32_t>(),
+                     row_status.data_ptr<int32_t>(), has_tokens ? token_status.data_ptr<int32_t>() : nullptr,
+                     reinterpret_cast<uint64_t*>(verdict.data_ptr<int64_t>()),
+                     device_status(device.index()).data_ptr<int32_t>(), stream_of(stream)),
+                 "device metadata");
+    if (!scheduler_owned) {
+      const auto host = verdict.cpu();   // 16 bytes: the only read-back of the step
+      const uint64_t first = static_cast<uint64_t>(host.data_ptr<int64_t>()[0]);
+      const uint64_t token = static_cast<uint64_t>(host.data_ptr<int64_t>()[1]);
+      if (first != UINT64_MAX || token != UINT64_MAX) clear_status_bits(device.index(), GK_DEV_BAD_METADATA);
+      TORCH_CHECK(first == UINT64_MAX, "GaudiRT device metadata: invalid scheduler metadata at row ", first >> 8,
+                  ", code ", first & 255);
+      TORCH_CHECK(token == UINT64_MAX, "GaudiRT device metadata: token ID outside vocabulary at row ", token);
     }
   }
 
@@ -210,14 +261,14 @@ class PagedMetadata : public torch::CustomClassHolder {
                                                        std::vector<int64_t> prefixes, std::vector<int64_t> lengths,
                                                        int64_t slots) {
     return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
-                                              std::move(lengths), slots, at::Tensor(), 0);
+                                              std::move(lengths), slots, at::Tensor(), 0, false);
   }
   static c10::intrusive_ptr<PagedMetadata> from_device_with_tokens(
       const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
       const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
       const at::Tensor& token_ids, int64_t vocabulary) {
     return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
-                                              std::move(lengths), slots, token_ids, vocabulary);
+                                              std::move(lengths), slots, token_ids, vocabulary, false);
   }
   static c10::intrusive_ptr<PagedMetadata> from_scheduler(const at::Tensor& locations, const at::Tensor& batch_requests,
                                                           const at::Tensor& positions, const at::Tensor& mapping,
@@ -225,7 +276,8 @@ class PagedMetadata : public torch::CustomClassHolder {
                                                           int64_t slots, const c10::optional<at::Tensor>& token_ids,
                                                           int64_t vocabulary) {
     return c10::make_intrusive<PagedMetadata>(locations, batch_requests, positions, mapping, std::move(prefixes),
-                                              std::move(lengths), slots, token_ids.value_or(at::Tensor()), vocabulary);
+                                              std::move(lengths), slots, token_ids.value_or(at::Tensor()), vocabulary,
+                                              true);
   }
   static c10::intrusive_ptr<PagedMetadata> from_scheduler_fused(
       const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
@@ -652,6 +704,122 @@ std::tuple<at::Tensor, at::Tensor> rotary_embedding_positions(const at::Tensor& 
                                     cache.dim() == 2 ? cache.size(0) : 0, head_dim, rotary_dim, is_neox);
 }
 
+// ---------------------------------------------------------------------------------------------
+// slot allocator and decode-length update (src/bridge/paged_slot_allocator.cpp,
+// src/bridge/eager_scheduler.cpp)
+// ---------------------------------------------------------------------------------------------
+void require_indices(const at::Tensor& tensor) {
+  TORCH_CHECK(tensor.is_cuda() && tensor.scalar_type() == at::kLong && tensor.dim() == 1 && tensor.is_contiguous(),
+              "GaudiRT paged allocator: expected contiguous device int64 indices");
+}
+
+std::tuple<at::Tensor, int64_t> allocate_paged_slots(const at::Tensor& last_slots, const at::Tensor& free_pages,
+                                                     std::vector<int64_t> prefixes, std::vector<int64_t> lengths,
+                                                     int64_t page_size) {
+  require_indices(last_slots);
+  require_indices(free_pages);
+  TORCH_CHECK(!prefixes.empty() && prefixes.size() == lengths.size() &&
+                  last_slots.numel() == static_cast<int64_t>(prefixes.size()) && last_slots.device() == free_pages.device(),
+              "GaudiRT paged allocator: unsupported page size or request count");
+  const int64_t n = static_cast<int64_t>(prefixes.size());
+  const auto device = last_slots.device();
+  c10::cuda::CUDAGuard guard(device);
+  auto staging = at::empty({n * 4}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+  int64_t total = 0, pages = 0;
+  check_status(gk_paged_slots_layout(prefixes.data(), lengths.data(), n, page_size, free_pages.numel(),
+                                     staging.data_ptr<int32_t>(), &total, &pages),
+               "paged allocator");
+  auto records = staging.to(device, /*non_blocking=*/true);
+  auto result = at::empty({total}, last_slots.options());
+  const auto stream = at::cuda::getCurrentCUDAStream(device.index());
+  check_status(gk_paged_slots_allocate(last_slots.data_ptr<int64_t>(), free_pages.data_ptr<int64_t>(),
+                                       records.data_ptr<int32_t>(), n, total, page_size, result.data_ptr<int64_t>(),
+                                       nullptr, 0, 0, 0, nullptr, nullptr, nullptr, stream_of(stream)),
+               "paged allocator");
+  return {result, pages};
+}
+
+// Allocation fused with the two scatters a scheduler does next: the int32 slot list for the KV
+// store and the request-to-token table rows the attention kernel walks.  Not part of the
+// reference surface.
+std::tuple<at::Tensor, at::Tensor, int64_t> allocate_paged_slots_into(
+    const at::Tensor& last_slots, const at::Tensor& free_pages, std::vector<int64_t> prefixes,
+    std::vector<int64_t> lengths, int64_t page_size, at::Tensor& mapping, const at::Tensor& batch_requests) {
+  require_indices(last_slots);
+  require_indices(free_pages);
+  TORCH_CHECK(!prefixes.empty() && prefixes.size() == lengths.size() &&
+                  last_slots.numel() == static_cast<int64_t>(prefixes.size()) && last_slots.device() == free_pages.device(),
+              "GaudiRT paged allocator: unsupported page size or request count");
+  const int64_t n = static_cast<int64_t>(prefixes.size());
+  const auto device = last_slots.device();
+  TORCH_CHECK(mapping.is_cuda() && mapping.device() == device && mapping.scalar_type() == at::kInt && mapping.dim() == 2 &&
+                  mapping.stride(1) == 1 && batch_requests.is_cuda() && batch_requests.device() == device &&
+                  batch_requests.scalar_type() == at::kInt && batch_requests.dim() == 1 && batch_requests.numel() == n &&
+                  batch_requests.is_contiguous(),
+              "GaudiRT paged allocator: expected an int32 request map and int32 request ids on the same device");
+  for (int64_t i = 0; i < n; ++i)
+    TORCH_CHECK(prefixes[i] >= 0 && lengths[i] >= 0 && prefixes[i] + lengths[i] <= mapping.size(1),
+                "GaudiRT paged allocator: invalid request lengths");
+  c10::cuda::CUDAGuard guard(device);
+  auto staging = at::empty({n * 4}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+  int64_t total = 0, pages = 0;
+  check_status(gk_paged_slots_layout(prefixes.data(), lengths.data(), n, page_size, free_pages.numel(),
+                                     staging.data_ptr<int32_t>(), &total, &pages),
+               "paged allocator");
+  auto records = staging.to(device, /*non_blocking=*/true);
+  auto result = at::empty({total}, last_slots.options());
+  auto locations = at::empty({total}, batch_requests.options());
+  const auto stream = at::cuda::getCurrentCUDAStream(device.index());
+  check_status(gk_paged_slots_allocate(last_slots.data_ptr<int64_t>(), free_pages.data_ptr<int64_t>(),
+                                       records.data_ptr<int32_t>(), n, total, page_size, result.data_ptr<int64_t>(),
+                                       mapping.data_ptr<int32_t>(), mapping.size(0), mapping.stride(0), mapping.size(1),
+                                       batch_requests.data_ptr<int32_t>(), locations.data_ptr<int32_t>(),
+                                       device_status(device.index()).data_ptr<int32_t>(), stream_of(stream)),
+               "paged allocator");
+  return {result, locations, pages};
+}
+
+at::Tensor release_paged_slots(const at::Tensor& slots, int64_t page_size, int64_t max_pages) {
+  require_indices(slots);
+  TORCH_CHECK(page_size >= 1 && page_size <= INT32_MAX && max_pages > 0 && max_pages <= INT32_MAX && slots.numel() > 0 &&
+                  slots.numel() <= (int64_t{1} << 30),
+              "GaudiRT paged allocator: invalid release geometry");
+  const auto device = slots.device();
+  c10::cuda::CUDAGuard guard(device);
+  uint64_t bytes = 0;
+  check_status(gk_paged_slots_release_workspace_bytes(slots.numel(), max_pages, &bytes), "paged allocator");
+  auto workspace = at::empty({static_cast<int64_t>(bytes)}, at::TensorOptions().dtype(at::kByte).device(device));
+  auto result = at::empty_like(slots);
+  auto count = at::empty({2}, at::TensorOptions().dtype(at::kInt).device(device));
+  const auto stream = at::cuda::getCurrentCUDAStream(device.index());
+  check_status(gk_paged_slots_release(slots.data_ptr<int64_t>(), slots.numel(), page_size, max_pages,
+                                      workspace.data_ptr(), result.data_ptr<int64_t>(), count.data_ptr<int32_t>(),
+                                      stream_of(stream)),
+               "paged allocator");
+  const auto host = count.cpu();   // the result's length is data dependent: one 8-byte read-back
+  const int32_t released = host.data_ptr<int32_t>()[0], outside = host.data_ptr<int32_t>()[1];
+  TORCH_CHECK(outside == 0 && released > 0 && released <= slots.numel(),
+              "GaudiRT paged allocator: released slot is outside the KV pool");
+  return result.narrow(0, 0, released);
+}
+
+std::tuple<at::Tensor, at::Tensor> advance_decode_lengths(const at::Tensor& seq_lens, const at::Tensor& orig_seq_lens) {
+  TORCH_CHECK(seq_lens.is_cuda() && orig_seq_lens.device() == seq_lens.device() && seq_lens.scalar_type() == at::kLong &&
+                  orig_seq_lens.scalar_type() == at::kInt && seq_lens.dim() == 1 &&
+                  orig_seq_lens.sizes() == seq_lens.sizes() && seq_lens.numel() <= (int64_t{1} << 30) &&
+                  seq_lens.is_contiguous() && orig_seq_lens.is_contiguous(),
+              "GaudiRT decode lengths: expected matching contiguous int64 and int32 vectors");
+  auto next = at::empty_like(seq_lens), orig_next = at::empty_like(orig_seq_lens);
+  if (!seq_lens.numel()) return {next, orig_next};
+  c10::cuda::CUDAGuard guard(seq_lens.device());
+  const auto stream = at::cuda::getCurrentCUDAStream(seq_lens.device().index());
+  check_status(gk_advance_decode_lengths(seq_lens.data_ptr<int64_t>(), orig_seq_lens.data_ptr<int32_t>(),
+                                         seq_lens.numel(), next.data_ptr<int64_t>(), orig_next.data_ptr<int32_t>(),
+                                         stream_of(stream)),
+               "decode lengths");
+  return {next, orig_next};
+}
+
 // Reads and clears the device status word of the current device (synchronises the stream).
 int64_t take_device_status() {
   auto& word = device_status(at::cuda::current_device());
@@ -711,6 +879,10 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_allocate_paged_kv(int layers, int slots, int heads, int head_dim) -> Tensor", &gaudirt_b200::allocate_paged_kv);
   m.def("_paged_attn_kv_tile(int rows) -> int", &gaudirt_b200::paged_attn_kv_tile);
   m.def("_take_device_status() -> int", &gaudirt_b200::take_device_status);
+  m.def("_allocate_paged_slots", &gaudirt_b200::allocate_paged_slots);
+  m.def("_allocate_paged_slots_into", &gaudirt_b200::allocate_paged_slots_into);
+  m.def("_release_paged_slots", &gaudirt_b200::release_paged_slots);
+  m.def("_advance_decode_lengths(Tensor seq_lens, Tensor orig_seq_lens) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
@@ -723,4 +895,5 @@ TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("rotary_embedding", TORCH_FN(gaudirt_b200::rotary_embedding));
   m.impl("rotary_embedding_positions", TORCH_FN(gaudirt_b200::rotary_embedding_positions));
   m.impl("_rotary_embedding_validated", TORCH_FN(gaudirt_b200::rotary_embedding_validated));
+  m.impl("_advance_decode_lengths", TORCH_FN(gaudirt_b200::advance_decode_lengths));
 }

@@ -58,7 +58,8 @@ enum gk_status {
 enum gk_device_status {
   GK_DEV_BAD_SLOT = 1,          /* a slot outside [0, slots) was met: the access was skipped   */
   GK_DEV_BAD_TABLE = 2,         /* a table entry outside [0, slots) was met: key left out      */
-  GK_DEV_WAIT_EXPIRED = 4       /* a bounded wait ran out                                      */
+  GK_DEV_WAIT_EXPIRED = 4,      /* a bounded wait ran out                                      */
+  GK_DEV_BAD_METADATA = 8       /* device-side metadata validation rejected a row              */
 };
 
 GK_API const char* gk_status_string(int status);
@@ -253,6 +254,77 @@ GK_API int gk_rotary_kv_store_bf16(const void* q, const void* k, const void* v, 
                             int64_t k_width, int head_dim, int rotary_dim, int is_neox,
                             void* q_out, void* k_out, void* pool_k, void* pool_v, int64_t slots,
                             int32_t* status, gk_stream_t stream);
+
+/* ---- the steps either side of the path ------------------------------------------------------
+ * Slot allocation, replaces gk_paged_alloc_i32_v1 and its host set-up
+ * (src/bridge/paged_slot_allocator.cpp:91-151; known answers tests/paged_slots_device_smoke.py:16-33).
+ * gk_paged_slots_layout is the host half: it checks the request lists like the reference
+ * (message through gk_metadata_error) and writes one int32 record {prefix, length, first token,
+ * first fresh page} per request; *total_out = new tokens, *pages_out = fresh pages consumed
+ * (must not exceed free_page_count).  records_out may be NULL for a sizing call.
+ * gk_paged_slots_allocate takes those records in device memory (16-byte aligned) and writes
+ * slots_out[total]: token j of request r gets last_slots[r] + 1 + j while it still fits the
+ * partly filled page ((-prefix) mod page_size tokens), then
+ * free_pages[first_page + k / page_size] * page_size + k % page_size.
+ * Optional fused outputs, which save the scheduler two scatter launches: `locations_out`
+ * (int32 copy of the slots, the KV store's input) and `table` (the request-to-token table of
+ * the attention kernel: table[row(r)][prefix + j] = slot, row(r) = table_rows ? table_rows[r] : r).
+ * A slot that does not fit int32 or a table cell out of range is skipped and reported in *status. */
+GK_API int gk_paged_slots_layout(const int64_t* prefixes, const int64_t* lengths, int64_t n_requests,
+                          int64_t page_size, int64_t free_page_count, int32_t* records_out,
+                          int64_t* total_out, int64_t* pages_out);
+GK_API int gk_paged_slots_allocate(const int64_t* last_slots, const int64_t* free_pages,
+                            const int32_t* records, int64_t n_requests, int64_t total,
+                            int64_t page_size, int64_t* slots_out, int32_t* table,
+                            int64_t table_row_count, int64_t table_stride, int64_t table_context,
+                            const int32_t* table_rows, int32_t* locations_out, int32_t* status,
+                            gk_stream_t stream);
+
+/* Slot release, replaces gk_paged_free_i32_v1 (src/bridge/paged_slot_allocator.cpp:153-209):
+ * pages_out receives slot / page_size for every slot, in order of first occurrence, each page
+ * once; count_out[0] = number of pages written, count_out[1] = number of slots that were not
+ * inside (0, max_pages * page_size) (the reference raises "released slot is outside the KV
+ * pool" for those; they are left out here).  pages_out holds n_slots entries; `workspace` is
+ * 256-byte aligned device memory of gk_paged_slots_release_workspace_bytes bytes.  The result
+ * does not depend on thread scheduling. */
+GK_API int gk_paged_slots_release_workspace_bytes(int64_t n_slots, int64_t max_pages,
+                                           uint64_t* bytes_out);
+GK_API int gk_paged_slots_release(const int64_t* slots, int64_t n_slots, int64_t page_size,
+                           int64_t max_pages, void* workspace, int64_t* pages_out,
+                           int32_t* count_out, gk_stream_t stream);
+
+/* Replaces advance_decode_lengths (src/bridge/eager_scheduler.cpp:51-82): next = current + 1
+ * for both vectors in one launch, inputs left untouched, no host copy in either direction. */
+GK_API int gk_advance_decode_lengths(const int64_t* seq_lens, const int32_t* orig_seq_lens,
+                              int64_t count, int64_t* next_seq_lens, int32_t* next_orig_seq_lens,
+                              gk_stream_t stream);
+
+/* Validation of device-resident step metadata, replaces gk_paged_metadata_i32_v1 /
+ * gk_scheduler_metadata_i32_v1 / gk_token_indices_i32_v1 (src/bridge/paged_metadata.cpp:26-79,
+ * 326-430).  locations / positions [rows], batch_requests [n_seq] and token_ids [rows] are
+ * int32, or int64 where their bit of wide_mask (1, 2, 4, 8 in that order: locations,
+ * batch_requests, positions, token_ids) is set.  seq is a device copy of the host's per-sequence
+ * int32 records {first_row, n_rows, prefix, index into batch_requests} (16-byte aligned).
+ * Outputs: int32 locations / row-expanded requests / positions (/ tokens), last_token_out[n_seq]
+ * (may be NULL), row_status[rows] with a code per row:
+ *   1 slot or position out of range (or beyond int32)   2 request id out of range
+ *   3 table[request][position] != slot                  4 slot written by two rows
+ *   5 position != prefix + offset in its sequence       6 visible table entry outside [0, slots)
+ *   7 cached-prefix entry names a slot this step writes
+ * (6 and 7 are charged to the first row of the sequence), token_status[rows] (1 = token outside
+ * [0, vocabulary)), first_error[0] = min over bad rows of (row << 8 | code), first_error[1] =
+ * first row with a bad token, both UINT64_MAX when clean.  table == NULL (a table owned and
+ * vouched for by the scheduler) skips 3, 6 and 7.  Any rejection also sets GK_DEV_BAD_METADATA
+ * in *status (may be NULL).  `workspace`: gk_paged_metadata_device_workspace_bytes(slots) bytes.
+ * Rejected entries are replaced by 0 in the int32 outputs so later kernels stay in bounds. */
+GK_API int gk_paged_metadata_device_workspace_bytes(int64_t slots, uint64_t* bytes_out);
+GK_API int gk_paged_metadata_device_validate(
+    const void* locations, const void* batch_requests, const void* positions, const void* token_ids,
+    int wide_mask, int64_t vocabulary, const int32_t* table, int64_t n_requests, int64_t context,
+    int64_t table_stride, int64_t slots, const int32_t* seq, int64_t n_seq, int64_t rows,
+    void* workspace, int32_t* locations_out, int32_t* requests_out, int32_t* positions_out,
+    int32_t* tokens_out, int32_t* last_token_out, int32_t* row_status, int32_t* token_status,
+    uint64_t* first_error, int32_t* status, gk_stream_t stream);
 
 /* ---- attention without any device allocation ---------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that must not

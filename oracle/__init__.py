@@ -13,6 +13,8 @@ project), captured as fixtures under ``tests/golden/`` by
 reference's tests carry (``tests/fused_norm_midpoint_smoke.py:19-35``,
 ``tests/decoder_cpu_reference_test.py:66-68``, ``tests/attention_plan_smoke.py:29-38``,
 ``tests/paged_slots_device_smoke.py:16-37``).  Unpinned corners (no reference test
-exercises them): ``weight_offset != 0`` in the RMS norms.
+exercises them): ``weight_offset != 0`` in the RMS norms; row code 5 of
+``device_metadata_status`` (the reference's validating kernel is not in its tree; codes
+1-4, 6 and 7 are the ones ``tests/paged_device_metadata_smoke.py:130-150`` expects).
 """
 from .paged_oracle import *  # noqa: F401,F403

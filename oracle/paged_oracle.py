@@ -28,7 +28,7 @@ __all__ = [
     "isolated_errors", "fp32_softmax_gate", "tile_indices", "tile_softmax", "online_merge",
     "online_finalize", "split_kv_attend", "rms_norm", "fused_add_rms_norm", "rotary_embedding",
     "rotary_cache", "validate_paged_metadata", "allocate_paged_slots", "release_paged_slots",
-    "gather_dim_last",
+    "device_metadata_status", "gather_dim_last",
 ]
 
 # KV tile of the reference's multi-tile path (src/bridge/paged_metadata.hpp:15, exposed to
@@ -479,6 +479,58 @@ def release_paged_slots(slots, page_size, max_pages):
             seen.add(page)
             pages.append(page)
     return pages
+
+
+def device_metadata_status(locations, batch_requests, positions, mapping, prefixes, lengths, slots,
+                           check_table=True):
+    """Row codes of the device-input metadata form (``src/bridge/paged_metadata.cpp:176-430``; the
+    validating kernel itself is not part of the reference tree, so the numbering is pinned by what
+    ``tests/paged_device_metadata_smoke.py:130-150`` observes -- 1 out-of-range slot or position,
+    2 out-of-range request, 3 slot differs from the table, 4 duplicate slot, 6 bad visible table
+    entry, 7 cached prefix aliases a slot written this step -- and 5, position not equal to
+    prefix + offset, is this build's own number for the one rule the test does not exercise).
+    Returns ``(codes per row, last row index per sequence)``; a duplicate is charged to the later
+    row, 6 and 7 to the first row of the sequence."""
+    n_req, context = len(mapping), len(mapping[0])
+    codes, last, written, row = [], [], set(), 0
+    firsts = []
+    for b, (prefix, length) in enumerate(zip(prefixes, lengths)):
+        firsts.append(row)
+        request = int(batch_requests[b])
+        for i in range(length):
+            slot, position = int(locations[row]), int(positions[row])
+            if not (0 <= slot < slots and 0 <= position < context):
+                code = 1
+            elif not 0 <= request < n_req:
+                code = 2
+            elif position != prefix + i:
+                code = 5
+            elif check_table and int(mapping[request][position]) != slot:
+                code = 3
+            elif slot in written:
+                code = 4
+            else:
+                code = 0
+                written.add(slot)
+            codes.append(code)
+            row += 1
+        last.append(row - 1)
+    if check_table:
+        for b, (prefix, length) in enumerate(zip(prefixes, lengths)):
+            request = int(batch_requests[b])
+            if not 0 <= request < n_req:
+                continue
+            worst = 0
+            for p in range(prefix + length):
+                slot = int(mapping[request][p])
+                if not 0 <= slot < slots:
+                    worst = 6
+                    break
+                if p < prefix and slot in written:
+                    worst = worst or 7
+            if worst and codes[firsts[b]] == 0:
+                codes[firsts[b]] = worst
+    return codes, last
 
 
 def gather_dim_last(shards):

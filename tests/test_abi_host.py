@@ -114,3 +114,33 @@ def test_schedule_rejects_unsupported_geometry():
     for q_heads, kv_heads, d in ((32, 8, 96), (34, 1, 128), (9, 2, 128)):
         with pytest.raises(abi.GkError, match="unsupported"):
             H.plan(seq, q_heads, kv_heads, d)
+
+
+def test_slot_layout_records_and_errors():
+    """Host half of slot allocation: per-request records, totals and the reference's argument
+    errors (src/bridge/paged_slot_allocator.cpp:95-112)."""
+    import ctypes as C
+    lib = abi.lib()
+
+    def layout(prefixes, lengths, page, free):
+        n = len(prefixes)
+        p = (C.c_int64 * n)(*prefixes)
+        l = (C.c_int64 * n)(*lengths)
+        records = (C.c_int32 * (4 * n))()
+        total, pages = C.c_int64(-1), C.c_int64(-1)
+        status = lib.gk_paged_slots_layout(p, l, n, page, free, records, C.byref(total), C.byref(pages))
+        return status, list(records), total.value, pages.value
+
+    for page in (1, 16, 64):
+        prefixes, lengths = [0, 7, page, 2 * page - 1], [19, 14, 20, 66]
+        status, records, total, pages = layout(prefixes, lengths, page, 1 << 20)
+        _, used = oracle.allocate_paged_slots([0] * 4, list(range(1 << 12)), prefixes, lengths, page)
+        assert status == 0 and total == sum(lengths) and pages == used
+        assert records[0::4] == prefixes and records[1::4] == lengths
+        assert records[2::4] == list(np.cumsum([0] + lengths[:-1]))
+        fresh = [(p + n + page - 1) // page - (p + page - 1) // page for p, n in zip(prefixes, lengths)]
+        assert records[3::4] == list(np.cumsum([0] + fresh[:-1]))
+    for args, text in ((([0], [40], 16, 2), b"insufficient free pages"), (([0], [0], 16, 2), b"invalid token count"),
+                       (([-1], [4], 16, 2), b"invalid request lengths"), (([0], [4], 0, 2), b"unsupported page size"),
+                       (([1 << 31], [4], 16, 2), b"invalid request lengths")):
+        assert layout(*args)[0] == 5 and text in lib.gk_metadata_error()
