@@ -76,6 +76,42 @@ def main():
         gbs = nbytes / ms / 1e6
         print(f"{name:58s} {ms:8.4f} {gbs:9.1f} {gbs / peak:22.3f}")
 
+    # The steps either side of the path, timed through their operators (launch-bound: microseconds
+    # per call, host time included).
+    steps = []
+    i64 = lambda values: torch.tensor(values, dtype=torch.int64, device=dev)
+    free = torch.randperm(1 << 20, device=dev)
+    for label, batch, prefix, length in (("decode step, 256 requests x 1 token", 256, 4095, 1),
+                                         ("chunked prefill, 16 requests x 512 tokens", 16, 4096, 512)):
+        last = i64([7 * 128 + 126] * batch)
+        args = (last, free, [prefix] * batch, [length] * batch, 128)
+        steps.append((f"_allocate_paged_slots  {label}", _time(lambda: torch.ops.gaudirt._allocate_paged_slots(*args), [()])))
+    table = torch.arange(1, 1 + 256 * 4096, dtype=torch.int32, device=dev).view(256, 4096)
+    steps.append(("_release_paged_slots  256 x 4096 slots -> 8192 pages",
+                  _time(lambda: torch.ops.gaudirt._release_paged_slots(table.view(-1).long(), 128, 1 << 14), [()])))
+    steps.append(("_release_paged_slots  one request, 4096 slots -> 32 pages",
+                  _time(lambda: torch.ops.gaudirt._release_paged_slots(table[3].long(), 128, 1 << 14), [()])))
+    seq, orig = i64([4096] * 256), torch.full((256,), 4096, dtype=torch.int32, device=dev)
+    steps.append(("_advance_decode_lengths  256 requests",
+                  _time(lambda: torch.ops.gaudirt._advance_decode_lengths(seq, orig), [()])))
+    requests = torch.arange(256, dtype=torch.int32, device=dev)
+    positions = torch.full((256,), 4095, dtype=torch.int32, device=dev)
+    locations = table[:, 4095].contiguous()
+    slots = 256 * 4096 + 1
+    steps.append(("PagedMetadata.from_device  256 x ctx 4096 (checks 1M table entries)",
+                  _time(lambda: rt.PagedMetadata.from_device(locations, requests, positions, table, [4095] * 256,
+                                                             [1] * 256, slots), [()])))
+    steps.append(("PagedMetadata._from_scheduler  same, no read-back",
+                  _time(lambda: rt.PagedMetadata._from_scheduler(locations, requests, positions, table, [4095] * 256,
+                                                                 [1] * 256, slots, None, 0), [()])))
+    host = [t.cpu() for t in (locations, requests, positions, table)]
+    steps.append(("PagedMetadata(host lists)  same step validated on the host",
+                  _time(lambda: rt.PagedMetadata(host[0], host[1], host[2], host[3], slots), [()], iters=5)))
+    print()
+    for name, ms in steps:
+        print(f"{name:72s} {ms * 1e3:9.1f} us per call")
+    assert rt._C._take_device_status() == 0
+
 
 if __name__ == "__main__":
     main()
