@@ -9,6 +9,8 @@
 // tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact.
 #include "gk_common.cuh"
 
+#include <algorithm>
+
 namespace gk {
 namespace {
 
@@ -53,16 +55,53 @@ __device__ __forceinline__ double block_sum(double v, double* shared) {
 
 // One CTA per row.  VEC = 8: 16-byte loads, the row is held in registers between the reduction
 // and the write (hidden <= 256 threads * 8 * 4).  VEC = 1: any alignment, second pass re-reads.
-template <int VEC, bool FUSED>
+// Partial results of the tensor-parallel ranks, summed in rank order (PARTS variant below).
+struct PartList {
+  const unsigned short* p[GK_MAX_OUTPUTS];
+  int n;
+};
+
+// Rank-ordered sum of bf16 partials the way the reference's all-reduce defines it
+// (tests/tp4_gather_reduce_smoke.py:16-20): fp32 accumulator seeded with rank 0, one fp32 add per
+// further rank, one rounding to bf16.  Loads bypass L1: the partials were written by other GPUs.
+__device__ __forceinline__ void rank_sum8(const PartList& parts, int64_t offset, unsigned short (&out)[8]) {
+  float acc[8];
+  {
+    const uint4 a = __ldcg(reinterpret_cast<const uint4*>(parts.p[0] + offset));
+    const unsigned short* av = reinterpret_cast<const unsigned short*>(&a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = __uint_as_float((uint32_t)av[e] << 16);
+  }
+  for (int r = 1; r < parts.n; ++r) {
+    const uint4 b = __ldcg(reinterpret_cast<const uint4*>(parts.p[r] + offset));
+    const unsigned short* bv = reinterpret_cast<const unsigned short*>(&b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], __uint_as_float((uint32_t)bv[e] << 16));
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[e] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[e]));
+}
+
+__global__ void __launch_bounds__(256) rank_sum_kernel(const PartList parts, int64_t vectors, unsigned short* __restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vectors; i += (int64_t)gridDim.x * blockDim.x) {
+    unsigned short v[8];
+    rank_sum8(parts, i * 8, v);
+    *reinterpret_cast<uint4*>(out + i * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+// PARTS: x is not read; the row comes from rank_sum8 over parts (row stride x_stride).
+template <int VEC, bool FUSED, bool PARTS = false>
 __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __restrict__ x,
                                                        const unsigned short* __restrict__ residual,
                                                        const unsigned short* __restrict__ weight,
                                                        unsigned short* __restrict__ y, unsigned short* __restrict__ u_out,
                                                        int64_t x_stride, int64_t r_stride, int hidden, double epsilon,
-                                                       double weight_offset) {
+                                                       double weight_offset, const PartList parts = PartList{}) {
+  static_assert(!PARTS || (VEC == 8 && FUSED), "the rank-sum front exists for the vectorised fused form only");
   __shared__ double partial[8];
   const int64_t row = blockIdx.x;
-  const unsigned short* xr = x + row * x_stride;
+  const unsigned short* xr = PARTS ? nullptr : x + row * x_stride;
   const unsigned short* rr = FUSED ? residual + row * r_stride : nullptr;
   unsigned short* yr = y + row * (int64_t)hidden;
   unsigned short* ur = FUSED ? u_out + row * (int64_t)hidden : nullptr;
@@ -74,7 +113,14 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
     for (int it = 0; it < kItems; ++it) {
       const int col = (it * 256 + threadIdx.x) * 8;
       if (col < hidden) {
-        uint4 a = __ldg(reinterpret_cast<const uint4*>(xr + col));
+        uint4 a;
+        if (PARTS) {
+          unsigned short summed[8];
+          rank_sum8(parts, row * x_stride + col, summed);
+          a = *reinterpret_cast<const uint4*>(summed);
+        } else {
+          a = __ldg(reinterpret_cast<const uint4*>(xr + col));
+        }
         const unsigned short* av = reinterpret_cast<const unsigned short*>(&a);
         if (FUSED) {
           uint4 b = __ldg(reinterpret_cast<const uint4*>(rr + col));
@@ -372,6 +418,51 @@ extern "C" int gk_fused_add_rms_norm_bf16(const void* x, const void* residual, c
   if (!residual) return GK_ERR_INVALID_ARGUMENT;
   return norm_common(x, residual, weight, (double)epsilon, (double)weight_offset, rows, hidden, x_row_stride,
                      residual_row_stride, y, u, stream);
+}
+
+static int parts_ok(const void* const* parts, int world, gk::PartList* list) {
+  if (!parts || world < 1 || world > GK_MAX_OUTPUTS) return GK_ERR_INVALID_ARGUMENT;
+  list->n = world;
+  for (int r = 0; r < world; ++r) {
+    if (!parts[r] || (reinterpret_cast<uintptr_t>(parts[r]) & 15)) return GK_ERR_INVALID_ARGUMENT;
+    list->p[r] = static_cast<const unsigned short*>(parts[r]);
+  }
+  return GK_OK;
+}
+
+extern "C" int gk_rank_sum_bf16(const void* const* parts, int world, int64_t count, void* out, gk_stream_t stream) {
+  if (count == 0) return GK_OK;
+  gk::PartList list{};
+  if (const int bad = parts_ok(parts, world, &list)) return bad;
+  if (!out || count < 0 || (reinterpret_cast<uintptr_t>(out) & 15)) return GK_ERR_INVALID_ARGUMENT;
+  if (count % 8) return GK_ERR_UNSUPPORTED;
+  const int64_t vectors = count / 8;
+  const unsigned blocks = (unsigned)std::min<int64_t>((vectors + 255) / 256, 148 * 8);
+  gk::rank_sum_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(list, vectors,
+                                                                                 static_cast<unsigned short*>(out));
+  return gk::check_launch();
+}
+
+extern "C" int gk_rank_sum_add_rms_norm_bf16(const void* const* parts, int world, int64_t part_row_stride,
+                                             const void* residual, const void* weight, float epsilon,
+                                             float weight_offset, int64_t rows, int64_t hidden,
+                                             int64_t residual_row_stride, void* y, void* u, gk_stream_t stream) {
+  if (rows == 0) return GK_OK;
+  gk::PartList list{};
+  if (const int bad = parts_ok(parts, world, &list)) return bad;
+  if (!residual || !weight || !y || !u || rows < 0 || hidden <= 0 || !(epsilon > 0.f) || part_row_stride < hidden ||
+      residual_row_stride < hidden)
+    return GK_ERR_INVALID_ARGUMENT;
+  if (hidden > 8192 || rows > 0x7fffffffLL || hidden % 8 || part_row_stride % 8 || residual_row_stride % 8)
+    return GK_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y) |
+       reinterpret_cast<uintptr_t>(u)) & 15)
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::rms_norm_kernel<8, true, true><<<(unsigned)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      nullptr, static_cast<const unsigned short*>(residual), static_cast<const unsigned short*>(weight),
+      static_cast<unsigned short*>(y), static_cast<unsigned short*>(u), part_row_stride, residual_row_stride, (int)hidden,
+      (double)epsilon, (double)weight_offset, list);
+  return gk::check_launch();
 }
 
 extern "C" int gk_rotary_bf16(const void* q, const void* k, int64_t q_row_stride, int64_t k_row_stride,

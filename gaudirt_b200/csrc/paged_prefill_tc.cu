@@ -27,9 +27,8 @@
 // stages each, so Q K_{j+1}^T and the loads run under softmax_j and P_j V_j under softmax_{j+1}.
 // Every mbarrier wait is bounded: on expiry the CTA raises GK_DEV_WAIT_EXPIRED, drains its
 // copies, frees its TMEM and returns.
-#include "gk_common.cuh"
+#include "tc_common.cuh"
 
-#include <cuda.h>
 #include <string.h>
 #include <math_constants.h>
 
@@ -70,113 +69,6 @@ struct Shared {
 
 __device__ __forceinline__ uint32_t tile_off(int r, int c) {
   return (c >> 3) * kPanelBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-}
-
-// SWIZZLE_128B shared-memory matrix descriptor (version 1).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return (uint64_t)((saddr >> 4) & 0x3fff) | (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16 |
-         (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32 | (uint64_t)1 << 46 | (uint64_t)2 << 61;
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-// Arrive once all cp.async of the calling thread issued so far have landed (counted arrival).
-__device__ __forceinline__ void bar_arrive_on_copies(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void bar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// One 2-D TMA box (64 columns x box rows of the [kv_heads*slots, 128] pool view) into shared memory.
-__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
-      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait; returns false (and raises the CTA's abort flag) when it gives up.  The loaders,
-// whose waits are long and off the critical path, give try_wait a suspend-time hint so that they
-// sleep in hardware instead of spinning through issue slots the softmax warps need.
-constexpr int kSpinLimit = 1 << 22;
-constexpr int kPatientHintNs = 1000, kPatientLimit = 1 << 20;
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, Shared* sh) {
-  const uint32_t addr = smem_u32(bar);
-  for (int i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok)
-                 : "r"(addr), "r"(parity)
-                 : "memory");
-    if (ok) return true;
-    if ((i & 1023) == 1023 && *reinterpret_cast<volatile int*>(&sh->abort)) return false;
-  }
-  atomicExch(&sh->abort, 1);
-  return false;
-}
-__device__ __forceinline__ bool bar_wait_patient(uint64_t* bar, uint32_t parity, Shared* sh) {
-  const uint32_t addr = smem_u32(bar);
-  for (int i = 0; i < kPatientLimit; ++i) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok)
-                 : "r"(addr), "r"(parity), "r"(kPatientHintNs)
-                 : "memory");
-    if (ok) return true;
-    if (*reinterpret_cast<volatile int*>(&sh->abort)) return false;
-  }
-  atomicExch(&sh->abort, 1);
-  return false;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
-      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
-      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
-      "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
-      "r"(r[31])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 128.
@@ -271,7 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j & 1;
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], (j >> 1) & 1, sh));
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], (j >> 1) & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
       const uint32_t s_addr = tmem + st * kTile + wg * 64 + lane_base;
@@ -318,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       // the two halves of a row meet through an mbarrier (a bounded wait, unlike bar.sync)
       sh->exchange[st][wg][pr] = mx;
       bar_arrive(&sh->swap[st]);
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[st], (j >> 1) & 1, sh));
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[st], (j >> 1) & 1, &sh->abort));
       if (!alive) break;
       mx = fmaxf(mx, sh->exchange[st][wg ^ 1][pr]);
       // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
@@ -332,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       }
       const float mu = m == -CUDART_INF_F ? 0.f : m;
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st ^ 1], ((j - 1) >> 1) & 1, sh));
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st ^ 1], ((j - 1) >> 1) & 1, &sh->abort));
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
@@ -346,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         tc_fence_before();
       }
       if (j >= 2) {                                                // P[st] was last read by P.V of tile j-2
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, sh));
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, &sh->abort));
         if (!alive) break;
       }
       // probabilities, rounded to bf16 for the second product; l from the fp32 values
@@ -372,10 +264,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     }
     // epilogue: O / l -> bf16 rows of the output
     const int last = n_tiles - 1;
-    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[last & 1], (last >> 1) & 1, sh));
+    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[last & 1], (last >> 1) & 1, &sh->abort));
     sh->exchange[n_tiles & 1][wg][pr] = l;
     bar_arrive(&sh->swap[2]);
-    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[2], 0, sh));
+    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[2], 0, &sh->abort));
     l += sh->exchange[n_tiles & 1][wg ^ 1][pr];
     if (alive) {
       tc_fence_after();
@@ -445,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
       if (j >= 2) {   // stage free: K once Q.K^T of tile j-2 completed, V once P.V of tile j-2 completed
         uint64_t* freed = is_v ? &sh->pv_done[st] : &sh->s_full[st];
-        alive = __all_sync(0xffffffffu, bar_wait_patient(freed, ((j - 2) >> 1) & 1, sh));
+        alive = __all_sync(0xffffffffu, bar_wait_patient(freed, ((j - 2) >> 1) & 1, &sh->abort));
         if (!alive) break;
       }
       const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
@@ -477,8 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     bool alive = true;
     auto issue_pv = [&](int i) {
       const int st = i & 1;
-      if (!bar_wait(&sh->p_full[st], (i >> 1) & 1, sh)) return false;
-      if (!bar_wait(&sh->v_full[st], (i >> 1) & 1, sh)) return false;
+      if (!bar_wait(&sh->p_full[st], (i >> 1) & 1, &sh->abort)) return false;
+      if (!bar_wait(&sh->v_full[st], (i >> 1) & 1, &sh->abort)) return false;
       fence_async_smem();
       tc_fence_after();
       const uint32_t v_addr = v_base + st * kTileBytes, pa = p_addr + st * kTileBytes;
@@ -493,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     };
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int st = j & 1;
-      alive = bar_wait(&sh->k_full[st], (j >> 1) & 1, sh);
+      alive = bar_wait(&sh->k_full[st], (j >> 1) & 1, &sh->abort);
       if (!alive) break;
       fence_async_smem();
       tc_fence_after();
@@ -514,25 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   __syncthreads();
   if (tid == 0 && sh->abort && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
-}
-
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &status) != cudaSuccess ||
-        status != cudaDriverEntryPointSuccess) {
-      (void)cudaGetLastError();
-      sym = nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(sym);
-  }();
-  return fn;
 }
 
 // 2-D view [kv_heads*slots rows, 128 bf16] of one pool half; boxes of 64 columns x box_rows rows.

@@ -820,6 +820,88 @@ std::tuple<at::Tensor, at::Tensor> advance_decode_lengths(const at::Tensor& seq_
   return {next, orig_next};
 }
 
+// ---------------------------------------------------------------------------------------------
+// o_proj and its rank-ordered sum (the chain O-Proj -> AllReduce -> AddRMSNorm of the
+// reference's tensor-parallel decoder; src/bridge/communicator.cpp:373-417)
+// ---------------------------------------------------------------------------------------------
+void oproj_into(const at::Tensor& input, const at::Tensor& weight, const std::vector<at::Tensor>& outs) {
+  TORCH_CHECK(input.is_cuda() && weight.device() == input.device() && input.scalar_type() == at::kBFloat16 &&
+                  weight.scalar_type() == at::kBFloat16 && input.dim() == 2 && weight.dim() == 2 &&
+                  input.size(1) == weight.size(1) && input.stride(1) == 1 && weight.stride(1) == 1,
+              "GaudiRT o_proj: expected BF16 device matrices input [rows, k] and weight [n, k]");
+  TORCH_CHECK(!outs.empty() && outs.size() <= GK_MAX_OUTPUTS, "GaudiRT o_proj: invalid destination count");
+  std::vector<void*> ptrs;
+  for (const auto& t : outs) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.size(0) == input.size(0) &&
+                    t.size(1) == weight.size(0) && t.stride(1) == 1 && t.stride(0) == outs.front().stride(0),
+                "GaudiRT o_proj: destinations must be BF16 [rows, n] blocks of equal stride");
+    ptrs.push_back(t.data_ptr());
+  }
+  const auto device = input.device();
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_oproj_bf16(input.data_ptr(), input.stride(0), weight.data_ptr(), weight.stride(0), input.size(0),
+                             weight.size(0), input.size(1), ptrs.data(), (int)ptrs.size(), outs.front().stride(0),
+                             device_status(device.index()).data_ptr<int32_t>(),
+                             stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "o_proj");
+}
+
+at::Tensor oproj(const at::Tensor& input, const at::Tensor& weight) {
+  TORCH_CHECK(input.dim() == 2 && weight.dim() == 2, "GaudiRT o_proj: expected matrices");
+  auto out = at::empty({input.size(0), weight.size(0)}, input.options().memory_format(at::MemoryFormat::Contiguous));
+  oproj_into(input, weight, {out});
+  return out;
+}
+
+void oproj_push(const at::Tensor& input, const at::Tensor& weight, at::TensorList outs) {
+  oproj_into(input, weight, std::vector<at::Tensor>(outs.begin(), outs.end()));
+}
+
+std::vector<const void*> part_pointers(at::TensorList parts) {
+  TORCH_CHECK(!parts.empty() && parts.size() <= GK_MAX_OUTPUTS, "GaudiRT rank sum: invalid rank count");
+  std::vector<const void*> ptrs;
+  for (const auto& t : parts) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.sizes() == parts.front().sizes() &&
+                    t.strides() == parts.front().strides() && t.device() == parts.front().device(),
+                "GaudiRT rank sum: partials must be BF16 device tensors of one shape and layout");
+    ptrs.push_back(t.data_ptr());
+  }
+  return ptrs;
+}
+
+at::Tensor rank_sum(at::TensorList parts) {
+  const auto ptrs = part_pointers(parts);
+  TORCH_CHECK(parts.front().is_contiguous(), "GaudiRT rank sum: partials must be contiguous");
+  auto out = at::empty_like(parts.front());
+  const auto device = out.device();
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_rank_sum_bf16(ptrs.data(), (int)ptrs.size(), out.numel(), out.data_ptr(),
+                                stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "rank sum");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> rank_sum_add_rms_norm(at::TensorList parts, const at::Tensor& residual,
+                                                         const at::Tensor& weight, double epsilon, double weight_offset) {
+  const auto ptrs = part_pointers(parts);
+  const auto& first = parts.front();
+  TORCH_CHECK(first.dim() == 2 && first.stride(1) == 1 && residual.is_cuda() && residual.device() == first.device() &&
+                  residual.scalar_type() == at::kBFloat16 && residual.sizes() == first.sizes() && residual.stride(1) == 1 &&
+                  weight.device() == first.device() && weight.scalar_type() == at::kBFloat16 && weight.dim() == 1 &&
+                  weight.size(0) == first.size(1) && weight.is_contiguous() && std::isfinite(epsilon) && epsilon > 0,
+              "GaudiRT rank sum: expected BF16 [rows, hidden] partials and residual, [hidden] weight");
+  auto y = at::empty(first.sizes(), first.options().memory_format(at::MemoryFormat::Contiguous));
+  auto u = at::empty_like(y);
+  const auto device = first.device();
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_rank_sum_add_rms_norm_bf16(ptrs.data(), (int)ptrs.size(), first.stride(0), residual.data_ptr(),
+                                             weight.data_ptr(), (float)epsilon, (float)weight_offset, first.size(0),
+                                             first.size(1), residual.stride(0), y.data_ptr(), u.data_ptr(),
+                                             stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "rank sum + norm");
+  return {y, u};
+}
+
 // Reads and clears the device status word of the current device (synchronises the stream).
 int64_t take_device_status() {
   auto& word = device_status(at::cuda::current_device());
@@ -883,6 +965,11 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_allocate_paged_slots_into", &gaudirt_b200::allocate_paged_slots_into);
   m.def("_release_paged_slots", &gaudirt_b200::release_paged_slots);
   m.def("_advance_decode_lengths(Tensor seq_lens, Tensor orig_seq_lens) -> (Tensor, Tensor)");
+  m.def("_oproj(Tensor input, Tensor weight) -> Tensor");
+  m.def("_oproj_push(Tensor input, Tensor weight, Tensor(a!)[] outs) -> ()");
+  m.def("_rank_sum(Tensor[] parts) -> Tensor");
+  m.def("_rank_sum_add_rms_norm(Tensor[] parts, Tensor residual, Tensor weight, float epsilon, "
+        "float weight_offset=0.0) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
@@ -896,4 +983,8 @@ TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("rotary_embedding_positions", TORCH_FN(gaudirt_b200::rotary_embedding_positions));
   m.impl("_rotary_embedding_validated", TORCH_FN(gaudirt_b200::rotary_embedding_validated));
   m.impl("_advance_decode_lengths", TORCH_FN(gaudirt_b200::advance_decode_lengths));
+  m.impl("_oproj", TORCH_FN(gaudirt_b200::oproj));
+  m.impl("_oproj_push", TORCH_FN(gaudirt_b200::oproj_push));
+  m.impl("_rank_sum", TORCH_FN(gaudirt_b200::rank_sum));
+  m.impl("_rank_sum_add_rms_norm", TORCH_FN(gaudirt_b200::rank_sum_add_rms_norm));
 }

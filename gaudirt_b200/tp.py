@@ -133,3 +133,76 @@ class OutputGather:
         gathered = self._local[self._turn % self.depth]
         self._turn += 1
         return gathered
+
+
+class RowParallelOutput:
+    """o_proj on this rank's heads, the rank-ordered sum of the partials, and the next layer's fused
+    residual-add RMS norm (`O-Proj -> AllReduce -> AddRMSNorm`, the reference's usual tensor-parallel
+    chain; sum semantics of ``src/bridge/communicator.cpp:373-417``: fp32 accumulator seeded with
+    rank 0, ranks added in order, one rounding to bf16, so every rank holds the same bits).
+
+    * ``mode="push"`` -- the tensor-core GEMM's epilogue stores its bf16 partial `[rows, hidden]` into
+      slot `rank` of every peer's receive buffer (symmetric memory), one bounded completion barrier
+      follows, and the sum is taken inside the norm kernel's prologue: no collective kernel runs and
+      the summed activation is never written out.
+    * ``mode="nccl"`` -- the baseline: local GEMM, `all_gather_into_tensor` of the partials, then the
+      same rank-ordered sum + norm kernel (bit-identical by construction).
+    """
+
+    WAIT_CYCLES = OutputGather.WAIT_CYCLES
+
+    def __init__(self, rows: int, hidden: int, device, group=None, mode: str = "push", depth: int = 2):
+        if mode not in ("push", "nccl"):
+            raise ValueError("GaudiRT: o_proj exchange mode must be 'push' or 'nccl'")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.rows, self.hidden, self.mode, self.depth = rows, hidden, mode, depth
+        self.device = torch.device(device)
+        self._turn = 0
+        self._epoch = 0
+        if mode == "nccl" or self.world == 1:
+            self.mode = "nccl"
+            self._parts = torch.empty(self.world, rows, hidden, dtype=torch.bfloat16, device=self.device)
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+        shape = (depth, self.world, rows, hidden)
+        self._local = symm_mem.empty(*shape, dtype=torch.bfloat16, device=self.device)
+        self._flags = symm_mem.empty(max(self.world, 8), dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        self._buf_handle = symm_mem.rendezvous(self._local, self.group)
+        self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
+        self._peers = []            # [depth][peer] -> slot `rank` of that peer's receive buffer
+        for d in range(depth):
+            self._peers.append([(self._local if p == self.rank else
+                                 self._buf_handle.get_buffer(p, shape, torch.bfloat16))[d][self.rank]
+                                for p in range(self.world)])
+        self._peer_flags = [self._flags if p == self.rank else
+                            self._flag_handle.get_buffer(p, (self._flags.numel(),), torch.int32)
+                            for p in range(self.world)]
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def partials(self, attn_out, weight):
+        """This step's `[world, rows, hidden]` partials as a list of per-rank views, exchanged."""
+        if self.mode == "nccl":
+            mine = torch.ops.gaudirt._oproj(attn_out, weight)
+            if self.world == 1:
+                return [mine]
+            dist.all_gather_into_tensor(self._parts.view(self.world * self.rows, self.hidden), mine, group=self.group)
+            return list(self._parts.unbind(0))
+        d = self._turn % self.depth
+        torch.ops.gaudirt._oproj_push(attn_out, weight, self._peers[d])
+        self._epoch += 1
+        torch.ops.gaudirt._peer_barrier(self._peer_flags, self.rank, self._epoch, self.WAIT_CYCLES)
+        self._turn += 1
+        return list(self._local[d].unbind(0))
+
+    def forward(self, attn_out, weight, residual, gamma, epsilon, weight_offset=0.0):
+        """`attn_out [rows, local_heads*d]`, `weight [hidden, local_heads*d]` (this rank's columns of
+        o_proj) -> `(normed, new_residual)` of the next layer, identical on every rank."""
+        return torch.ops.gaudirt._rank_sum_add_rms_norm(self.partials(attn_out, weight), residual, gamma, epsilon,
+                                                        weight_offset)
+
+    def all_reduce(self, attn_out, weight):
+        """o_proj followed by the plain rank-ordered sum (the all-reduced activation itself)."""
+        return torch.ops.gaudirt._rank_sum(self.partials(attn_out, weight))

@@ -326,6 +326,33 @@ GK_API int gk_paged_metadata_device_validate(
     int32_t* tokens_out, int32_t* last_token_out, int32_t* row_status, int32_t* token_status,
     uint64_t* first_error, int32_t* status, gk_stream_t stream);
 
+/* ---- o_proj and its rank-ordered sum --------------------------------------------------------
+ * The step behind the attention block in tensor-parallel decode (docs/DESIGN.md:34 of the
+ * reference names the chain O-Proj -> AllReduce -> AddRMSNorm): every rank multiplies its heads
+ * by its slice of the o_proj weight, the partial results are summed in rank order
+ * (src/bridge/communicator.cpp:373-417, expectation tests/tp4_gather_reduce_smoke.py:16-20), and
+ * the sum enters the next layer's fused residual-add RMS norm.
+ *
+ * gk_oproj_bf16: out[m, n] = bf16(a[m, k] . weight[n, k]^T), bf16 operands, fp32 accumulation on
+ * the tensor cores (tcgen05, accumulators in TMEM, operands by TMA).  n and k must be multiples
+ * of 64, strides (elements) multiples of 8, pointers 16-byte aligned.  The same result is stored
+ * to all n_outs destinations (host array of device pointers, common row stride): a destination
+ * may be a peer GPU's receive buffer, which makes the exchange part of this kernel's epilogue.
+ * gk_rank_sum_bf16: out[i] = bf16(((f32(parts[0][i]) + f32(parts[1][i])) + ...)), one fp32
+ * rounding per add, rank order fixed, so every rank computes the same bits; count % 8 == 0.
+ * gk_rank_sum_add_rms_norm_bf16: that sum as the `x` of gk_fused_add_rms_norm_bf16, without
+ * writing it out: u = bf16(sum + residual), y = norm(u).  hidden % 8 == 0, hidden <= 8192. */
+GK_API int gk_oproj_bf16(const void* a, int64_t a_row_stride, const void* weight,
+                  int64_t weight_row_stride, int64_t m, int64_t n, int64_t k, void* const* outs,
+                  int n_outs, int64_t out_row_stride, int32_t* status, gk_stream_t stream);
+GK_API int gk_rank_sum_bf16(const void* const* parts, int world, int64_t count, void* out,
+                     gk_stream_t stream);
+GK_API int gk_rank_sum_add_rms_norm_bf16(const void* const* parts, int world, int64_t part_row_stride,
+                                  const void* residual, const void* weight, float epsilon,
+                                  float weight_offset, int64_t rows, int64_t hidden,
+                                  int64_t residual_row_stride, void* y, void* u,
+                                  gk_stream_t stream);
+
 /* ---- attention without any device allocation ---------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that must not
  * allocate device memory on their hot path: a serving engine that has handed all HBM to its own

@@ -28,7 +28,7 @@ __all__ = [
     "isolated_errors", "fp32_softmax_gate", "tile_indices", "tile_softmax", "online_merge",
     "online_finalize", "split_kv_attend", "rms_norm", "fused_add_rms_norm", "rotary_embedding",
     "rotary_cache", "validate_paged_metadata", "allocate_paged_slots", "release_paged_slots",
-    "device_metadata_status", "gather_dim_last",
+    "device_metadata_status", "gather_dim_last", "linear_bf16", "canonical_rank_sum",
 ]
 
 # KV tile of the reference's multi-tile path (src/bridge/paged_metadata.hpp:15, exposed to
@@ -537,3 +537,21 @@ def gather_dim_last(shards):
     """AllGatherDimLast (``src/bridge/segmented_runner.cpp:170-191``): rank-major concatenation of
     ``[B, cols]`` shards along the last dimension."""
     return torch.cat(list(shards), dim=-1)
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``bf16(x @ weight.T)`` with the product evaluated in binary64 and rounded once: the truth an
+    fp32-accumulating tensor-core GEMM is held against (it may differ in the last bf16 bit where the
+    fp32 sum lands on the other side of a rounding boundary)."""
+    exact = x.double() @ weight.double().t()
+    return bf16_from_f64(exact).to(torch.bfloat16)
+
+
+def canonical_rank_sum(tensors):
+    """The reference's all-reduce result (``tests/tp4_gather_reduce_smoke.py:16-20``, device rule
+    ``src/bridge/communicator.cpp:373-417``): fp32 accumulator seeded with rank 0, the other ranks
+    added in rank order with one fp32 rounding each, one final rounding to the input dtype."""
+    total = None
+    for part in tensors:
+        total = part.to(torch.float32) if total is None else total + part.to(torch.float32)
+    return total.to(tensors[0].dtype)

@@ -61,6 +61,36 @@ def _worker(rank, world, port, result):
             kp, vp = oracle.pool_views(ref_pool)
             ref = oracle.attend_fp32_softmax(c.q, kp, vp, c.requests, c.positions, c.mapping, q_heads, kv_heads, d, c.scale)
             oracle.fp32_softmax_gate(b.cpu().double(), ref)
+        # o_proj on the un-gathered heads -> rank-ordered sum -> residual-add RMS norm: the partials
+        # exchanged by the GEMM epilogue's peer stores against the NCCL all-gather of the same partials
+        hidden, rows = 512, len(ctx)
+        gen = torch.Generator().manual_seed(77)
+        w_full = (torch.randn(hidden, q_heads * d, generator=gen) / (q_heads * d) ** 0.5).bfloat16()
+        gamma = (1 + 0.02 * torch.randn(hidden, generator=gen)).bfloat16()
+        residuals = [torch.randn(rows, hidden, generator=gen).bfloat16() for _ in layer_cases]
+        w_mine = w_full[:, shard.q_columns(d)].contiguous().to(dev)
+        chain = {}
+        for mode in ("nccl", "push"):
+            row_parallel = tp.RowParallelOutput(rows, hidden, dev, mode=mode)
+            got = []
+            for full, res in zip(outs["push"], residuals):
+                mine = full[:, shard.q_columns(d)]                       # this rank's heads, a strided view
+                y, u = row_parallel.forward(mine, w_mine, res.to(dev), gamma.to(dev), 1e-5, 0.0)
+                got.append((y.clone(), u.clone(), row_parallel.all_reduce(mine, w_mine).clone()))
+            torch.cuda.synchronize()
+            chain[mode] = got
+        ok = ok and rt._C._take_device_status() == 0
+        for full, res, a, b in zip(outs["push"], residuals, chain["nccl"], chain["push"]):
+            for x, y in zip(a, b):
+                assert torch.equal(x.view(torch.int16), y.view(torch.int16)), "o_proj push != nccl"
+            parts = [oracle.linear_bf16(full.cpu()[:, tp.HeadShard(r, world, q_heads, kv_heads).q_columns(d)],
+                                        w_full[:, tp.HeadShard(r, world, q_heads, kv_heads).q_columns(d)])
+                     for r in range(world)]
+            reduced = oracle.canonical_rank_sum(parts)
+            assert float((b[2].cpu() != reduced).double().mean()) < 0.03   # fp32 tensor-core sums vs binary64, last bit
+            assert float((b[2].cpu().double() - reduced.double()).abs().max()) <= 2 ** -6 * float(reduced.abs().max())
+            _, want_u = oracle.fused_add_rms_norm(b[2].cpu(), res, gamma, 1e-5, 0.0, dtype=torch.float64)
+            assert torch.equal(b[1].cpu().double(), want_u)               # given the summed activation, bit-exact
         result[rank] = bool(ok)
         dist.barrier()
         dist.destroy_process_group()
