@@ -127,6 +127,9 @@ def parse():
     ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample; 0 = sized for a few seconds")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--combine", default="auto", choices=["auto", "fused", "separate"], help="experiments only")
+    ap.add_argument("--oproj", action="store_true",
+                    help="experiments only (config 5): follow attention by o_proj on the un-gathered heads, the "
+                         "rank-ordered sum of the partials and the residual-add RMS norm, instead of the output gather")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
     return ap.parse_args()
@@ -185,7 +188,12 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def workload_config(w: Workload, world: int, gather: str):
+def workload_config(w: Workload, world: int, gather: str, oproj: bool = False):
+    if oproj:
+        return {"workload": w.describe.replace("fused_add_rms_norm + rotary + KV store + attention",
+                                               "rotary + KV store + attention + o_proj + rank-ordered sum + add-RMS-norm"),
+                "parallelism": f"tp{world} (KV heads sharded, o_proj row-parallel, partials exchanged by: {gather})",
+                "cache": "inputs larger than L2: every layer reads its own KV pool and o_proj weight"}
     return {"workload": w.describe,
             "parallelism": (f"tp{world} (KV heads sharded, attention output gathered along the last dim: {gather})"
                             if world > 1 else "single GPU"),
@@ -357,11 +365,24 @@ def run_b200(args):
         cache = torch.cat((ang.cos(), ang.sin()), dim=-1).float().to(torch.bfloat16).to(dev)
     resident = [h.to(dev) for h in host_in]
 
-    gather = tp.OutputGather(R, hq * d, dev, mode=args.gather) if world > 1 else None
+    gather = tp.OutputGather(R, hq * d, dev, mode=args.gather) if world > 1 and not args.oproj else None
     lib = abi.lib()
+    row_parallel = o_weight = None
+    if args.oproj:
+        if not w.front:
+            raise SystemExit("--oproj belongs to config 5 (the layer step that owns a hidden state)")
+        row_parallel = tp.RowParallelOutput(R, w.hidden, dev, mode=args.gather)
+        ogen = torch.Generator(device=dev).manual_seed(20261150 + rank)
+        o_weight = [(torch.randn(w.hidden, hq * d, generator=ogen, device=dev) / (w.q_heads * d) ** 0.5).to(torch.bfloat16)
+                    for _ in range(L)]
 
     def layer(l, md, q, k, v, x=None, res=None):
         """One layer of the step on the current stream; returns the gathered attention output."""
+        if row_parallel is not None:
+            # rotary -> store + attention on this rank's heads -> o_proj, rank-ordered sum, add + norm
+            q, k = torch.ops.gaudirt.rotary_embedding(q, k, cache, md, d, d, True)
+            attn = torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], md, d, scale)
+            return row_parallel.forward(attn, o_weight[l], res, gamma, 1e-5, 1.0)[0]
         if w.front:
             torch.ops.gaudirt.fused_add_rms_norm(x, res, gamma, 1e-5, 1.0)
             q, k = torch.ops.gaudirt.rotary_embedding(q, k, cache, md, d, d, True)
@@ -509,6 +530,8 @@ def run_b200(args):
                     "frac_of_8TBs_nominal": achieved / 8000.0}
         mine_per_layer = 2 + (1 if len(combine) else 0) + (1 if gather is not None and gather.mode == "push" else 0) + \
             (2 if w.front else 0)
+        if row_parallel is not None:       # rotary, store, attention (+ combine), o_proj, (barrier), sum + add + norm
+            mine_per_layer = 5 + (1 if len(combine) else 0) + (1 if row_parallel.mode == "push" else 0)
     h2d = sum(h[0].numel() * 2 for h in host_in) * L + (3 * R + mapping.numel() + 1) * 4 + work.nbytes + \
         (combine.nbytes if len(combine) else 0)
     line = {
@@ -516,7 +539,7 @@ def run_b200(args):
         "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(w, world, args.gather),
+        "config": workload_config(w, world, args.gather, args.oproj),
         "kv_read_gbs_whole_step": kv_bytes * L * world / ms_per_step / 1e6,
         "roofline": roofline,
         "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),

@@ -86,7 +86,7 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
     if (lane == 0) {
       for (int kt = 0; kt < k_steps; ++kt) {
         const int s = kt % T::kStages;
-        if (kt >= T::kStages && !bar_wait_patient(&sh->empty[s], ((kt / T::kStages) - 1) & 1, &sh->abort)) break;
+        if (kt >= T::kStages && !bar_wait(&sh->empty[s], ((kt / T::kStages) - 1) & 1, &sh->abort)) break;
         bar_arrive_expect_tx(&sh->full[s], T::kStageBytes);
         const uint32_t dst = tiles + s * T::kStageBytes;
 #pragma unroll
@@ -115,7 +115,7 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
       if (alive) umma_commit(&sh->done);
     }
   } else {
-    const bool alive = __all_sync(0xffffffffu, bar_wait_patient(&sh->done, 0, &sh->abort));
+    const bool alive = __all_sync(0xffffffffu, bar_wait(&sh->done, 0, &sh->abort));
     if (alive) {
       tc_fence_after();
       const int quarter = warp & 3;                 // the TMEM lanes a warp may read: 32 * (warp % 4) ...

@@ -1,6 +1,6 @@
 """Kernel-level timings of the small kernels of the path against the HBM roofline.
 
-    python -m gaudirt_b200.microbench
+    python -m gaudirt_b200.microbench [rows|oproj|steps ...]      (no argument: all sections)
 
 Times `kv_store`, `fused_add_rms_norm`, `rotary_embedding` and the split-KV combine alone with CUDA
 events (inputs larger than L2 are cycled so no launch re-reads cached data) and prints algorithmic
@@ -26,7 +26,7 @@ def _time(fn, sets, iters=20):
     return a.elapsed_time(b) / iters
 
 
-def main():
+def main(sections=()):
     import gaudirt_b200 as rt
     from gaudirt_b200 import raw as H
     dev = "cuda:0"
@@ -36,7 +36,16 @@ def main():
     if os.path.exists(path):
         peak = float(json.load(open(path))["hbm_gbs"])
     rows = []
+    want = lambda name: not sections or name in sections
+    if want("rows"):
+        _row_kernels(rows, H, dev, peak)
+    if want("oproj"):
+        _oproj(dev, peak, path)
+    if want("steps"):
+        _steps(rt, dev)
 
+
+def _row_kernels(rows, H, dev, peak):
     # KV store, chunked-prefill size: 8192 rows x 8 KV heads x 128
     kv_heads, d, slots, n = 8, 128, 1 << 20, 8192
     sets = []
@@ -76,6 +85,35 @@ def main():
         gbs = nbytes / ms / 1e6
         print(f"{name:58s} {ms:8.4f} {gbs:9.1f} {gbs / peak:22.3f}")
 
+
+
+def _oproj(dev, peak, path):
+    # o_proj (tcgen05): time against max(weight + activation bytes / copy peak, flops / cuBLAS bf16 peak);
+    # weights are cycled through more copies than L2 holds.  torch's library GEMM is timed beside it.
+    tpeak = 1590.0
+    if os.path.exists(path):
+        tpeak = float(json.load(open(path)).get("bf16_tflops", tpeak))
+    print()
+    print(f"{'gk_oproj_bf16  m x n x k':44s} {'us':>8s} {'TFLOP/s':>9s} {'GB/s':>8s} {'of roofline':>12s} {'library us':>11s}")
+    for label, m, n, k in (("TP8 shard, 70B geometry, batch 64", 64, 8192, 1024),
+                           ("TP8 shard, 70B geometry, batch 256", 256, 8192, 1024),
+                           ("1 GPU, 8B geometry, batch 256", 256, 4096, 4096),
+                           ("1 GPU, 70B geometry, batch 256", 256, 8192, 8192),
+                           ("chunked prefill, 8192 rows, 8B geometry", 8192, 4096, 4096)):
+        copies = max(2, min(12, (160 << 20) // (n * k * 2) + 1))
+        sets = [(torch.randn(m, k, device=dev).to(torch.bfloat16), (torch.randn(n, k, device=dev) / k ** 0.5).to(torch.bfloat16))
+                for _ in range(copies)]
+        ms = _time(lambda x, w: torch.ops.gaudirt._oproj(x, w), sets, iters=3 * copies)
+        lib = _time(lambda x, w: torch.nn.functional.linear(x, w), sets, iters=3 * copies)
+        flops, nbytes = 2.0 * m * n * k, 2.0 * (n * k + m * k + m * n)
+        bound_ms = max(flops / tpeak / 1e9, nbytes / peak / 1e6)
+        print(f"{label + f'  {m}x{n}x{k}':44s} {ms * 1e3:8.1f} {flops / ms / 1e9:9.1f} {nbytes / ms / 1e6:8.0f} "
+              f"{bound_ms / ms:12.3f} {lib * 1e3:11.1f}")
+        del sets
+
+
+
+def _steps(rt, dev):
     # The steps either side of the path, timed through their operators (launch-bound: microseconds
     # per call, host time included).
     steps = []
@@ -114,4 +152,5 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    import sys
+    main(tuple(sys.argv[1:]))

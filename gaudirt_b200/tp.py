@@ -154,8 +154,11 @@ class RowParallelOutput:
     def __init__(self, rows: int, hidden: int, device, group=None, mode: str = "push", depth: int = 2):
         if mode not in ("push", "nccl"):
             raise ValueError("GaudiRT: o_proj exchange mode must be 'push' or 'nccl'")
-        self.group = group if group is not None else dist.group.WORLD
-        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        else:                               # a single process: the sum has one term
+            self.group, self.rank, self.world = None, 0, 1
         self.rows, self.hidden, self.mode, self.depth = rows, hidden, mode, depth
         self.device = torch.device(device)
         self._turn = 0
@@ -185,17 +188,20 @@ class RowParallelOutput:
     def partials(self, attn_out, weight):
         """This step's `[world, rows, hidden]` partials as a list of per-rank views, exchanged."""
         if self.mode == "nccl":
-            mine = torch.ops.gaudirt._oproj(attn_out, weight)
-            if self.world == 1:
-                return [mine]
-            dist.all_gather_into_tensor(self._parts.view(self.world * self.rows, self.hidden), mine, group=self.group)
-            return list(self._parts.unbind(0))
+            return self.exchange(torch.ops.gaudirt._oproj(attn_out, weight))
         d = self._turn % self.depth
         torch.ops.gaudirt._oproj_push(attn_out, weight, self._peers[d])
         self._epoch += 1
         torch.ops.gaudirt._peer_barrier(self._peer_flags, self.rank, self._epoch, self.WAIT_CYCLES)
         self._turn += 1
         return list(self._local[d].unbind(0))
+
+    def exchange(self, mine):
+        """Baseline exchange of an already computed `[rows, hidden]` partial: all-gather, rank-major."""
+        if self.world == 1:
+            return [mine]
+        dist.all_gather_into_tensor(self._parts.view(self.world * self.rows, self.hidden), mine, group=self.group)
+        return list(self._parts.unbind(0))
 
     def forward(self, attn_out, weight, residual, gamma, epsilon, weight_offset=0.0):
         """`attn_out [rows, local_heads*d]`, `weight [hidden, local_heads*d]` (this rank's columns of
