@@ -33,6 +33,7 @@ PROTOTYPES = {
                                        f32, i32, i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_multi_bf16": (i32, [vp, vp, vp, i64, vp, i32, i64, i32, i32, vp]),
     "gk_peer_barrier": (i32, [vp, i32, i32, i32, i64, vp, vp]),
+    "gk_peer_barrier_counted": (i32, [vp, i32, i32, vp, i64, vp, vp]),
     "gk_rms_norm_bf16": (i32, [vp, vp, f32, f32, i64, i64, i64, vp, vp]),
     "gk_fused_add_rms_norm_bf16": (i32, [vp, vp, vp, f32, f32, i64, i64, i64, i64, vp, vp, vp]),
     "gk_rotary_bf16": (i32, [vp, vp, i64, i64, vp, i64, vp, i64, i64, i64, i32, i32, i32, vp, vp, vp, vp]),

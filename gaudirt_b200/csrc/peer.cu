@@ -14,9 +14,19 @@ struct PeerFlags {
   int32_t* ptr[GK_MAX_OUTPUTS];   // ptr[p] = rank p's flag array [world], mapped into this process
 };
 
+// With `counter` the epoch is kept on the device (this launch uses *counter + 1 and stores it back),
+// so the same launch can be replayed from a CUDA graph; every rank must issue the same sequence of
+// barriers.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerFlags flags, int rank, int world, int epoch,
-                                                          long long max_cycles, int32_t* status) {
+                                                          int32_t* counter, long long max_cycles, int32_t* status) {
   const int lane = threadIdx.x;
+  if (counter) {
+    if (lane == 0) {
+      epoch = *counter + 1;
+      *counter = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+  }
   if (lane >= world) return;
   // The launch is stream-ordered after the kernels that wrote the peers' buffers; the fence
   // orders those writes before the flag for observers on other GPUs.
@@ -49,6 +59,21 @@ extern "C" int gk_peer_barrier(int32_t* const* flags, int rank, int world, int32
     if (!flags[p] || (reinterpret_cast<uintptr_t>(flags[p]) & 3)) return GK_ERR_INVALID_ARGUMENT;
     f.ptr[p] = flags[p];
   }
-  gk::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, rank, world, epoch, (long long)max_cycles, status);
+  gk::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, rank, world, epoch, nullptr,
+                                                                                (long long)max_cycles, status);
+  return gk::check_launch();
+}
+
+extern "C" int gk_peer_barrier_counted(int32_t* const* flags, int rank, int world, int32_t* epoch_counter,
+                                       int64_t max_cycles, int32_t* status, gk_stream_t stream) {
+  if (!flags || !epoch_counter || world <= 0 || world > GK_MAX_OUTPUTS || rank < 0 || rank >= world || max_cycles <= 0)
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::PeerFlags f{};
+  for (int p = 0; p < world; ++p) {
+    if (!flags[p] || (reinterpret_cast<uintptr_t>(flags[p]) & 3)) return GK_ERR_INVALID_ARGUMENT;
+    f.ptr[p] = flags[p];
+  }
+  gk::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, rank, world, 0, epoch_counter,
+                                                                                (long long)max_cycles, status);
   return gk::check_launch();
 }

@@ -579,6 +579,26 @@ void peer_barrier(at::TensorList flags, int64_t rank, int64_t epoch, int64_t max
                "peer barrier");
 }
 
+// The barrier with its epoch in device memory (`counter`, int32[1] on this rank): graph-replayable.
+void peer_barrier_counted(at::TensorList flags, int64_t rank, at::Tensor& counter, int64_t max_cycles) {
+  TORCH_CHECK(!flags.empty() && flags.size() <= GK_MAX_OUTPUTS && rank >= 0 && rank < (int64_t)flags.size(),
+              "GaudiRT: invalid peer barrier arguments");
+  std::vector<int32_t*> ptrs;
+  for (const auto& f : flags) {
+    TORCH_CHECK(f.is_cuda() && f.scalar_type() == at::kInt && f.is_contiguous() && f.numel() >= (int64_t)flags.size(),
+                "GaudiRT: peer barrier flags must be int32 device arrays of at least world entries");
+    ptrs.push_back(f.data_ptr<int32_t>());
+  }
+  const auto device = flags[rank].device();
+  TORCH_CHECK(counter.is_cuda() && counter.device() == device && counter.scalar_type() == at::kInt && counter.numel() == 1,
+              "GaudiRT: the barrier epoch counter must be one int32 on this rank's device");
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_peer_barrier_counted(ptrs.data(), (int)rank, (int)flags.size(), counter.data_ptr<int32_t>(), max_cycles,
+                                       device_status(device.index()).data_ptr<int32_t>(),
+                                       stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "peer barrier");
+}
+
 at::Tensor paged_attn(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, at::Tensor& key_pool,
                       at::Tensor& value_pool, const c10::intrusive_ptr<PagedMetadata>& metadata, int64_t head_dim,
                       double scale, double softcap, int64_t sliding_window) {
@@ -949,6 +969,7 @@ TORCH_LIBRARY(gaudirt, m) {
         "Tensor locations, Tensor plan, Tensor(c!)[] outputs, int head_dim, float scale, float softcap=0.0, "
         "int sliding_window=-1) -> ()");
   m.def("_peer_barrier(Tensor(a!)[] flags, int rank, int epoch, int max_cycles) -> ()");
+  m.def("_peer_barrier_counted(Tensor(a!)[] flags, int rank, Tensor(b!) counter, int max_cycles) -> ()");
   m.def("rms_norm(Tensor input, Tensor weight, float epsilon, float weight_offset=0.0) -> Tensor");
   m.def("fused_add_rms_norm(Tensor input, Tensor residual, Tensor weight, float epsilon, float weight_offset=0.0) -> (Tensor, Tensor)");
   m.def("rotary_embedding(Tensor query, Tensor key, Tensor cache, "
@@ -977,6 +998,7 @@ TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("_paged_attn_validated", TORCH_FN(gaudirt_b200::paged_attn_validated));
   m.impl("_paged_attn_push", TORCH_FN(gaudirt_b200::paged_attn_push));
   m.impl("_peer_barrier", TORCH_FN(gaudirt_b200::peer_barrier));
+  m.impl("_peer_barrier_counted", TORCH_FN(gaudirt_b200::peer_barrier_counted));
   m.impl("rms_norm", TORCH_FN(gaudirt_b200::rms_norm));
   m.impl("fused_add_rms_norm", TORCH_FN(gaudirt_b200::fused_add_rms_norm));
   m.impl("rotary_embedding", TORCH_FN(gaudirt_b200::rotary_embedding));

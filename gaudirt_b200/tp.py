@@ -14,7 +14,10 @@ for the plumbing:
   completion barrier with a bounded wait.  No collective kernel and no transpose run.
 
 Buffers are double-buffered: a buffer is written again only after one full barrier has passed, so a
-peer still reading layer L's activation never sees layer L+1's stores.
+peer still reading layer L's activation never sees layer L+1's stores.  The barrier keeps its epoch
+in device memory, so a whole step (all layers) can be captured in one CUDA graph and replayed; a
+captured step must contain a multiple of `depth` exchanges so that every replay starts on the same
+buffer (`graph_safe`).
 """
 from __future__ import annotations
 
@@ -84,6 +87,7 @@ class OutputGather:
         self._local = symm_mem.empty(depth, rows, width, dtype=torch.bfloat16, device=self.device)
         self._flags = symm_mem.empty(max(self.world, 8), dtype=torch.int32, device=self.device)
         self._flags.zero_()
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)     # barrier epoch, kept on the device
         self._buf_handle = symm_mem.rendezvous(self._local, self.group)
         self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
         block = slice(self.rank * cols, (self.rank + 1) * cols)
@@ -100,6 +104,10 @@ class OutputGather:
                             for p in range(self.world)]
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)          # every rank's flags are zero before anyone signals
+
+    def graph_safe(self, exchanges_per_step: int) -> bool:
+        """Whether a step of that many exchanges may be captured in a CUDA graph and replayed."""
+        return self.mode == "nccl" or (exchanges_per_step % self.depth == 0 and self._turn % self.depth == 0)
 
     def destinations(self):
         """Tensors the attention epilogue of this step must write (push mode)."""
@@ -128,8 +136,7 @@ class OutputGather:
 
     def finish(self):
         """Push mode: signal + bounded wait, then hand out the gathered buffer of this step."""
-        self._epoch += 1
-        torch.ops.gaudirt._peer_barrier(self._peer_flags, self.rank, self._epoch, self.WAIT_CYCLES)
+        torch.ops.gaudirt._peer_barrier_counted(self._peer_flags, self.rank, self._counter, self.WAIT_CYCLES)
         gathered = self._local[self._turn % self.depth]
         self._turn += 1
         return gathered
@@ -172,6 +179,7 @@ class RowParallelOutput:
         self._local = symm_mem.empty(*shape, dtype=torch.bfloat16, device=self.device)
         self._flags = symm_mem.empty(max(self.world, 8), dtype=torch.int32, device=self.device)
         self._flags.zero_()
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._buf_handle = symm_mem.rendezvous(self._local, self.group)
         self._flag_handle = symm_mem.rendezvous(self._flags, self.group)
         self._peers = []            # [depth][peer] -> slot `rank` of that peer's receive buffer
@@ -182,6 +190,7 @@ class RowParallelOutput:
         self._peer_flags = [self._flags if p == self.rank else
                             self._flag_handle.get_buffer(p, (self._flags.numel(),), torch.int32)
                             for p in range(self.world)]
+        self._slots = [list(self._local[d].unbind(0)) for d in range(depth)]
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
@@ -191,10 +200,13 @@ class RowParallelOutput:
             return self.exchange(torch.ops.gaudirt._oproj(attn_out, weight))
         d = self._turn % self.depth
         torch.ops.gaudirt._oproj_push(attn_out, weight, self._peers[d])
-        self._epoch += 1
-        torch.ops.gaudirt._peer_barrier(self._peer_flags, self.rank, self._epoch, self.WAIT_CYCLES)
+        torch.ops.gaudirt._peer_barrier_counted(self._peer_flags, self.rank, self._counter, self.WAIT_CYCLES)
         self._turn += 1
-        return list(self._local[d].unbind(0))
+        return self._slots[d]
+
+    def graph_safe(self, exchanges_per_step: int) -> bool:
+        """Whether a step of that many exchanges may be captured in a CUDA graph and replayed."""
+        return self.mode == "nccl" or (exchanges_per_step % self.depth == 0 and self._turn % self.depth == 0)
 
     def exchange(self, mine):
         """Baseline exchange of an already computed `[rows, hidden]` partial: all-gather, rank-major."""

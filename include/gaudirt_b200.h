@@ -215,6 +215,11 @@ GK_API int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* p
  * after max_cycles SM clock cycles and sets GK_DEV_WAIT_EXPIRED in *status; it never traps. */
 GK_API int gk_peer_barrier(int32_t* const* flags, int rank, int world, int32_t epoch,
                     int64_t max_cycles, int32_t* status, gk_stream_t stream);
+/* The same barrier with the epoch kept in device memory: the launch uses *epoch_counter + 1 and
+ * stores it back, so it takes no per-call host value and can be replayed from a CUDA graph.  All
+ * ranks must issue the same sequence of barriers on counters that start equal. */
+GK_API int gk_peer_barrier_counted(int32_t* const* flags, int rank, int world, int32_t* epoch_counter,
+                            int64_t max_cycles, int32_t* status, gk_stream_t stream);
 
 /* ---- front of a decode layer ---------------------------------------------------------------
  * Replace gk_rms_norm_bf16_v1 / gk_fused_add_rms_norm_bf16_v1 (src/bridge/fx_op_lowering.cpp:450-478,
