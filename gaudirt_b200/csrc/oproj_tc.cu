@@ -6,14 +6,17 @@
 // slot of every tensor-parallel peer's receive buffer -- so the exchange rides on the epilogue's
 // stores and no separate collective moves the partials.
 //
-// One CTA owns a [128 * MT] x 64 block of the output (MT = 1 or 2 accumulators, 64 TMEM columns
-// each) and walks K in steps of 64:
+// One CTA owns a [128 * MT] x BN block of the output (MT = 1 or 2 accumulators of BN = 128 or 64
+// TMEM columns each) and walks its K range in steps of 64:
 //   warp 0     one thread issues the TMA loads of a stage: MT boxes [128 x 64] of A and one box
-//              [64 x 64] of W, 128-byte swizzle, no multicast; rows past M are zero-filled by TMA
-//   warp 1     one thread issues tcgen05.mma.kind::f16 (M 128, N 64, K 16) four times per box and
+//              [BN x 64] of W, 128-byte swizzle, no multicast; rows past M are zero-filled by TMA
+//   warp 1     one thread issues tcgen05.mma.kind::f16 (M 128, N BN, K 16) four times per box and
 //              commits the stage back to the loader, finally the accumulators to the epilogue
-//   warps 2-5  epilogue: tcgen05.ld of the thread's row, rounding to bf16, 128-byte row segments
-//              stored to every destination
+//   warps 2-5  epilogue: tcgen05.ld of the thread's row, rounding to bf16, row segments stored to
+//              every destination
+// A kernel of this shape is bound by how fast one SM takes in operand boxes, so small problems are
+// cut along K over a thread-block cluster (2 or 4 CTAs per output block) until the grid fills the
+// GPU; the cluster adds its fp32 accumulators through distributed shared memory in a fixed order.
 // Every mbarrier wait is bounded; on expiry the CTA raises GK_DEV_WAIT_EXPIRED, frees its TMEM and
 // returns.
 #include "tc_common.cuh"
@@ -23,18 +26,23 @@
 namespace gk {
 namespace {
 
-constexpr int kBM = 128, kBN = 64, kBK = 64;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kABytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kWBytes = kBN * kBK * 2;   //  8 KiB
 constexpr int kLinearThreads = 192;
 constexpr int kMaxStages = 8;
+constexpr int kMaxSplit = 4;
+constexpr double kSplitOverheadUs = 6.0;
 
-template <int MT>
+template <int MT, int BN>
 struct LinearTile {
+  static constexpr int kWBytes = BN * kBK * 2;
   static constexpr int kStageBytes = MT * kABytes + kWBytes;
-  static constexpr int kStages = MT == 1 ? 8 : 5;
-  static constexpr int kTmemCols = MT == 1 ? 64 : 128;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > kMaxStages ? kMaxStages : (192 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = MT * BN < 32 ? 32 : MT * BN;
+  static constexpr int kReduceBytes = MT * BN * kBM * 4;         // fp32 accumulators parked for the split-K sum
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+  static_assert(kReduceBytes <= kStages * kStageBytes, "the reduce buffer reuses the pipeline stages");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns: a power of two");
 };
 
 struct LinearShared {
@@ -51,17 +59,52 @@ struct LinearParams {
   int32_t* status;
 };
 
-template <int MT>
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster; release/acquire so that shared-memory writes before it are
+// visible to remote reads after it.
+__device__ __forceinline__ void cluster_sync() {
+  __syncwarp();                                              // the elected threads rejoin their warps first
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_smem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+// No memory clobber: the caller issues a batch of these before the first use so that they overlap;
+// the cluster barrier in front of the batch (which has the clobber) orders them after the writes.
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// Split-K: the CTAs of a cluster (gridDim.z of them) take consecutive K ranges of the same output
+// block, park their fp32 accumulators in their own shared memory and, after a cluster barrier, each
+// adds up a column slice over all CTAs in split order through distributed shared memory -- a fixed
+// order, so the result does not depend on scheduling -- and stores it.
+template <int MT, int BN>
 __global__ void __launch_bounds__(kLinearThreads, 1)
 linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w) {
-  using T = LinearTile<MT>;
+  using T = LinearTile<MT, BN>;
   extern __shared__ unsigned char raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   LinearShared* sh = reinterpret_cast<LinearShared*>(base + T::kStages * T::kStageBytes);
   const uint32_t tiles = smem_u32(base);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (kBM * MT);
-  const int k_steps = p.k / kBK;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (kBM * MT);
+  const int split = (int)cluster_size(), part = (int)cluster_rank();
+  const int all_steps = p.k / kBK, per = (all_steps + split - 1) / split;
+  const int k_first = part * per, k_steps = max(0, min(all_steps, k_first + per) - k_first);
 
   if (tid == 0) {
     for (int s = 0; s < T::kStages; ++s) {
@@ -89,14 +132,15 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
         if (kt >= T::kStages && !bar_wait(&sh->empty[s], ((kt / T::kStages) - 1) & 1, &sh->abort)) break;
         bar_arrive_expect_tx(&sh->full[s], T::kStageBytes);
         const uint32_t dst = tiles + s * T::kStageBytes;
+        const int x = (k_first + kt) * kBK;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_box(dst + mt * kABytes, &map_a, kt * kBK, m0 + mt * kBM, &sh->full[s]);
-        tma_load_box(dst + MT * kABytes, &map_w, kt * kBK, n0, &sh->full[s]);
+        for (int mt = 0; mt < MT; ++mt) tma_load_box(dst + mt * kABytes, &map_a, x, m0 + mt * kBM, &sh->full[s]);
+        tma_load_box(dst + MT * kABytes, &map_w, x, n0, &sh->full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kBN);
+      constexpr uint32_t idesc = umma_idesc_bf16(BN);
       bool alive = true;
       for (int kt = 0; kt < k_steps && alive; ++kt) {
         const int s = kt % T::kStages;
@@ -108,40 +152,97 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int k4 = 0; k4 < kBK / 16; ++k4)
-            umma_bf16(tmem + mt * kBN, umma_desc(a + mt * kABytes + k4 * 32, 16, 1024), umma_desc(w + k4 * 32, 16, 1024),
+            umma_bf16(tmem + mt * BN, umma_desc(a + mt * kABytes + k4 * 32, 16, 1024), umma_desc(w + k4 * 32, 16, 1024),
                       idesc, (kt > 0 || k4 > 0) ? 1u : 0u);
         umma_commit(&sh->empty[s]);
       }
       if (alive) umma_commit(&sh->done);
     }
-  } else {
-    const bool alive = __all_sync(0xffffffffu, bar_wait(&sh->done, 0, &sh->abort));
-    if (alive) {
-      tc_fence_after();
-      const int quarter = warp & 3;                 // the TMEM lanes a warp may read: 32 * (warp % 4) ...
-      const int row = quarter * 32 + lane;
+  }
+
+  // Epilogue warps: thread = one of the 128 accumulator rows (a warp reads TMEM lanes 32 * (warp % 4) ...).
+  const int quarter = warp & 3, row = quarter * 32 + lane;
+  float* park = reinterpret_cast<float*>(base);             // [mt][column][row] fp32, the stages are drained by now
+  bool alive = true;
+  if (warp >= 2) {
+    alive = k_steps == 0 || __all_sync(0xffffffffu, bar_wait(&sh->done, 0, &sh->abort));
+    if (alive) tc_fence_after();
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int64_t out_row = (int64_t)m0 + mt * kBM + row;
-        uint32_t packed[kBN / 2];
+    for (int mt = 0; mt < MT; ++mt) {
+      const int64_t out_row = (int64_t)m0 + mt * kBM + row;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t acc[32];
-          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + mt * kBN + half * 32, acc);
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t acc[32];
+        if (alive && k_steps > 0) {
+          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + mt * BN + c0, acc);
+        } else {
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            packed[half * 16 + c] = pack_bf16(__uint_as_float(acc[2 * c]), __uint_as_float(acc[2 * c + 1]));
+          for (int c = 0; c < 32; ++c) acc[c] = 0u;
         }
-        if (out_row < p.m) {
-          for (int o = 0; o < p.n_outs; ++o) {
-            uint4* dst = reinterpret_cast<uint4*>(p.outs[o] + out_row * p.out_stride + n0);
+        if (split > 1) {
 #pragma unroll
-            for (int c = 0; c < kBN / 8; ++c)
-              dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          for (int c = 0; c < 32; ++c) park[(mt * BN + c0 + c) * kBM + row] = __uint_as_float(acc[c]);
+        } else if (out_row < p.m) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) packed[c] = pack_bf16(__uint_as_float(acc[2 * c]), __uint_as_float(acc[2 * c + 1]));
+          for (int o = 0; o < p.n_outs; ++o) {
+            uint4* dst = reinterpret_cast<uint4*>(p.outs[o] + out_row * p.out_stride + n0 + c0);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
           }
         }
       }
     }
+  }
+  if (split > 1) {
+    cluster_sync();                                          // every CTA's accumulators are parked
+    if (warp >= 2) {
+      // This CTA adds up columns [part * width, (part + 1) * width) of the block.  A thread takes four
+      // consecutive rows (one 16-byte load per column and CTA, a warp reads 512 contiguous bytes) of
+      // every fourth 8-column group.
+      const int width = BN / split, c_first = part * width;
+      const int t = tid - 64, rows4 = (t & 31) * 4, group = t >> 5;
+      uint32_t peer[kMaxSplit];
+#pragma unroll
+      for (int s = 0; s < kMaxSplit; ++s) peer[s] = peer_smem_addr(smem_u32(park), (uint32_t)min(s, split - 1));
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll 1
+        for (int c0 = group * 8; c0 < width; c0 += 32) {
+          float4 sum[8];
+          const uint32_t offset = (uint32_t)(((mt * BN + c_first + c0) * kBM + rows4) * 4);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) sum[c] = ld_cluster_f32x4(peer[0] + offset + c * kBM * 4);
+#pragma unroll
+          for (int s = 1; s < kMaxSplit; ++s) {
+            if (s < split) {
+              float4 next[8];
+#pragma unroll
+              for (int c = 0; c < 8; ++c) next[c] = ld_cluster_f32x4(peer[s] + offset + c * kBM * 4);
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                sum[c].x = __fadd_rn(sum[c].x, next[c].x);
+                sum[c].y = __fadd_rn(sum[c].y, next[c].y);
+                sum[c].z = __fadd_rn(sum[c].z, next[c].z);
+                sum[c].w = __fadd_rn(sum[c].w, next[c].w);
+              }
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int64_t out_row = (int64_t)m0 + mt * kBM + rows4 + r;
+            if (out_row >= p.m) break;
+            const float* f = reinterpret_cast<const float*>(sum) + r;          // element r of every column's float4
+            const uint4 packed = make_uint4(pack_bf16(f[0], f[4]), pack_bf16(f[8], f[12]), pack_bf16(f[16], f[20]),
+                                            pack_bf16(f[24], f[28]));
+            for (int o = 0; o < p.n_outs; ++o)
+              *reinterpret_cast<uint4*>(p.outs[o] + out_row * p.out_stride + n0 + c_first + c0) = packed;
+          }
+        }
+      }
+    }
+    cluster_sync();                                          // nobody leaves while its memory is still being read
   }
 
   tc_fence_before();
@@ -164,20 +265,60 @@ bool make_matrix_map(CUtensorMap* map, const void* data, int64_t rows, int64_t c
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MT>
-int launch_linear(const LinearParams& p, const CUtensorMap& map_a, const CUtensorMap& map_w, cudaStream_t stream) {
-  using T = LinearTile<MT>;
+template <int MT, int BN>
+int launch_linear(const LinearParams& p, const CUtensorMap& map_a, const CUtensorMap& map_w, int split, cudaStream_t stream) {
+  using T = LinearTile<MT, BN>;
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
   if (device < 0 || device >= 64 || !configured[device]) {
-    if (cudaFuncSetAttribute(linear_tc_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(linear_tc_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
+        cudaSuccess)
       return check_launch();
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  const dim3 grid((unsigned)(p.n / kBN), (unsigned)((p.m + kBM * MT - 1) / (kBM * MT)));
-  linear_tc_kernel<MT><<<grid, kLinearThreads, T::kSmemBytes, stream>>>(p, map_a, map_w);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)(p.n / BN), (unsigned)((p.m + kBM * MT - 1) / (kBM * MT)), (unsigned)split);
+  config.blockDim = dim3(kLinearThreads);
+  config.dynamicSmemBytes = T::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute cluster;
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 1;
+  cluster.val.clusterDim.y = 1;
+  cluster.val.clusterDim.z = (unsigned)split;
+  config.attrs = &cluster;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, linear_tc_kernel<MT, BN>, p, map_a, map_w) != cudaSuccess) return check_launch();
   return check_launch();
+}
+
+// Block width and K cut, from a cost model fitted to measurements on B200: an SM takes in operand
+// boxes at about 76 GB/s whatever the box sizes, a wave of CTAs therefore costs
+// k-steps x stage bytes / 76 GB/s, and summing a cluster's accumulators through distributed shared
+// memory costs a few microseconds once.
+struct LinearChoice {
+  int bn, split;
+};
+LinearChoice choose_linear(int64_t m, int64_t n, int64_t k, int mt, int sms) {
+  const int64_t m_blocks = (m + kBM * mt - 1) / (kBM * mt), k_steps = k / kBK;
+  LinearChoice best{64, 1};
+  double best_us = 1e30;
+  for (int bn = 128; bn >= 64; bn /= 2) {
+    if (n % bn) continue;
+    for (int split = 1; split <= kMaxSplit; split *= 2) {
+      if (split > 1 && (bn / split < 32 || k_steps / split < 4)) break;
+      const int64_t ctas = (n / bn) * m_blocks * split, waves = (ctas + sms - 1) / sms;
+      const double stage_kb = mt * 16.0 + bn / 8.0;
+      const double us = (double)waves * (double)((k_steps + split - 1) / split) * stage_kb * (1.0 / 76.0) +
+                        (split > 1 ? kSplitOverheadUs : 0.0);
+      if (us < best_us) {
+        best_us = us;
+        best = LinearChoice{bn, split};
+      }
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -190,7 +331,7 @@ extern "C" int gk_oproj_bf16(const void* a, int64_t a_row_stride, const void* we
   if (m == 0) return GK_OK;
   if (!a || !weight || !outs || n_outs < 1 || n_outs > GK_MAX_OUTPUTS || m < 0 || n <= 0 || k <= 0)
     return GK_ERR_INVALID_ARGUMENT;
-  if (n % kBN || k % kBK || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || (m + 255) / 256 > 65535)
+  if (n % 64 || k % kBK || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || (m + 255) / 256 > 65535)
     return GK_ERR_UNSUPPORTED;
   if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(weight)) & 15) || (a_row_stride & 7) ||
       (weight_row_stride & 7) || (out_row_stride & 7) || a_row_stride < k || weight_row_stride < k || out_row_stride < n)
@@ -206,11 +347,20 @@ extern "C" int gk_oproj_bf16(const void* a, int64_t a_row_stride, const void* we
   p.n = (int)n;
   p.k = (int)k;
   p.status = status;
+  static int sms[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return check_launch();
+  if (!sms[device] && cudaDeviceGetAttribute(&sms[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+    return check_launch();
+  const int mt = m > kBM ? 2 : 1;
+  const LinearChoice choice = choose_linear(m, n, k, mt, sms[device]);
+  const int bn = choice.bn, split = choice.split;
   alignas(64) CUtensorMap map_a, map_w;
   memset(&map_a, 0, sizeof(map_a));
   memset(&map_w, 0, sizeof(map_w));
-  if (!make_matrix_map(&map_a, a, m, k, a_row_stride, kBM) || !make_matrix_map(&map_w, weight, n, k, weight_row_stride, kBN))
+  if (!make_matrix_map(&map_a, a, m, k, a_row_stride, kBM) || !make_matrix_map(&map_w, weight, n, k, weight_row_stride, bn))
     return GK_ERR_UNSUPPORTED;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  return m > kBM ? launch_linear<2>(p, map_a, map_w, s) : launch_linear<1>(p, map_a, map_w, s);
+  if (bn == 128) return mt == 2 ? launch_linear<2, 128>(p, map_a, map_w, split, s) : launch_linear<1, 128>(p, map_a, map_w, split, s);
+  return mt == 2 ? launch_linear<2, 64>(p, map_a, map_w, split, s) : launch_linear<1, 64>(p, map_a, map_w, split, s);
 }
