@@ -129,6 +129,9 @@ def parse():
     ap.add_argument("--combine", default="auto", choices=["auto", "fused", "separate"], help="experiments only")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the resident step kernel by kernel instead of replaying it from one CUDA graph")
+    ap.add_argument("--e2e-host-metadata", action="store_true",
+                    help="end-to-end step: validate the metadata on the host and upload the whole request-to-token "
+                         "table every step (default: table resident on the device, step indices validated there)")
     ap.add_argument("--oproj", action="store_true",
                     help="experiments only (config 5): follow attention by o_proj on the un-gathered heads, the "
                          "rank-ordered sum of the partials and the residual-add RMS norm, instead of the output gather")
@@ -403,12 +406,28 @@ def run_b200(args):
         return last
 
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    table_dev = md.request_mapping()
+    host_index = [locations.pin_memory(), torch.arange(B, dtype=torch.int32).pin_memory(), positions.pin_memory()]
+    prefix_list, length_list = (w.ctx - w.chunk).tolist(), [w.chunk] * B
 
     def e2e_step():
         """The same step from HOST buffers: metadata built from CPU tensors, per layer the inputs
         copied in from pinned memory and the layer's result copied back, copies overlapped with compute."""
         main = torch.cuda.current_stream()
-        step_md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+        if args.e2e_host_metadata:
+            step_md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+        else:
+            # The serving form of the reference (PagedMetadata.from_device): the request-to-token table is
+            # state that lives on the device like the pool; the step's slot, request and position vectors
+            # come from pinned host memory and are validated against the table on the GPU.
+            # Validation and its read-back run on the copy stream, so the host does not wait for the previous
+            # step's layers still queued on the compute stream.
+            with torch.cuda.stream(copy_in):
+                index = [t.to(dev, non_blocking=True) for t in host_index]
+                step_md = rt.PagedMetadata.from_device(*index, table_dev, prefix_list, length_list, slots)
+            for t in index + [step_md.row_locations(), step_md.rotary_header()]:
+                t.record_stream(main)                 # allocated on the copy stream, consumed on the compute stream
+            main.wait_stream(copy_in)
         step_md.attention_plan(hq, hkv, d)
         staged = {}
 
@@ -567,7 +586,8 @@ def run_b200(args):
             (2 if w.front else 0)
         if row_parallel is not None:       # rotary, store, attention (+ combine), o_proj, (barrier), sum + add + norm
             mine_per_layer = 5 + (1 if len(combine) else 0) + (1 if row_parallel.mode == "push" else 0)
-    h2d = sum(h[0].numel() * 2 for h in host_in) * L + (3 * R + mapping.numel() + 1) * 4 + work.nbytes + \
+    index_bytes = (3 * R + mapping.numel() + 1) * 4 if args.e2e_host_metadata else (2 * R + B) * 4 + B * 16
+    h2d = sum(h[0].numel() * 2 for h in host_in) * L + index_bytes + work.nbytes + \
         (combine.nbytes if len(combine) else 0)
     line = {
         "metric": METRIC if w.chunk == 1 else "paged_prefill_tokens_per_s", "value": tokens_s, "unit": "tokens/s",
@@ -578,7 +598,10 @@ def run_b200(args):
         "kv_read_gbs_whole_step": kv_bytes * L * world / ms_per_step / 1e6,
         "roofline": roofline,
         "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(L * R * hq * world * d * 2)},
+                "d2h_bytes_per_step": int(L * R * hq * world * d * 2) + (0 if args.e2e_host_metadata else 24),
+                "metadata": ("validated on the host, request-to-token table uploaded every step" if args.e2e_host_metadata
+                             else "request-to-token table resident on the device; the step's slot / request / position "
+                                  "vectors copied from pinned host memory and validated on the GPU (24-byte read-back)")},
         "gpu_launches": args.steps * L * mine_per_layer,
         "launch_mode": "one CUDA graph per step, replayed" if graph is not None else "eager, kernel by kernel",
         "clocks": clocks.summary(),

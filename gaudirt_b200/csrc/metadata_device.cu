@@ -92,24 +92,33 @@ __global__ void prefix_kernel(const RowArgs a) {
   if (request < 0 || request >= a.n_requests) return;
   const int prefix = s.z, end = s.z + s.y;
   const int32_t* row = a.table + request * a.table_stride;
-  __shared__ int worst;
-  if (threadIdx.x == 0) worst = 0x7fffffff;
+  __shared__ int worst, page;
+  if (threadIdx.x == 0) {
+    worst = 0x7fffffff;
+    page = 0x40000000;
+  }
   __syncthreads();
-  int code = 0x7fffffff;
+  int code = 0x7fffffff, my_page = 0x40000000;
   for (int base = blockIdx.y * kPrefixChunk; base < end; base += gridDim.y * kPrefixChunk) {
     const int stop = min(end, base + kPrefixChunk);
     for (int p = base + threadIdx.x; p < stop; p += blockDim.x) {
       const int32_t slot = row[p];
       if (slot < 0 || (int64_t)slot >= a.slots) code = min(code, 6);
       else if (p < prefix && (a.written[slot >> 5] >> (slot & 31) & 1)) code = min(code, 7);
+      // A break in slot contiguity at position p only allows pages that end there.
+      if (p > 0 && slot != row[p - 1] + 1) my_page = min(my_page, p & -p);
     }
   }
   if (code != 0x7fffffff) atomicMin(&worst, code);
+  if (my_page != 0x40000000) atomicMin(&page, my_page);
   __syncthreads();
-  if (threadIdx.x == 0 && worst != 0x7fffffff) {
-    atomicCAS(a.row_status + s.x, 0, worst);
-    report(a.first_error, s.x, worst);
-    if (a.status) atomicOr(a.status, GK_DEV_BAD_METADATA);
+  if (threadIdx.x == 0) {
+    if (worst != 0x7fffffff) {
+      atomicCAS(a.row_status + s.x, 0, worst);
+      report(a.first_error, s.x, worst);
+      if (a.status) atomicOr(a.status, GK_DEV_BAD_METADATA);
+    }
+    if (page != 0x40000000) atomicMin(a.first_error + 2, (unsigned long long)page);
   }
 }
 
@@ -140,7 +149,7 @@ extern "C" int gk_paged_metadata_device_validate(
     return GK_ERR_INVALID_ARGUMENT;
   auto s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(workspace, 0, (size_t)(((uint64_t)slots + 31) / 32 * 4), s);
-  if (e == cudaSuccess) e = cudaMemsetAsync(first_error, 0xFF, 2 * sizeof(uint64_t), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(first_error, 0xFF, 3 * sizeof(uint64_t), s);
   if (e != cudaSuccess) {
     g_last_cuda_error = (int)e;
     return GK_ERR_CUDA;

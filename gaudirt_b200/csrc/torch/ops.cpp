@@ -164,7 +164,7 @@ class PagedMetadata : public torch::CustomClassHolder {
   // expands request ids to rows and checks every row and visible table entry.  With
   // `scheduler_owned` the table is vouched for by the scheduler (not re-checked) and a rejection
   // only sets GK_DEV_BAD_METADATA in the device status word, so nothing synchronises; otherwise
-  // the 16-byte verdict is read back and a rejection raises here.
+  // the 24-byte verdict is read back and a rejection raises here.
   PagedMetadata(const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions,
                 const at::Tensor& mapping, std::vector<int64_t> prefixes, std::vector<int64_t> lengths, int64_t slots,
                 const at::Tensor& token_ids, int64_t vocabulary, bool scheduler_owned) {
@@ -231,7 +231,7 @@ class PagedMetadata : public torch::CustomClassHolder {
     uint64_t workspace_bytes = 0;
     check_status(gk_paged_metadata_device_workspace_bytes(slots, &workspace_bytes), "device metadata");
     auto workspace = at::empty({static_cast<int64_t>(workspace_bytes)}, at::TensorOptions().dtype(at::kByte).device(device));
-    auto verdict = at::empty({2}, at::TensorOptions().dtype(at::kLong).device(device));
+    auto verdict = at::empty({3}, at::TensorOptions().dtype(at::kLong).device(device));
     const int wide = (loc.scalar_type() == at::kLong ? 1 : 0) | (req.scalar_type() == at::kLong ? 2 : 0) |
                      (pos.scalar_type() == at::kLong ? 4 : 0) | (has_tokens && tok.scalar_type() == at::kLong ? 8 : 0);
     const auto stream = at::cuda::getCurrentCUDAStream(device.index());
@@ -246,9 +246,13 @@ class PagedMetadata : public torch::CustomClassHolder {
                      device_status(device.index()).data_ptr<int32_t>(), stream_of(stream)),
                  "device metadata");
     if (!scheduler_owned) {
-      const auto host = verdict.cpu();   // 16 bytes: the only read-back of the step
+      const auto host = verdict.cpu();   // 24 bytes: the only read-back of the step
       const uint64_t first = static_cast<uint64_t>(host.data_ptr<int64_t>()[0]);
       const uint64_t token = static_cast<uint64_t>(host.data_ptr<int64_t>()[1]);
+      // Largest page the visible table ranges are contiguous in: the kernels then walk one table
+      // entry per page and the prefill kernel may fetch whole pages by TMA.
+      const uint64_t page = static_cast<uint64_t>(host.data_ptr<int64_t>()[2]);
+      page_tokens_ = static_cast<int64_t>(std::min<uint64_t>(page, 128));
       if (first != UINT64_MAX || token != UINT64_MAX) clear_status_bits(device.index(), GK_DEV_BAD_METADATA);
       TORCH_CHECK(first == UINT64_MAX, "GaudiRT device metadata: invalid scheduler metadata at row ", first >> 8,
                   ", code ", first & 255);

@@ -317,8 +317,10 @@ GK_API int gk_advance_decode_lengths(const int64_t* seq_lens, const int32_t* ori
  *   5 position != prefix + offset in its sequence       6 visible table entry outside [0, slots)
  *   7 cached-prefix entry names a slot this step writes
  * (6 and 7 are charged to the first row of the sequence), token_status[rows] (1 = token outside
- * [0, vocabulary)), first_error[0] = min over bad rows of (row << 8 | code), first_error[1] =
- * first row with a bad token, both UINT64_MAX when clean.  table == NULL (a table owned and
+ * [0, vocabulary)), first_error[3]: [0] = min over bad rows of (row << 8 | code), [1] = first row
+ * with a bad token, both UINT64_MAX when clean, [2] = the smallest (p & -p) over the visible
+ * positions p where table[p] != table[p-1] + 1, i.e. the largest power-of-two page size whose
+ * pages are slot-contiguous in every visible range (UINT64_MAX: no break at all).  table == NULL (a table owned and
  * vouched for by the scheduler) skips 3, 6 and 7.  Any rejection also sets GK_DEV_BAD_METADATA
  * in *status (may be NULL).  `workspace`: gk_paged_metadata_device_workspace_bytes(slots) bytes.
  * Rejected entries are replaced by 0 in the int32 outputs so later kernels stay in bounds. */

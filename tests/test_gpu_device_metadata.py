@@ -65,6 +65,29 @@ def test_accepts_and_expands(rt, rows):
     assert rt._C._take_device_status() == 0
 
 
+def test_page_size_is_detected_on_the_device(rt):
+    """The device form finds the same page granularity as the host form (largest power of two <= 128 whose
+    pages are slot-contiguous in every visible range)."""
+    assert build(rt, *batch(33)[:6]).page_tokens() == 128             # each request's slots are one run
+    for page in (16, 64):
+        n_req, context = 3, 256
+        gen = torch.Generator().manual_seed(page)
+        blocks = torch.randperm(n_req * context // page, generator=gen).view(n_req, context // page)
+        mapping = (blocks[:, :, None] * page * 2 + 1 + torch.arange(page)[None, None, :]).reshape(n_req, context)
+        mapping = mapping.to(torch.int32)                               # pages start 2 * page apart: never adjacent
+        prefixes, lengths = [40, 0, 200], [3, 70, 1]
+        requests = torch.tensor([2, 0, 1])
+        positions = torch.cat([torch.arange(p, p + l) for p, l in zip(prefixes, lengths)])
+        row_requests = torch.repeat_interleave(requests, torch.tensor(lengths))
+        locations = mapping[row_requests, positions].long()
+        slots = int(mapping.max()) + 1
+        md = rt.PagedMetadata.from_device(locations.to(DEV), requests.to(DEV), positions.to(DEV), mapping.to(DEV),
+                                          prefixes, lengths, slots)
+        host = rt.PagedMetadata(locations, row_requests, positions, mapping, slots)
+        assert md.page_tokens() == host.page_tokens() == page
+    assert rt._C._take_device_status() == 0
+
+
 def rejected(rt, values, code):
     want, _ = oracle.device_metadata_status(*[v.tolist() if torch.is_tensor(v) else v for v in values], SLOTS)
     assert code in want
