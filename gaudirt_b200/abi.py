@@ -50,6 +50,9 @@ PROTOTYPES = {
     "gk_oproj_bf16": (i32, [vp, i64, vp, i64, i64, i64, i64, vp, i32, i64, vp, vp]),
     "gk_rank_sum_bf16": (i32, [vp, i32, i64, vp, vp]),
     "gk_rank_sum_add_rms_norm_bf16": (i32, [vp, i32, i64, vp, vp, f32, f32, i64, i64, i64, vp, vp, vp]),
+    "gk_vocab_argmax": (i32, [vp, i32, i64, i64, i64, vp, vp]),
+    "gk_apply_vocab_bitmask": (i32, [vp, i32, i64, i64, i64, vp, i64, i64, vp, i64, i64, i32, vp, vp]),
+    "gk_sample_vocab": (i32, [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, vp, i32, C.c_uint64, i32, vp, vp]),
     "gk_paged_attn_static_scratch_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, i64,
                                                 vp, i64, f32, f32, i32, i32, i32, i32, vp, vp]),
 }

@@ -16,6 +16,7 @@
 #include <cstring>
 #include <memory>
 #include <mutex>
+#include <random>
 #include <tuple>
 #include <utility>
 #include <vector>
@@ -926,6 +927,137 @@ std::tuple<at::Tensor, at::Tensor> rank_sum_add_rms_norm(at::TensorList parts, c
   return {y, u};
 }
 
+// ---------------------------------------------------------------------------------------------
+// after the LM head: argmax, grammar bitmask, sampling (src/bridge/sampler_vocab.cpp:333-485)
+// ---------------------------------------------------------------------------------------------
+void require_logits(const at::Tensor& logits, const char* what) {
+  TORCH_CHECK(logits.defined() && logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 &&
+                  (logits.scalar_type() == at::kBFloat16 || logits.scalar_type() == at::kFloat),
+              "GaudiRT ", what, ": logits must be a 2D bf16 or fp32 tensor on the active device");
+}
+
+at::Tensor vocabulary_argmax(const at::Tensor& logits) {
+  require_logits(logits, "argmax");
+  TORCH_CHECK(logits.size(1) > 0, "GaudiRT argmax: empty vocabulary");
+  auto out = at::empty({logits.size(0)}, logits.options().dtype(at::kLong));
+  const auto device = logits.device();
+  c10::cuda::CUDAGuard guard(device);
+  check_status(gk_vocab_argmax(logits.data_ptr(), logits.scalar_type() == at::kFloat, logits.size(0), logits.size(1),
+                               logits.stride(0), out.data_ptr<int64_t>(),
+                               stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "argmax");
+  return out;
+}
+
+at::Tensor batch_vector(const at::Tensor& tensor, int64_t batch, at::ScalarType dtype, const char* name,
+                        const c10::Device& device) {
+  TORCH_CHECK(tensor.defined(), "GaudiRT sampler: missing required ", name);
+  TORCH_CHECK(tensor.scalar_type() == dtype, "GaudiRT sampler: unexpected dtype for ", name);
+  at::Tensor flat;
+  if (tensor.dim() == 1 && tensor.size(0) == batch) flat = tensor;
+  else if (tensor.dim() == 2 && tensor.size(0) == batch && tensor.size(1) == 1) flat = tensor.reshape({batch});
+  else if (tensor.numel() == 1 && tensor.dim() <= 2) flat = tensor.reshape({1}).expand({batch});
+  else TORCH_CHECK(false, "GaudiRT sampler: invalid shape for ", name);
+  return flat.to(device, /*non_blocking=*/true).contiguous();
+}
+
+at::Tensor sample_from_logits(const at::Tensor& logits, const at::Tensor& temperatures, const at::Tensor& top_ps,
+                              const at::Tensor& top_ks, const at::Tensor& min_ps, const c10::optional<at::Tensor>& seeds,
+                              const c10::optional<at::Tensor>& positions, bool nan_to_neg_inf) {
+  require_logits(logits, "sampler");
+  const int64_t batch = logits.size(0), vocabulary = logits.size(1);
+  TORCH_CHECK(batch > 0 && batch <= (int64_t{1} << 30) && vocabulary > 0 && vocabulary <= INT32_MAX,
+              "GaudiRT sampler: logits shape outside supported range");
+  const auto device = logits.device();
+  c10::cuda::CUDAGuard guard(device);
+  const auto temperature = batch_vector(temperatures, batch, at::kFloat, "temperatures", device);
+  const auto top_p = batch_vector(top_ps, batch, at::kFloat, "top_ps", device);
+  const auto top_k = batch_vector(top_ks, batch, at::kInt, "top_ks", device);
+  const auto min_p = batch_vector(min_ps, batch, at::kFloat, "min_ps", device);
+  at::Tensor seed, position;
+  const bool has_seeds = seeds.has_value() && seeds->defined();
+  if (has_seeds) {
+    seed = batch_vector(*seeds, batch, at::kLong, "seeds", device);
+    if (positions.has_value() && positions->defined()) {
+      TORCH_CHECK(positions->scalar_type() == at::kInt || positions->scalar_type() == at::kLong,
+                  "GaudiRT sampler: positions must be int32 or int64");
+      position = batch_vector(*positions, batch, positions->scalar_type(), "positions", device);
+    }
+  }
+  // Unseeded calls draw a fresh base from a process-wide generator, per call.
+  static std::mutex mutex;
+  static std::mt19937_64 generator{std::random_device{}()};
+  uint64_t base = 0;
+  if (!has_seeds) {
+    std::lock_guard<std::mutex> lock(mutex);
+    base = generator();
+  }
+  auto out = at::empty({batch}, logits.options().dtype(at::kInt));
+  check_status(gk_sample_vocab(logits.data_ptr(), logits.scalar_type() == at::kFloat, batch, vocabulary, logits.stride(0),
+                               temperature.data_ptr<float>(), top_p.data_ptr<float>(), top_k.data_ptr<int32_t>(),
+                               min_p.data_ptr<float>(), has_seeds ? seed.data_ptr<int64_t>() : nullptr,
+                               position.defined() ? position.data_ptr() : nullptr,
+                               position.defined() && position.scalar_type() == at::kLong, base, nan_to_neg_inf,
+                               out.data_ptr<int32_t>(), stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "sampler");
+  return out;
+}
+
+at::Tensor& apply_token_bitmask_inplace_(at::Tensor& logits, const at::Tensor& bitmask,
+                                         const c10::optional<at::Tensor>& indices, int64_t vocab_size, bool mask_tail) {
+  TORCH_CHECK(logits.defined() && logits.is_cuda() && (logits.dim() == 1 || logits.dim() == 2) &&
+                  (logits.scalar_type() == at::kBFloat16 || logits.scalar_type() == at::kFloat),
+              "GaudiRT bitmask: logits must be a 1D or 2D bf16/fp32 tensor on the active device");
+  TORCH_CHECK(bitmask.defined() && bitmask.scalar_type() == at::kInt && (bitmask.dim() == 1 || bitmask.dim() == 2) &&
+                  (bitmask.device().is_cpu() || bitmask.device() == logits.device()),
+              "GaudiRT bitmask: bitmask must be a 1D or 2D int32 tensor on CPU or active device");
+  auto work = logits.dim() == 1 ? logits.unsqueeze(0) : logits;
+  TORCH_CHECK(work.stride(1) == 1, "GaudiRT bitmask: logits columns must be contiguous");
+  const auto device = logits.device();
+  c10::cuda::CUDAGuard guard(device);
+  auto mask = (bitmask.dim() == 1 ? bitmask.unsqueeze(0) : bitmask).to(device, /*non_blocking=*/true).contiguous();
+  const int64_t batch = work.size(0), cols = work.size(1), mask_rows = mask.size(0), mask_words = mask.size(1);
+  TORCH_CHECK(cols > 0 && cols <= INT32_MAX && mask_words > 0 && mask_words <= INT32_MAX,
+              "GaudiRT bitmask: invalid tensor dimensions");
+  const int64_t mask_bits = mask_words * 32;
+  int64_t active = std::min(cols, mask_bits);
+  if (vocab_size >= 0) {
+    TORCH_CHECK(vocab_size <= cols, "GaudiRT bitmask: vocab_size exceeds logits width");
+    TORCH_CHECK(mask_tail || vocab_size <= mask_bits, "GaudiRT bitmask: bitmask is smaller than vocab_size");
+    active = std::min(vocab_size, mask_bits);
+  }
+  at::Tensor rows;
+  int64_t listed = 0;
+  if (indices.has_value() && indices->defined()) {
+    const auto& idx = *indices;
+    TORCH_CHECK(idx.dim() <= 1 && (idx.scalar_type() == at::kInt || idx.scalar_type() == at::kLong) &&
+                    (idx.device().is_cpu() || idx.device() == device),
+                "GaudiRT bitmask: indices must be an int32 or int64 tensor on CPU or active device");
+    if (idx.numel() == 0) return logits;
+    if (idx.device().is_cpu()) {                              // host indices are checked here, device ones in the kernel
+      const auto host = idx.reshape({-1}).to(at::kLong);
+      for (int64_t i = 0; i < host.numel(); ++i) {
+        const int64_t row = host.data_ptr<int64_t>()[i];
+        TORCH_CHECK(row >= 0 && row < batch && row < mask_rows, "GaudiRT bitmask: index ", row,
+                    " out of bounds for logits/bitmask rows (", batch, "/", mask_rows, ")");
+      }
+    }
+    rows = idx.reshape({-1}).to(device, /*non_blocking=*/true).to(at::kInt).contiguous();
+    listed = rows.numel();
+  } else {
+    TORCH_CHECK(mask_rows == batch, "GaudiRT bitmask: bitmask row count (", mask_rows, ") must match logits batch (", batch,
+                ")");
+    if (batch == 0) return logits;
+  }
+  check_status(gk_apply_vocab_bitmask(work.data_ptr(), work.scalar_type() == at::kFloat, batch, cols, work.stride(0),
+                                      mask.data_ptr<int32_t>(), mask_rows, mask_words,
+                                      rows.defined() ? rows.data_ptr<int32_t>() : nullptr, listed, active, mask_tail,
+                                      device_status(device.index()).data_ptr<int32_t>(),
+                                      stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+               "bitmask");
+  return logits;
+}
+
 // Reads and clears the device status word of the current device (synchronises the stream).
 int64_t take_device_status() {
   auto& word = device_status(at::cuda::current_device());
@@ -990,6 +1122,11 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_allocate_paged_slots_into", &gaudirt_b200::allocate_paged_slots_into);
   m.def("_release_paged_slots", &gaudirt_b200::release_paged_slots);
   m.def("_advance_decode_lengths(Tensor seq_lens, Tensor orig_seq_lens) -> (Tensor, Tensor)");
+  m.def("sample_from_logits(Tensor logits, Tensor temperatures, Tensor top_ps, Tensor top_ks, Tensor min_ps, "
+        "Tensor? seeds=None, Tensor? positions=None, bool nan_to_neg_inf=True) -> Tensor");
+  m.def("apply_token_bitmask_inplace_(Tensor(a!) logits, Tensor bitmask, Tensor? indices=None, "
+        "int vocab_size=-1, bool mask_tail=False) -> Tensor(a!)");
+  m.def("_vocabulary_argmax(Tensor logits) -> Tensor");
   m.def("_oproj(Tensor input, Tensor weight) -> Tensor");
   m.def("_oproj_push(Tensor input, Tensor weight, Tensor(a!)[] outs) -> ()");
   m.def("_rank_sum(Tensor[] parts) -> Tensor");
@@ -1009,6 +1146,9 @@ TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("rotary_embedding_positions", TORCH_FN(gaudirt_b200::rotary_embedding_positions));
   m.impl("_rotary_embedding_validated", TORCH_FN(gaudirt_b200::rotary_embedding_validated));
   m.impl("_advance_decode_lengths", TORCH_FN(gaudirt_b200::advance_decode_lengths));
+  m.impl("sample_from_logits", TORCH_FN(gaudirt_b200::sample_from_logits));
+  m.impl("apply_token_bitmask_inplace_", TORCH_FN(gaudirt_b200::apply_token_bitmask_inplace_));
+  m.impl("_vocabulary_argmax", TORCH_FN(gaudirt_b200::vocabulary_argmax));
   m.impl("_oproj", TORCH_FN(gaudirt_b200::oproj));
   m.impl("_oproj_push", TORCH_FN(gaudirt_b200::oproj_push));
   m.impl("_rank_sum", TORCH_FN(gaudirt_b200::rank_sum));

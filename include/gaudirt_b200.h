@@ -360,6 +360,36 @@ GK_API int gk_rank_sum_add_rms_norm_bf16(const void* const* parts, int world, in
                                   int64_t residual_row_stride, void* y, void* u,
                                   gk_stream_t stream);
 
+/* ---- after the LM head ------------------------------------------------------------------------
+ * Replace gk_argmax_parts/finish, gk_apply_vocab_bitmask_{f32,bf16} and gk_sample_vocab_{f32,bf16}
+ * (src/bridge/argmax_vocab.cpp, src/bridge/sampler_vocab.cpp:289-485).  logits: [rows, cols] bf16
+ * (is_f32 = 0) or fp32 (is_f32 = 1), row stride in elements, columns contiguous.
+ * gk_vocab_argmax: out[row] = index of the maximum with torch.argmax's rules (NaN is the largest
+ * value, the first of equal values wins, -0 == +0).
+ * gk_apply_vocab_bitmask: for every listed row (all rows, or row_indices[n_indices] on the device;
+ * duplicates are harmless, an index outside the logits or the mask sets GK_DEV_BAD_METADATA and is
+ * skipped) column c becomes -inf when c < active_cols and bit (c & 31) of bitmask[row][c >> 5] is 0,
+ * or when c >= active_cols and mask_tail is set; every other element is left untouched.
+ * gk_sample_vocab: one token per row.  temperature <= 0: the argmax (NaN counted as -inf when
+ * nan_to_neg_inf).  Otherwise, with w = exp((x - max) / temperature): keep w >= the top_k-th
+ * largest w (top_k outside [1, cols) keeps all), of those keep w >= the largest t whose mass
+ * {w >= t} reaches top_p of the kept mass, keep w >= min_p; draw from the kept set in proportion to
+ * w.  The draw is a pure function of (logits row, parameters, seeds[row], positions[row]):
+ * u = splitmix64(splitmix64(seed ^ splitmix64(position))) scaled to the kept mass, masses summed
+ * in 2^-40 fixed point.  seeds == NULL: rows are seeded from base_seed; positions may be NULL. */
+GK_API int gk_vocab_argmax(const void* logits, int is_f32, int64_t rows, int64_t cols,
+                    int64_t row_stride, int64_t* out, gk_stream_t stream);
+GK_API int gk_apply_vocab_bitmask(void* logits, int is_f32, int64_t rows, int64_t cols,
+                           int64_t row_stride, const int32_t* bitmask, int64_t mask_rows,
+                           int64_t mask_words, const int32_t* row_indices, int64_t n_indices,
+                           int64_t active_cols, int mask_tail, int32_t* status,
+                           gk_stream_t stream);
+GK_API int gk_sample_vocab(const void* logits, int is_f32, int64_t rows, int64_t cols,
+                    int64_t row_stride, const float* temperatures, const float* top_ps,
+                    const int32_t* top_ks, const float* min_ps, const int64_t* seeds,
+                    const void* positions, int positions_are_i64, uint64_t base_seed,
+                    int nan_to_neg_inf, int32_t* out, gk_stream_t stream);
+
 /* ---- attention without any device allocation ---------------------------------------------
  * This entry point has no counterpart in the reference.  It is for callers that must not
  * allocate device memory on their hot path: a serving engine that has handed all HBM to its own

@@ -28,7 +28,8 @@ __all__ = [
     "isolated_errors", "fp32_softmax_gate", "tile_indices", "tile_softmax", "online_merge",
     "online_finalize", "split_kv_attend", "rms_norm", "fused_add_rms_norm", "rotary_embedding",
     "rotary_cache", "validate_paged_metadata", "allocate_paged_slots", "release_paged_slots",
-    "device_metadata_status", "gather_dim_last", "linear_bf16", "canonical_rank_sum",
+    "device_metadata_status", "gather_dim_last", "linear_bf16", "canonical_rank_sum", "apply_vocab_bitmask",
+    "sampling_support",
 ]
 
 # KV tile of the reference's multi-tile path (src/bridge/paged_metadata.hpp:15, exposed to
@@ -555,3 +556,52 @@ def canonical_rank_sum(tensors):
     for part in tensors:
         total = part.to(torch.float32) if total is None else total + part.to(torch.float32)
     return total.to(tensors[0].dtype)
+
+
+def apply_vocab_bitmask(logits, bitmask, indices=None, vocab_size=-1, mask_tail=False):
+    """Grammar bitmask (rule of ``tests/vocab_bitmask_device_smoke.py:14-33``): in every listed row,
+    column ``c < active`` becomes ``-inf`` when bit ``c & 31`` of word ``c >> 5`` of the row's mask is
+    clear, columns ``>= active`` become ``-inf`` only with ``mask_tail``; ``active`` is the smaller of
+    the mask's bit count and ``vocab_size`` (the logits width when negative).  Returns a new tensor."""
+    out = logits.clone()
+    work = out.view(1, -1) if out.dim() == 1 else out
+    masks = bitmask.view(1, -1) if bitmask.dim() == 1 else bitmask
+    cols = work.size(1)
+    active = min(cols if vocab_size < 0 else vocab_size, masks.size(1) * 32)
+    column = torch.arange(cols)
+    rows = range(work.size(0)) if indices is None else sorted({int(i) for i in indices.reshape(-1).tolist()})
+    for r in rows:
+        words = masks[r].to(torch.int64) & 0xFFFFFFFF
+        allowed = (words[(column.clamp(max=max(active, 1) - 1)) >> 5] >> (column & 31)) & 1
+        banned = torch.where(column < active, allowed == 0, torch.full((cols,), bool(mask_tail)))
+        work[r, banned] = float("-inf")
+    return out
+
+
+def sampling_support(row, temperature, top_p, top_k, min_p, nan_to_neg_inf=True):
+    """Tokens a draw may return for one row under this build's sampling rule (the reference's
+    sampling kernel is not in its tree; its test, ``tests/sampler_vocab_device_smoke.py:24-88``,
+    pins the support in a few scenarios and the distribution, not the algorithm): with
+    ``w = exp((x - max) / temperature)``, keep ``w >=`` the ``top_k``-th largest, of those the
+    smallest high-``w`` set (ties kept) whose mass reaches ``top_p`` of theirs, and ``w >= min_p``.
+    ``temperature <= 0`` gives the argmax, lowest index first.  Returns ``(indices, probabilities)``
+    in binary64; thresholds closer than a few fp32 ulps to a weight are the caller's to avoid."""
+    x = row.double().clone()
+    if nan_to_neg_inf:
+        x[torch.isnan(x)] = float("-inf")
+    if not temperature > 0:
+        return torch.tensor([int(torch.argmax(x))]), torch.tensor([1.0], dtype=torch.float64)
+    w = torch.exp((x - x.max()) / temperature)
+    keep = torch.ones_like(w, dtype=torch.bool)
+    if 1 <= top_k < w.numel():
+        keep &= w >= torch.sort(w, descending=True).values[top_k - 1]
+    if top_p < 1.0:
+        order = torch.argsort(torch.where(keep, w, torch.zeros_like(w)), descending=True)
+        sorted_w = torch.where(keep, w, torch.zeros_like(w))[order]
+        need = top_p * sorted_w.sum()
+        reached = int(torch.nonzero(torch.cumsum(sorted_w, 0) >= need)[0])
+        keep &= w >= sorted_w[reached]
+    if min_p > 0:
+        keep &= w >= min_p
+    indices = torch.nonzero(keep).reshape(-1)
+    return indices, w[indices] / w[indices].sum()
