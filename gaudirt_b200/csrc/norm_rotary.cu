@@ -65,18 +65,25 @@ struct PartList {
 // (tests/tp4_gather_reduce_smoke.py:16-20): fp32 accumulator seeded with rank 0, one fp32 add per
 // further rank, one rounding to bf16.  Loads bypass L1: the partials were written by other GPUs.
 __device__ __forceinline__ void rank_sum8(const PartList& parts, int64_t offset, unsigned short (&out)[8]) {
+  // All ranks' vectors are requested before the first add, so their latencies overlap; the adds then
+  // run in rank order.
+  uint4 v[GK_MAX_OUTPUTS];
+#pragma unroll
+  for (int r = 0; r < GK_MAX_OUTPUTS; ++r)
+    if (r < parts.n) v[r] = __ldcg(reinterpret_cast<const uint4*>(parts.p[r] + offset));
   float acc[8];
   {
-    const uint4 a = __ldcg(reinterpret_cast<const uint4*>(parts.p[0] + offset));
-    const unsigned short* av = reinterpret_cast<const unsigned short*>(&a);
+    const unsigned short* av = reinterpret_cast<const unsigned short*>(&v[0]);
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = __uint_as_float((uint32_t)av[e] << 16);
   }
-  for (int r = 1; r < parts.n; ++r) {
-    const uint4 b = __ldcg(reinterpret_cast<const uint4*>(parts.p[r] + offset));
-    const unsigned short* bv = reinterpret_cast<const unsigned short*>(&b);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], __uint_as_float((uint32_t)bv[e] << 16));
+  for (int r = 1; r < GK_MAX_OUTPUTS; ++r) {
+    if (r < parts.n) {
+      const unsigned short* bv = reinterpret_cast<const unsigned short*>(&v[r]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], __uint_as_float((uint32_t)bv[e] << 16));
+    }
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) out[e] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[e]));

@@ -111,6 +111,15 @@ def _oproj(dev, peak, path):
               f"{bound_ms / ms:12.3f} {lib * 1e3:11.1f}")
         del sets
 
+    # the sum of 8 ranks' partials fused into the residual-add norm (the partials live on this GPU here)
+    sets = []
+    for i in range(6):
+        parts = torch.randn(8, 64, 8192, device=dev).to(torch.bfloat16)
+        sets.append((list(parts.unbind(0)), torch.randn(64, 8192, device=dev).to(torch.bfloat16),
+                     torch.ones(8192, dtype=torch.bfloat16, device=dev)))
+    ms = _time(lambda parts, res, w: torch.ops.gaudirt._rank_sum_add_rms_norm(parts, res, w, 1e-5, 1.0), sets, iters=30)
+    print(f"{'_rank_sum_add_rms_norm  8 ranks x 64 x 8192':44s} {ms * 1e3:8.1f} us  "
+          f"({(8 + 3) * 64 * 8192 * 2 / ms / 1e6:.0f} GB/s)")
 
 
 def _steps(rt, dev):
