@@ -163,7 +163,9 @@ def norm_rotary_cases(ref_tests):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    ref = sys.argv[1]
     ref_tests = os.path.join(ref, "tests")
     sys.path.insert(0, ref_tests)
     torch.set_num_threads(2)
