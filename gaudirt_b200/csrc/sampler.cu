@@ -22,7 +22,7 @@
 namespace gk {
 namespace {
 
-constexpr int kRowThreads = 1024;
+constexpr int kRowThreads = 512;        // several rows share an SM, so one row's barriers hide behind another's loads
 
 template <typename T>
 __device__ __forceinline__ float load_logit(const T* row, int64_t i);
@@ -31,6 +31,57 @@ __device__ __forceinline__ float load_logit<float>(const float* row, int64_t i) 
 template <>
 __device__ __forceinline__ float load_logit<unsigned short>(const unsigned short* row, int64_t i) {
   return __uint_as_float((uint32_t)row[i] << 16);
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& q, float (&v)[16 / sizeof(T)]);
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& q, float (&v)[4]) {
+  v[0] = __uint_as_float(q.x); v[1] = __uint_as_float(q.y); v[2] = __uint_as_float(q.z); v[3] = __uint_as_float(q.w);
+}
+template <>
+__device__ __forceinline__ void unpack16<unsigned short>(const uint4& q, float (&v)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    v[2 * e] = __uint_as_float(w[e] << 16);
+    v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+  }
+}
+
+// Visits every (index, value) of a row once, the whole CTA together: 16-byte loads when the row
+// starts on a 16-byte boundary, element loads otherwise and for the tail.  The order of visits is
+// not index order; every reduction built on it is order-independent.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_logit(const T* row, int64_t cols, F&& visit) {
+  constexpr int V = 16 / sizeof(T);
+  int64_t done = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // Four loads are requested before the first is used: a row is read by one CTA, so memory
+    // latency has to be covered by loads in flight per thread.
+    const int64_t vectors = cols / V, stride = blockDim.x;
+    int64_t v = threadIdx.x;
+    for (; v + 3 * stride < vectors; v += 4 * stride) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(row + (v + u * stride) * V);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float x[V];
+        unpack16<T>(q[u], x);
+#pragma unroll
+        for (int e = 0; e < V; ++e) visit((v + u * stride) * V + e, x[e]);
+      }
+    }
+    for (; v < vectors; v += stride) {
+      float x[V];
+      unpack16<T>(*reinterpret_cast<const uint4*>(row + v * V), x);
+#pragma unroll
+      for (int e = 0; e < V; ++e) visit(v * V + e, x[e]);
+    }
+    done = vectors * V;
+  }
+  for (int64_t i = done + threadIdx.x; i < cols; i += blockDim.x) visit(i, load_logit(row, i));
 }
 
 // Order-preserving key of a float for unsigned comparison; NaN sorts above +inf (torch.argmax
@@ -69,16 +120,38 @@ __device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long 
   return total;
 }
 
+// CTA-wide exclusive prefix sum in thread order; *total gets the sum over all threads.
+__device__ unsigned long long block_exclusive_scan_u64(unsigned long long v, unsigned long long* scratch,
+                                                       unsigned long long* total) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  unsigned long long mine = lane < (int)(blockDim.x >> 5) ? scratch[lane] : 0ull, across = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, across, o);
+    if (lane >= o) across += up;
+  }
+  *total = __shfl_sync(0xffffffffu, across, 31);
+  return __shfl_sync(0xffffffffu, across - mine, warp) + incl - v;
+}
+
 // (key << 32 | ~index): the maximum is the largest key at the lowest index.
 template <typename T>
 __device__ unsigned long long row_argmax(const T* row, int64_t cols, bool nan_is_lowest, unsigned long long* scratch) {
   unsigned long long best = 0;
-  for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float f = load_logit(row, i);
+  for_each_logit(row, cols, [&](int64_t i, float f) {
     if (nan_is_lowest && f != f) f = -CUDART_INF_F;
     const unsigned long long key = ((unsigned long long)order_key(f) << 32) | (0xffffffffu - (uint32_t)i);
     best = key > best ? key : best;
-  }
+  });
   return block_max_u64(best, scratch);
 }
 
@@ -93,7 +166,7 @@ __global__ void __launch_bounds__(kRowThreads) argmax_kernel(const T* __restrict
 // ---- grammar bitmask -------------------------------------------------------------------------
 // Column c of a listed row becomes -inf when c < active and bit c of the row's mask is 0, or when
 // c >= active and mask_tail is set (tests/vocab_bitmask_device_smoke.py:14-33).  Allowed entries
-// are not touched, so nothing is read from the logits at all.
+// keep their bits: 16-byte groups without a banned column are neither read nor written.
 template <typename T>
 __global__ void __launch_bounds__(256) bitmask_kernel(T* __restrict__ logits, int64_t rows, int64_t cols, int64_t row_stride,
                                                       const int32_t* __restrict__ bitmask, int64_t mask_rows,
@@ -126,11 +199,36 @@ __global__ void __launch_bounds__(256) bitmask_kernel(T* __restrict__ logits, in
       }
     }
     if (cols - c0 < 32) banned &= (1u << (cols - c0)) - 1u;
-    if (banned == 0xffffffffu && (reinterpret_cast<uintptr_t>(out + c0) & 15) == 0) {   // a whole word goes: 16-byte stores
+    if (banned == 0u) continue;
+    if ((reinterpret_cast<uintptr_t>(out + c0) & 15) == 0 && c0 + 32 <= cols) {
+      // 16-byte groups: a fully banned group is stored, a mixed one is read, blended and stored back
+      // (scattered 2- and 4-byte stores cost more than reading the sectors they would half-fill)
+      constexpr int V = 16 / sizeof(T);
       const uint32_t fill = sizeof(T) == 2 ? 0xff80ff80u : 0xff800000u;
       uint4* dst = reinterpret_cast<uint4*>(out + c0);
 #pragma unroll
-      for (int v = 0; v < (int)(32 * sizeof(T) / 16); ++v) dst[v] = make_uint4(fill, fill, fill, fill);
+      for (int g = 0; g < 32 / V; ++g) {
+        const uint32_t bits = (banned >> (g * V)) & ((1u << V) - 1u);
+        if (bits == 0u) continue;
+        uint4 q = make_uint4(fill, fill, fill, fill);
+        if (bits != (1u << V) - 1u) {
+          q = dst[g];
+          uint32_t w[4] = {q.x, q.y, q.z, q.w};
+          if (sizeof(T) == 2) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (bits >> (2 * e) & 1u) w[e] = (w[e] & 0xffff0000u) | 0xff80u;
+              if (bits >> (2 * e + 1) & 1u) w[e] = (w[e] & 0x0000ffffu) | 0xff800000u;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (bits >> e & 1u) w[e] = 0xff800000u;
+          }
+          q = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        dst[g] = q;
+      }
       continue;
     }
     while (banned) {
@@ -150,24 +248,29 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
 }
 
 constexpr int kDigitBits = 11, kBins = 1 << kDigitBits;     // radix-select digit; 32 bits = 11 + 11 + 10
-constexpr float kMassScale = 1099511627776.0f;              // 2^40
 
 struct SampleShared {
   unsigned long long scratch[32];
-  unsigned long long mass[kBins];
+  unsigned int mass_lo[kBins], mass_hi[kBins];   // 64-bit bin masses as two words: 32-bit shared atomics are native
   unsigned int count[kBins];
   unsigned long long found_mass;
-  unsigned int found_prefix, found_count;
-  int found_index;
+  unsigned int found_prefix;
 };
 
-template <typename T>
-__device__ __forceinline__ float weight_of(const T* row, int64_t i, float top, float inv_temp, bool nan_low) {
-  float f = load_logit(row, i);
+__device__ __forceinline__ float weight_of(float f, float top, float inv_temp, bool nan_low) {
   if (f != f) f = nan_low ? -CUDART_INF_F : top;            // an unfiltered NaN is treated like the maximum
   return __expf((f - top) * inv_temp);                       // in [0, 1]; exp(-inf) = 0
 }
-__device__ __forceinline__ unsigned long long mass_of(float w) { return (unsigned long long)(w * kMassScale); }
+// floor(w * 2^40) for 0 <= w <= 1, from the bits of w (a float -> 64-bit integer conversion
+// instruction runs at a small fraction of the rate of these few integer operations).
+__device__ __forceinline__ unsigned long long mass_of(float w) {
+  const uint32_t bits = __float_as_uint(w);
+  const int exponent = (int)(bits >> 23);                    // w >= 0: no sign bit
+  if (exponent == 0) return 0ull;                            // zero and subnormals: below 2^-40 anyway
+  const unsigned long long mantissa = (bits & 0x7fffffu) | 0x800000u;
+  const int shift = exponent - 110;                          // (exponent - 127) + 40 - 23
+  return shift >= 0 ? mantissa << shift : (shift > -24 ? mantissa >> -shift : 0ull);
+}
 
 // Threshold search over the bit pattern of w (non-negative floats order like unsigned integers),
 // most significant digit first.  BY_MASS: the largest t with mass{floor <= w, w >= t} >= target;
@@ -182,29 +285,62 @@ __device__ uint32_t select_threshold(const T* row, int64_t cols, float top, floa
     shift -= bits;
     const uint32_t above = shift + bits >= 32 ? 0u : (0xffffffffu << (shift + bits));
     for (int b = threadIdx.x; b < kBins; b += blockDim.x) {
-      sh->mass[b] = 0;
+      sh->mass_lo[b] = 0;
+      sh->mass_hi[b] = 0;
       sh->count[b] = 0;
     }
     __syncthreads();
-    for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-      const float w = weight_of(row, i, top, inv_temp, nan_low);
+    for_each_logit(row, cols, [&](int64_t, float f) {
+      const float w = weight_of(f, top, inv_temp, nan_low);
       const uint32_t u = __float_as_uint(w);
-      if (u < floor_bits || (u & above) != prefix) continue;
+      if (u < floor_bits || (u & above) != prefix) return;
       const uint32_t digit = (u >> shift) & ((1u << bits) - 1u);
-      if (BY_MASS) atomicAdd(&sh->mass[digit], mass_of(w));
-      else atomicAdd(&sh->count[digit], 1u);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {                                 // walk the bins from the top until the target is covered
-      unsigned long long have = 0;
-      int digit = (1 << bits) - 1;
-      for (; digit > 0; --digit) {
-        const unsigned long long here = BY_MASS ? sh->mass[digit] : (unsigned long long)sh->count[digit];
-        if (have + here >= target) break;
-        have += here;
+      if (BY_MASS) {
+        // exact 64-bit add out of 32-bit atomics: the carry out of the low word is counted separately
+        const unsigned long long mass = mass_of(w);
+        const uint32_t low = (uint32_t)mass, high = (uint32_t)(mass >> 32);
+        if (low) {
+          const uint32_t before = atomicAdd(&sh->mass_lo[digit], low);
+          if (before > 0xffffffffu - low) atomicAdd(&sh->mass_hi[digit], 1u);
+        }
+        if (high) atomicAdd(&sh->mass_hi[digit], high);
+      } else {
+        atomicAdd(&sh->count[digit], 1u);
       }
-      sh->found_prefix = prefix | ((uint32_t)digit << shift);
-      sh->found_mass = have;
+    });
+    __syncthreads();
+    // Find the bin, counted from the top, at which the running total first reaches the target: thread t
+    // owns the four bins below 4t from the top, an exclusive scan over threads gives what lies above
+    // them.  (No thread finds one when everything together falls short: bin 0 is taken then.)
+    {
+      const int n_bins = 1 << bits;
+      unsigned long long value[4], mine = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int b = n_bins - 1 - (4 * (int)threadIdx.x + k);
+        value[k] = b < 0 ? 0ull
+                         : (BY_MASS ? ((unsigned long long)sh->mass_hi[b] << 32) | sh->mass_lo[b] : (unsigned long long)sh->count[b]);
+        mine += value[k];
+      }
+      unsigned long long total;
+      unsigned long long over = block_exclusive_scan_u64(mine, sh->scratch, &total);
+      if (threadIdx.x == 0) {
+        const unsigned long long lowest =
+            BY_MASS ? ((unsigned long long)sh->mass_hi[0] << 32) | sh->mass_lo[0] : (unsigned long long)sh->count[0];
+        sh->found_prefix = prefix;
+        sh->found_mass = total - lowest;
+      }
+      __syncthreads();
+      if (over < target && target <= over + mine) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (over < target && target <= over + value[k]) {
+            sh->found_prefix = prefix | ((uint32_t)(n_bins - 1 - (4 * (int)threadIdx.x + k)) << shift);
+            sh->found_mass = over;
+          }
+          over += value[k];
+        }
+      }
     }
     __syncthreads();
     prefix = sh->found_prefix;
@@ -246,29 +382,57 @@ sample_kernel(const T* __restrict__ logits, int64_t cols, int64_t row_stride, co
     const uint32_t kth = select_threshold<T, false>(row, cols, top, inv_temp, nl, 0u, (unsigned long long)k, &sh);
     floor_bits = kth > floor_bits ? kth : floor_bits;
   }
-  unsigned long long kept = 0;
-  for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    const float w = weight_of(row, i, top, inv_temp, nl);
-    if (__float_as_uint(w) >= floor_bits) kept += mass_of(w);
-  }
-  kept = block_sum_u64(kept, sh.scratch);
   const float top_p = top_ps[r];
-  if (top_p < 1.0f && kept > 0) {
-    const unsigned long long need = (unsigned long long)((double)kept * (double)fmaxf(top_p, 0.f));
-    floor_bits = select_threshold<T, true>(row, cols, top, inv_temp, nl, floor_bits, need > 0 ? need : 1, &sh);
-    kept = 0;
-    for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-      const float w = weight_of(row, i, top, inv_temp, nl);
+  if (top_p < 1.0f) {
+    unsigned long long kept = 0;
+    for_each_logit(row, cols, [&](int64_t, float f) {
+      const float w = weight_of(f, top, inv_temp, nl);
       if (__float_as_uint(w) >= floor_bits) kept += mass_of(w);
-    }
+    });
     kept = block_sum_u64(kept, sh.scratch);
+    if (kept > 0) {
+      const unsigned long long need = (unsigned long long)((double)kept * (double)fmaxf(top_p, 0.f));
+      floor_bits = select_threshold<T, true>(row, cols, top, inv_temp, nl, floor_bits, need > 0 ? need : 1, &sh);
+    }
   }
+
+  // Inverse transform in index order.  Thread t owns a contiguous run of columns, so an exclusive scan
+  // of the threads' kept masses is the running mass in index order; its total is the kept mass, the
+  // thread whose run contains u * kept walks it.
+  constexpr int V = 16 / sizeof(T);
+  const bool aligned = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const int64_t run = ((cols + blockDim.x - 1) / blockDim.x + V - 1) / V * V;
+  const int64_t lo = (int64_t)threadIdx.x * run, hi = lo + run < cols ? lo + run : cols;
+  auto kept_mass = [&](float f) {
+    const float w = weight_of(f, top, inv_temp, nl);
+    return __float_as_uint(w) >= floor_bits ? mass_of(w) : 0ull;
+  };
+  auto for_my_run = [&](auto&& visit) {                      // visit(index, value) in increasing index order
+    int64_t i = lo;
+    if (aligned) {
+      for (; i + 4 * V <= hi; i += 4 * V) {                  // four loads in flight
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(row + i + u * V);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float x[V];
+          unpack16<T>(q[u], x);
+#pragma unroll
+          for (int e = 0; e < V; ++e) visit(i + u * V + e, x[e]);
+        }
+      }
+    }
+    for (; i < hi; ++i) visit(i, load_logit(row, i));
+  };
+  unsigned long long mine = 0;
+  for_my_run([&](int64_t, float f) { mine += kept_mass(f); });
+  unsigned long long kept;
+  const unsigned long long before = block_exclusive_scan_u64(mine, sh.scratch, &kept);
   if (kept == 0) {
     if (threadIdx.x == 0) out[r] = greedy;
     return;
   }
-
-  // Inverse transform in index order: the first index whose running mass exceeds u * kept.
   unsigned long long seed = seeds ? (unsigned long long)seeds[r] : splitmix64(base_seed + (unsigned long long)r);
   if (seeds && positions) {
     const unsigned long long p = positions_wide ? (unsigned long long)static_cast<const int64_t*>(positions)[r]
@@ -276,53 +440,20 @@ sample_kernel(const T* __restrict__ logits, int64_t cols, int64_t row_stride, co
     seed = splitmix64(seed ^ splitmix64(p));
   }
   const unsigned long long target = __umul64hi(splitmix64(seed), kept);      // uniform in [0, kept)
-  if (threadIdx.x == 0) sh.found_index = greedy;
-  unsigned long long running = 0;
-  const int64_t tile = (int64_t)blockDim.x * 4;
-  for (int64_t base = 0; base < cols; base += tile) {
-    // thread t owns 4 consecutive columns of the tile, so index order = thread order
-    unsigned long long mine[4], sum = 0;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t i = base + (int64_t)threadIdx.x * 4 + e;
-      float w = 0.f;
-      if (i < cols) {
-        w = weight_of(row, i, top, inv_temp, nl);
-        if (__float_as_uint(w) < floor_bits) w = 0.f;
+  if (target >= before && target < before + mine) {                          // exactly one thread
+    unsigned long long at = before;
+    int found = greedy;
+    bool done = false;
+    for_my_run([&](int64_t i, float f) {
+      const unsigned long long mass = kept_mass(f);
+      if (!done && target < at + mass) {
+        found = (int)i;
+        done = true;
       }
-      mine[e] = mass_of(w);
-      sum += mine[e];
-    }
-    // inclusive scan over threads
-    unsigned long long incl = sum;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    __syncthreads();
-    if (lane == 31) sh.scratch[warp] = incl;
-    __syncthreads();
-    unsigned long long before = 0, total = 0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
-      if (w < warp) before += sh.scratch[w];
-      total += sh.scratch[w];
-    }
-    const unsigned long long start = running + before + incl - sum;      // mass in front of this thread
-    if (target >= start && target < start + sum) {
-      unsigned long long at = start;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (target >= at && target < at + mine[e]) sh.found_index = (int)(base + (int64_t)threadIdx.x * 4 + e);
-        at += mine[e];
-      }
-    }
-    running += total;
-    if (running > target) break;                             // uniform across the CTA
+      at += mass;
+    });
+    out[r] = found;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) out[r] = sh.found_index;
 }
 
 }  // namespace

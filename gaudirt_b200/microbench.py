@@ -1,6 +1,6 @@
 """Kernel-level timings of the small kernels of the path against the HBM roofline.
 
-    python -m gaudirt_b200.microbench [rows|oproj|steps ...]      (no argument: all sections)
+    python -m gaudirt_b200.microbench [rows|oproj|steps|vocab ...]      (no argument: all sections)
 
 Times `kv_store`, `fused_add_rms_norm`, `rotary_embedding` and the split-KV combine alone with CUDA
 events (inputs larger than L2 are cycled so no launch re-reads cached data) and prints algorithmic
@@ -43,6 +43,8 @@ def main(sections=()):
         _oproj(dev, peak, path)
     if want("steps"):
         _steps(rt, dev)
+    if want("vocab"):
+        _vocab(dev, peak)
 
 
 def _row_kernels(rows, H, dev, peak):
@@ -158,6 +160,39 @@ def _steps(rt, dev):
     for name, ms in steps:
         print(f"{name:72s} {ms * 1e3:9.1f} us per call")
     assert rt._C._take_device_status() == 0
+
+
+def _vocab(dev, peak):
+    # After the LM head: 256 rows x 131072 bf16 logits (67 MB per pass; more sets than L2 holds).
+    rows, vocab = 256, 131072
+    sets = [(torch.randn(rows, vocab, device=dev).mul_(3).to(torch.bfloat16),) for _ in range(4)]
+    nbytes = rows * vocab * 2
+    out = []
+    ms = _time(lambda x: torch.ops.gaudirt._vocabulary_argmax(x), sets)
+    out.append(("_vocabulary_argmax", ms, nbytes))
+    ms = _time(lambda x: torch.argmax(x, dim=-1), sets)
+    out.append(("torch.argmax (library)", ms, nbytes))
+    mask = torch.randint(-2 ** 31, 2 ** 31 - 1, (rows, vocab // 32), device=dev, dtype=torch.int64).to(torch.int32)
+    few = torch.zeros_like(mask)
+    few[:, 7] = 5                                                      # two allowed tokens per row: nearly all is written
+    ms = _time(lambda x: torch.ops.gaudirt.apply_token_bitmask_inplace_(x, mask), sets)
+    out.append(("apply_token_bitmask_inplace_  random mask (half banned)", ms, nbytes // 2))
+    ms = _time(lambda x: torch.ops.gaudirt.apply_token_bitmask_inplace_(x, few), sets)
+    out.append(("apply_token_bitmask_inplace_  2 tokens allowed", ms, nbytes))
+    sets = [(torch.randn(rows, vocab, device=dev).mul_(3).to(torch.bfloat16),) for _ in range(4)]
+    f32 = lambda v: torch.full((rows,), v, device=dev)
+    seeds, positions = torch.arange(rows, device=dev), torch.arange(rows, device=dev)
+    k_all, k_50 = torch.full((rows,), vocab, dtype=torch.int32, device=dev), torch.full((rows,), 50, dtype=torch.int32, device=dev)
+    for label, temp, top_p, top_k, min_p, passes in (("greedy (temperature 0)", 0.0, 1.0, k_all, 0.0, 1),
+                                                     ("temperature only", 0.8, 1.0, k_all, 0.0, 2),
+                                                     ("top_k 50 + top_p 0.9 + min_p 0.02", 0.8, 0.9, k_50, 0.02, 9)):
+        ms = _time(lambda x: torch.ops.gaudirt.sample_from_logits(x, f32(temp), f32(top_p), top_k, f32(min_p), seeds, positions, True),
+                   sets)
+        out.append((f"sample_from_logits  {label}", ms, nbytes * passes))
+    print()
+    print(f"{'256 x 131072 bf16 logits':66s} {'us':>8s} {'GB/s moved (all passes)':>24s} {'of copy peak':>13s}")
+    for name, ms, moved in out:
+        print(f"{name:66s} {ms * 1e3:8.1f} {moved / ms / 1e6:24.0f} {moved / ms / 1e6 / peak:13.3f}")
 
 
 if __name__ == "__main__":
