@@ -146,12 +146,27 @@ __device__ unsigned long long block_exclusive_scan_u64(unsigned long long v, uns
 // (key << 32 | ~index): the maximum is the largest key at the lowest index.
 template <typename T>
 __device__ unsigned long long row_argmax(const T* row, int64_t cols, bool nan_is_lowest, unsigned long long* scratch) {
-  unsigned long long best = 0;
+  // Per thread: a float maximum with its index (a thread meets its columns in increasing index
+  // order, so a strict comparison keeps the first of equals) and the first NaN; the 64-bit key is
+  // only built once per thread, for the reduction across the CTA.
+  float top = 0.f;
+  int top_at = 0x7fffffff, nan_at = 0x7fffffff;
   for_each_logit(row, cols, [&](int64_t i, float f) {
-    if (nan_is_lowest && f != f) f = -CUDART_INF_F;
-    const unsigned long long key = ((unsigned long long)order_key(f) << 32) | (0xffffffffu - (uint32_t)i);
-    best = key > best ? key : best;
+    if (f != f) {
+      if (!nan_is_lowest) {
+        nan_at = min(nan_at, (int)i);
+        return;
+      }
+      f = -CUDART_INF_F;
+    }
+    if (f > top || top_at == 0x7fffffff) {
+      top = f;
+      top_at = (int)i;
+    }
   });
+  unsigned long long best = 0;
+  if (nan_at != 0x7fffffff) best = (0xffffffffull << 32) | (0xffffffffu - (uint32_t)nan_at);
+  else if (top_at != 0x7fffffff) best = ((unsigned long long)order_key(top) << 32) | (0xffffffffu - (uint32_t)top_at);
   return block_max_u64(best, scratch);
 }
 
