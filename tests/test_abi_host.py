@@ -144,3 +144,52 @@ def test_slot_layout_records_and_errors():
                        (([-1], [4], 16, 2), b"invalid request lengths"), (([0], [4], 0, 2), b"unsupported page size"),
                        (([1 << 31], [4], 16, 2), b"invalid request lengths")):
         assert layout(*args)[0] == 5 and text in lib.gk_metadata_error()
+
+
+def test_entry_points_reject_bad_arguments_before_touching_the_device():
+    """Every check below fails in the host-side argument validation, so it runs without a GPU."""
+    import ctypes as C
+    lib = abi.lib()
+    INVALID, UNSUPPORTED = 1, 2
+    buf = (C.c_char * 4096)()
+    a16 = (C.addressof(buf) + 255) & ~255                                  # a 256-byte aligned host address stands in
+    ptr = C.c_void_p(a16)
+    odd = C.c_void_p(a16 + 2)
+    outs = (C.c_void_p * 1)(a16)
+    # o_proj: null pointers, misaligned operands, shapes the tiling does not cover
+    assert lib.gk_oproj_bf16(None, 64, ptr, 64, 8, 64, 64, outs, 1, 64, None, None) == INVALID
+    assert lib.gk_oproj_bf16(odd, 64, ptr, 64, 8, 64, 64, outs, 1, 64, None, None) == INVALID
+    assert lib.gk_oproj_bf16(ptr, 60, ptr, 64, 8, 64, 64, outs, 1, 64, None, None) == INVALID      # stride not 16-byte
+    assert lib.gk_oproj_bf16(ptr, 64, ptr, 64, 8, 96, 64, outs, 1, 96, None, None) == UNSUPPORTED  # n % 64
+    assert lib.gk_oproj_bf16(ptr, 100, ptr, 100, 8, 64, 100, outs, 1, 64, None, None) == UNSUPPORTED  # k % 64
+    assert lib.gk_oproj_bf16(ptr, 64, ptr, 64, 8, 64, 64, outs, 9, 64, None, None) == INVALID      # too many destinations
+    assert lib.gk_oproj_bf16(ptr, 64, ptr, 64, 0, 64, 64, outs, 1, 64, None, None) == 0            # nothing to do
+    # rank-ordered sum
+    parts = (C.c_void_p * 2)(a16, a16)
+    assert lib.gk_rank_sum_bf16(parts, 0, 64, ptr, None) == INVALID
+    assert lib.gk_rank_sum_bf16(parts, 2, 12, ptr, None) == UNSUPPORTED                             # count % 8
+    assert lib.gk_rank_sum_add_rms_norm_bf16(parts, 2, 64, ptr, ptr, 0.0, 0.0, 4, 64, 64, ptr, ptr, None) == INVALID  # eps
+    assert lib.gk_rank_sum_add_rms_norm_bf16(parts, 2, 16384, ptr, ptr, 1e-5, 0.0, 4, 16384, 16384, ptr, ptr, None) == UNSUPPORTED
+    # slot allocator
+    size = C.c_uint64(0)
+    assert lib.gk_paged_slots_release_workspace_bytes(5000, 512, C.byref(size)) == 0 and size.value == 2048 + 256
+    assert lib.gk_paged_slots_release_workspace_bytes(0, 512, C.byref(size)) == INVALID
+    assert lib.gk_paged_slots_release(ptr, 8, 16, 512, odd, ptr, ptr, None) == INVALID            # workspace alignment
+    assert lib.gk_paged_slots_allocate(ptr, ptr, odd, 1, 8, 16, ptr, None, 0, 0, 0, None, None, None, None) == INVALID
+    assert lib.gk_paged_slots_allocate(ptr, ptr, ptr, 1, 8, 0, ptr, None, 0, 0, 0, None, None, None, None) == INVALID
+    assert lib.gk_advance_decode_lengths(ptr, ptr, 0, ptr, ptr, None) == INVALID
+    # device metadata validation
+    assert lib.gk_paged_metadata_device_workspace_bytes(1 << 20, C.byref(size)) == 0 and size.value == (1 << 20) // 8
+    assert lib.gk_paged_metadata_device_workspace_bytes(0, C.byref(size)) == INVALID
+    assert lib.gk_paged_metadata_device_validate(ptr, ptr, ptr, None, 16, 0, ptr, 4, 64, 64, 100, ptr, 1, 1, ptr, ptr, ptr, ptr,
+                                                 None, None, ptr, None, ptr, None, None) == INVALID   # unknown width bit
+    assert lib.gk_paged_metadata_device_validate(ptr, ptr, ptr, None, 0, 0, ptr, 4, 64, 32, 100, ptr, 1, 1, ptr, ptr, ptr, ptr,
+                                                 None, None, ptr, None, ptr, None, None) == INVALID   # table stride < context
+    # after the LM head
+    assert lib.gk_vocab_argmax(ptr, 0, 4, 0, 0, ptr, None) == INVALID
+    assert lib.gk_apply_vocab_bitmask(ptr, 0, 4, 64, 64, ptr, 4, 1, None, 0, 64, 0, None, None) == INVALID   # 64 active > 32 mask bits
+    assert lib.gk_sample_vocab(ptr, 0, 4, 64, 64, ptr, ptr, ptr, ptr, None, ptr, 0, 0, 1, ptr, None) == INVALID  # positions without seeds
+    # peer barrier
+    flags = (C.c_void_p * 2)(a16, a16)
+    assert lib.gk_peer_barrier_counted(flags, 0, 2, None, 1000, None, None) == INVALID
+    assert lib.gk_peer_barrier(flags, 2, 2, 1, 1000, None, None) == INVALID
