@@ -26,9 +26,11 @@ __device__ __forceinline__ double bf16_to_double(unsigned short b) {
 }
 
 // bf16(x*c - y*s) resp. bf16(x*c + y*s), rounded once from the exact value, in fp32: the first
-// product of two bf16 values is exact, the fused multiply-add is evaluated toward zero and toward
-// +inf; if the two differ the result is inexact and the truncated one gets a sticky bit
-// (round-to-odd), which makes the final rounding to bf16 the rounding of the exact value.
+// product of two bf16 values is exact, the fused multiply-add is evaluated toward -inf and toward
+// +inf; if the two differ the result is inexact, and the one nearer zero (the truncation of the
+// exact value) gets a sticky bit (round-to-odd), which makes the final rounding to bf16 the
+// rounding of the exact value.  (Toward-zero against toward +inf alone would miss every inexact
+// negative result: both directions give the same float there.)
 __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned short c, unsigned short y,
                                                       unsigned short s, bool subtract) {
   const float xf = __uint_as_float((uint32_t)x << 16), cf = __uint_as_float((uint32_t)c << 16);
@@ -36,9 +38,9 @@ __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned
   const float sf = __uint_as_float((uint32_t)s << 16);
   if (subtract) yf = -yf;
   const float first = xf * cf;                                  // exact
-  const float toward_zero = __fmaf_rz(yf, sf, first), upward = __fmaf_ru(yf, sf, first);
-  float r = toward_zero;
-  if (toward_zero != upward) r = __uint_as_float(__float_as_uint(toward_zero) | 1u);
+  const float down = __fmaf_rd(yf, sf, first), up = __fmaf_ru(yf, sf, first);
+  float r = down < 0.f ? up : down;                             // toward zero
+  if (down != up) r = __uint_as_float(__float_as_uint(r) | 1u);
   return __bfloat16_as_ushort(__float2bfloat16_rn(r));
 }
 

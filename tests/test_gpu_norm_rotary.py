@@ -167,6 +167,51 @@ def test_rotary_with_metadata(rt, q_heads, k_heads, head_dim, rotary_dim, rows, 
             torch.ops.gaudirt.rotary_embedding(qd, kd, cache.to(DEV), md, head_dim, rotary_dim - 1, neox)
 
 
+def _hard_rotation_cases(count, seed=20261125):
+    """bf16 quadruples (a, b, cos, sin) for which a*cos - b*sin is inexact in fp32 and its fp32
+    truncation lies exactly on a bf16 rounding midpoint: rounding that truncation instead of the
+    exact value (a double rounding) gives the wrong bf16.  Both signs of the result are collected."""
+    rng = np.random.default_rng(seed)
+
+    def random_bf16(n):
+        x = (rng.standard_normal(n) * rng.choice([0.01, 0.3, 1.0, 7.0], n)).astype(np.float32)
+        u = x.view(np.uint32)
+        return ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).view(np.float32)
+
+    found = [np.empty((0, 4), np.float32)] * 2                       # [non-negative results, negative results]
+    while min(len(f) for f in found) < count:
+        a, b, c, s = (random_bf16(1 << 20) for _ in range(4))
+        exact = a.astype(np.float64) * c - b.astype(np.float64) * s   # exact in binary64
+        near = exact.astype(np.float32)
+        trunc = np.where(np.abs(near.astype(np.float64)) > np.abs(exact), np.nextafter(near, np.float32(0)), near)
+        hard = (trunc.astype(np.float64) != exact) & ((trunc.view(np.uint32) & 0xFFFF) == 0x8000)
+        for sign in (0, 1):
+            pick = hard & ((exact < 0) == bool(sign))
+            found[sign] = np.concatenate([found[sign], np.stack([a, b, c, s], 1)[pick]])
+    return np.concatenate([found[0][:count], found[1][:count]])
+
+
+def test_rotary_rounds_the_exact_value_for_both_signs(rt):
+    """Known hard inputs: the rotated element must be the rounding of the exact value, also when the
+    result is negative (directed roundings toward zero and toward +inf coincide there)."""
+    cases = _hard_rotation_cases(16)                                  # 32 quadruples, 4 per row
+    rows = len(cases) // 4
+    a, b, c, s = (torch.from_numpy(np.ascontiguousarray(cases[:, i])).view(rows, 4).to(torch.bfloat16) for i in range(4))
+    x = torch.cat([a, b], dim=1)                                      # neox pairs (i, i + 4) of one head of width 8
+    cache = torch.cat([c, s], dim=1)                                  # row r of the table: cos || sin
+    positions = torch.arange(rows, dtype=torch.int32)
+    truth = oracle.rotary_embedding(x, cache, positions, 8, 8, True, dtype=torch.float64)
+    want_first = oracle.bf16_from_f64(a.double() * c.double() - b.double() * s.double())
+    assert torch.equal(truth[:, :4], want_first)
+    naive = (a.float() * c.float() - b.float() * s.float()).to(torch.bfloat16).double()   # fp32 then bf16: double rounding
+    assert int((naive != want_first).sum()) >= 8, "the cases are meant to break a double rounding"
+    q_out, k_out = torch.ops.gaudirt.rotary_embedding_positions(x.to(DEV), x.to(DEV), cache.to(DEV), positions.to(DEV), 8, 8, True)
+    assert torch.equal(q_out.cpu().double(), truth) and torch.equal(k_out.cpu().double(), truth)
+    wide = torch.cat([x] * 16, dim=1)                                 # 16 heads: the 16-byte vector kernel
+    q_out, _ = torch.ops.gaudirt.rotary_embedding_positions(wide.to(DEV), x.to(DEV), cache.to(DEV), positions.to(DEV), 8, 8, True)
+    assert torch.equal(q_out.cpu().double(), torch.cat([truth] * 16, dim=1))
+
+
 def test_rotary_fused_with_kv_store_matches_the_two_kernels():
     gen = torch.Generator().manual_seed(5150)
     rows, q_heads, k_heads, d, slots = 64, 8, 1, 128, 4096
