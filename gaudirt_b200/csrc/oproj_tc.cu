@@ -12,8 +12,8 @@
 //              [BN x 64] of W, 128-byte swizzle, no multicast; rows past M are zero-filled by TMA
 //   warp 1     one thread issues tcgen05.mma.kind::f16 (M 128, N BN, K 16) four times per box and
 //              commits the stage back to the loader, finally the accumulators to the epilogue
-//   warps 2-5  epilogue: tcgen05.ld of the thread's row, rounding to bf16, row segments stored to
-//              every destination
+//   warps 2-5  epilogue: tcgen05.ld of the thread's row, rounding to bf16, the block staged in
+//              shared memory and stored to every destination as whole contiguous row segments
 // A kernel of this shape is bound by how fast one SM takes in operand boxes, so small problems are
 // cut along K over a thread-block cluster (2 or 4 CTAs per output block) until the grid fills the
 // GPU; the cluster adds its fp32 accumulators through distributed shared memory in a fixed order.
@@ -169,7 +169,6 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
     if (alive) tc_fence_after();
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-      const int64_t out_row = (int64_t)m0 + mt * kBM + row;
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t acc[32];
@@ -182,16 +181,44 @@ linear_tc_kernel(const LinearParams p, const __grid_constant__ CUtensorMap map_a
         if (split > 1) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) park[(mt * BN + c0 + c) * kBM + row] = __uint_as_float(acc[c]);
-        } else if (out_row < p.m) {
-          uint32_t packed[16];
+        } else if (p.n_outs == 1) {                         // one (local) destination: straight from registers
+          const int64_t out_row = (int64_t)m0 + mt * kBM + row;
+          if (out_row < p.m) {
+            uint4* dst = reinterpret_cast<uint4*>(p.outs[0] + out_row * p.out_stride + n0 + c0);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) packed[c] = pack_bf16(__uint_as_float(acc[2 * c]), __uint_as_float(acc[2 * c + 1]));
-          for (int o = 0; o < p.n_outs; ++o) {
-            uint4* dst = reinterpret_cast<uint4*>(p.outs[o] + out_row * p.out_stride + n0 + c0);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            for (int c = 0; c < 4; ++c)
+              dst[c] = make_uint4(pack_bf16(__uint_as_float(acc[8 * c]), __uint_as_float(acc[8 * c + 1])),
+                                  pack_bf16(__uint_as_float(acc[8 * c + 2]), __uint_as_float(acc[8 * c + 3])),
+                                  pack_bf16(__uint_as_float(acc[8 * c + 4]), __uint_as_float(acc[8 * c + 5])),
+                                  pack_bf16(__uint_as_float(acc[8 * c + 6]), __uint_as_float(acc[8 * c + 7])));
           }
+        } else {
+          // Several destinations (peers): the bf16 block is staged in shared memory ([mt][row][BN], 16-byte
+          // chunks XOR-swizzled by the row so that a thread-per-row write pattern is conflict-free) and
+          // stored row-contiguously below
+          uint4* stage = reinterpret_cast<uint4*>(base) + (mt * kBM + row) * (BN / 8);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            stage[(c0 / 8 + c) ^ (row & 7)] =
+                make_uint4(pack_bf16(__uint_as_float(acc[8 * c]), __uint_as_float(acc[8 * c + 1])),
+                           pack_bf16(__uint_as_float(acc[8 * c + 2]), __uint_as_float(acc[8 * c + 3])),
+                           pack_bf16(__uint_as_float(acc[8 * c + 4]), __uint_as_float(acc[8 * c + 5])),
+                           pack_bf16(__uint_as_float(acc[8 * c + 6]), __uint_as_float(acc[8 * c + 7])));
         }
+      }
+    }
+    if (split == 1 && p.n_outs > 1) {
+      // Coalesced stores: BN / 8 consecutive lanes write one row's BN * 2 contiguous bytes, to every
+      // destination (a peer's receive buffer gets whole 128-byte lines instead of 16-byte fragments).
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");         // the four epilogue warps only
+      constexpr int kChunks = BN / 8, kRowsPerPass = 128 / kChunks;
+      const int t = tid - 64, chunk = t % kChunks;
+      for (int r = t / kChunks; r < MT * kBM; r += kRowsPerPass) {
+        const int64_t out_row = (int64_t)m0 + r;
+        if (out_row >= p.m) break;                           // rows only grow with r
+        const uint4 v = reinterpret_cast<const uint4*>(base)[r * kChunks + (chunk ^ (r & 7))];
+        for (int o = 0; o < p.n_outs; ++o)
+          *reinterpret_cast<uint4*>(p.outs[o] + out_row * p.out_stride + n0 + chunk * 8) = v;
       }
     }
   }
