@@ -44,6 +44,22 @@ __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned
   return __bfloat16_as_ushort(__float2bfloat16_rn(r));
 }
 
+// bf16(a + b) of two bf16 values, rounded once from the exact sum, without leaving fp32: the add is
+// evaluated toward -inf and toward +inf; if the two differ the sum is inexact in fp32 and the one
+// nearer zero gets a sticky bit (round-to-odd) before the rounding to bf16.
+__device__ __forceinline__ unsigned short add_bf16_exact(unsigned short a, unsigned short b) {
+  const float af = __uint_as_float((uint32_t)a << 16), bf = __uint_as_float((uint32_t)b << 16);
+  const float down = __fadd_rd(af, bf), up = __fadd_ru(af, bf);
+  float r = up;                                                 // exact sum (x + -x gives +0 this way, as round-to-nearest does)
+  if (down != up) r = __uint_as_float(__float_as_uint(down < 0.f ? up : down) | 1u);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(r));
+}
+// u * u as a double: the square of a bf16 value has 16 significant bits, exact in fp32.
+__device__ __forceinline__ double square_bf16(unsigned short u) {
+  const float f = __uint_as_float((uint32_t)u << 16);
+  return (double)(f * f);
+}
+
 __device__ __forceinline__ double block_sum(double v, double* shared) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -135,17 +151,14 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
           uint4 b = __ldg(reinterpret_cast<const uint4*>(rr + col));
           const unsigned short* bv = reinterpret_cast<const unsigned short*>(&b);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) u[it][e] = bf16_from_double(bf16_to_double(av[e]) + bf16_to_double(bv[e]));
+          for (int e = 0; e < 8; ++e) u[it][e] = add_bf16_exact(av[e], bv[e]);
           *reinterpret_cast<uint4*>(ur + col) = *reinterpret_cast<const uint4*>(u[it]);
         } else {
 #pragma unroll
           for (int e = 0; e < 8; ++e) u[it][e] = av[e];
         }
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const double v = bf16_to_double(u[it][e]);
-          sumsq = fma(v, v, sumsq);
-        }
+        for (int e = 0; e < 8; ++e) sumsq += square_bf16(u[it][e]);
       }
     }
     const double total = block_sum(sumsq, partial);
@@ -167,11 +180,10 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
     for (int col = threadIdx.x; col < hidden; col += 256) {
       unsigned short v = __ldg(xr + col);
       if (FUSED) {
-        v = bf16_from_double(bf16_to_double(v) + bf16_to_double(__ldg(rr + col)));
+        v = add_bf16_exact(v, __ldg(rr + col));
         ur[col] = v;
       }
-      const double d = bf16_to_double(v);
-      sumsq = fma(d, d, sumsq);
+      sumsq += square_bf16(v);
     }
     const double total = block_sum(sumsq, partial);
     const double inv = rsqrt(total / (double)hidden + epsilon);
