@@ -193,3 +193,38 @@ def test_entry_points_reject_bad_arguments_before_touching_the_device():
     flags = (C.c_void_p * 2)(a16, a16)
     assert lib.gk_peer_barrier_counted(flags, 0, 2, None, 1000, None, None) == INVALID
     assert lib.gk_peer_barrier(flags, 2, 2, 1, 1000, None, None) == INVALID
+
+
+def test_slot_layout_random_batches_agree_with_the_oracle():
+    """Property check over random request mixes: totals, page counts and per-request offsets of the host
+    layout equal what the oracle's allocation rule implies."""
+    import ctypes as C
+    from hypothesis import given, settings, strategies as st
+    lib = abi.lib()
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.integers(1, 200), st.lists(st.tuples(st.integers(0, 3000), st.integers(0, 700)), min_size=1, max_size=40))
+    def check(page, requests):
+        prefixes, lengths = [p for p, _ in requests], [n for _, n in requests]
+        n = len(requests)
+        records = (C.c_int32 * (4 * n))()
+        total, pages = C.c_int64(-1), C.c_int64(-1)
+        status = lib.gk_paged_slots_layout((C.c_int64 * n)(*prefixes), (C.c_int64 * n)(*lengths), n, page, 1 << 30, records,
+                                           C.byref(total), C.byref(pages))
+        if sum(lengths) == 0:
+            assert status == 5
+            return
+        assert status == 0 and total.value == sum(lengths)
+        free = list(range(10 ** 6, 10 ** 6 + 4000))
+        slots, used = oracle.allocate_paged_slots([7] * n, free, prefixes, lengths, page)
+        assert pages.value == used and len(slots) == total.value
+        # the first fresh page of request r, as the oracle consumed them, is where the record points
+        at = 0
+        for r in range(n):
+            open_tail = min(lengths[r], (-prefixes[r]) % page)
+            assert records[4 * r + 2] == at
+            if lengths[r] > open_tail:
+                assert slots[at + open_tail] == free[records[4 * r + 3]] * page
+            at += lengths[r]
+
+    check()
