@@ -405,7 +405,9 @@ def run_b200(args):
             last = layer(l, md, *(t[l] for t in resident))
         return last
 
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # High priority for the input stream: the metadata validation kernels that run on it are tiny, and their CTAs should
+    # take the next free SM instead of queueing behind every pending CTA of the attention kernel in flight.
+    copy_in, copy_out = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
     table_dev = md.request_mapping()
     host_index = [locations.pin_memory(), torch.arange(B, dtype=torch.int32).pin_memory(), positions.pin_memory()]
     prefix_list, length_list = (w.ctx - w.chunk).tolist(), [w.chunk] * B
