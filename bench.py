@@ -456,7 +456,10 @@ def run_b200(args):
                 out.record_stream(copy_out)
                 host_out[l].copy_(out, non_blocking=True)
             if gather is not None and gather.mode == "push":
-                main.wait_stream(copy_out)        # the gathered buffer is reused two layers later
+                # The gathered buffer is written again by the PEERS two layers later, as soon as they pass the
+                # next barrier, which needs this rank's arrival: so this rank must not go on to the next layer
+                # (and its barrier) before its own read-back of this layer has finished.
+                main.wait_stream(copy_out)
         main.wait_stream(copy_out)
 
     def timed(fn, steps):
