@@ -162,7 +162,12 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.window = index, [], None, [None, None]
+
+    def mark(self):
+        """Call right before and right after the timed region (the sampler itself starts earlier, under the
+        warm-up's load, because nvidia-smi needs a few hundred milliseconds to deliver its first line)."""
+        self.window[0 if self.window[0] is None else 1] = time.monotonic()
 
     def __enter__(self):
         try:
@@ -177,20 +182,28 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([c.strip() for c in line.split(",")] + [time.monotonic()])
 
     def __exit__(self, *exc):
         if self.proc:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
+    def samples(self):
+        return sum(1 for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
+
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        good = [r for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        lo, hi = self.window
+        inside = [r for r in good if lo is not None and hi is not None and lo <= r[-1] <= hi + 0.02]
+        # a timed region shorter than the sampling period may hold no line: the lines taken under the same load
+        # during the warm-up right before it stand in then
+        rows, where = (inside, "timed region") if inside else (good, "warm-up, timed region and its untimed repeats (same load)")
+        sm, mx = [float(r[0]) for r in rows], [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v == "Active"})
+        reasons = sorted({n for r in rows for n, v in zip(names, r[2:6]) if v == "Active"})
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "window": where}
 
 
 def workload_config(w: Workload, world: int, gather: str, oproj: bool = False):
@@ -511,10 +524,19 @@ def run_b200(args):
             if world > 1:
                 dist.barrier()
     run_step = graph.replay if graph is not None else resident_step
-    for _ in range(max(args.warmup, 3)):
-        run_step()
     with ClockSampler(local) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            run_step()
+        torch.cuda.synchronize()
+        clocks.mark()
         total_ms = timed(run_step, args.steps)
+        clocks.mark()
+        # A timed region shorter than nvidia-smi's start-up leaves no sample: repeat the same step, untimed, until a few
+        # lines have been taken under that load (3 s at most).
+        extra_until = time.monotonic() + 3.0
+        while clocks.samples() < 3 and time.monotonic() < extra_until:
+            run_step()
+            torch.cuda.synchronize()
     for _ in range(2):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps)
