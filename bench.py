@@ -531,11 +531,12 @@ def run_b200(args):
         clocks.mark()
         total_ms = timed(run_step, args.steps)
         clocks.mark()
-        # A timed region shorter than nvidia-smi's start-up leaves no sample: repeat the same step, untimed, until a few
-        # lines have been taken under that load (3 s at most).
-        extra_until = time.monotonic() + 3.0
-        while clocks.samples() < 3 and time.monotonic() < extra_until:
-            run_step()
+        # A timed region shorter than nvidia-smi's start-up leaves no sample: repeat the same step, untimed, so that
+        # about half a second passes under that load.  The count comes from the all-reduced time, so every rank runs
+        # the same number of steps (their exchanges must pair up).
+        if total_ms < 500.0:
+            for _ in range(min(500, math.ceil((500.0 - total_ms) / (total_ms / args.steps)))):
+                run_step()
             torch.cuda.synchronize()
     for _ in range(2):
         e2e_step()
