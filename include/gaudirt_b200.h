@@ -334,9 +334,9 @@ GK_API int gk_paged_metadata_device_validate(
     uint64_t* first_error, int32_t* status, gk_stream_t stream);
 
 /* ---- o_proj and its rank-ordered sum --------------------------------------------------------
- * The step behind the attention block in tensor-parallel decode (docs/DESIGN.md:34 of the
- * reference names the chain O-Proj -> AllReduce -> AddRMSNorm): every rank multiplies its heads
- * by its slice of the o_proj weight, the partial results are summed in rank order
+ * The step behind the attention block in tensor-parallel decode (the reference's design notes
+ * name the chain O-Proj -> AllReduce -> AddRMSNorm): every rank multiplies its heads by its
+ * slice of the o_proj weight, the partial results are summed in rank order
  * (src/bridge/communicator.cpp:373-417, expectation tests/tp4_gather_reduce_smoke.py:16-20), and
  * the sum enters the next layer's fused residual-add RMS norm.
  *
