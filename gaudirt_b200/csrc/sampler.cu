@@ -365,6 +365,152 @@ __device__ uint32_t select_threshold(const T* row, int64_t cols, float top, floa
   return prefix > floor_bits ? prefix : floor_bits;
 }
 
+// bf16 rows only: a row has at most 65 536 distinct values, and the thresholds of top-k / top-p sit
+// among the largest of them.  One pass histograms count and mass over the 2 048 distinct bf16 values
+// just below the maximum (bin = distance in order-preserving 16-bit keys; every element of a bin
+// has the same weight, so a bin boundary is an exact threshold) and sums the rest as a tail; the
+// k-th largest weight and the top-p cut are then prefix searches over the bins.  Returns false when
+// a threshold falls into the tail, and the caller runs the general three-pass radix selects.
+__device__ __forceinline__ uint32_t key_bf16(uint32_t bits) {          // bits of a non-NaN bf16, -0 already folded into +0
+  return (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);
+}
+__device__ __forceinline__ float value_of_key_bf16(uint32_t key) {
+  const uint32_t bits = (key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu);
+  return __uint_as_float(bits << 16);
+}
+
+__device__ bool bf16_thresholds(const unsigned short* row, int64_t cols, float top, float inv_temp, bool nan_low, long long k,
+                                float top_p, float min_p, SampleShared* sh, uint32_t* floor_out) {
+  const uint32_t top_bits = __float_as_uint(top) >> 16;
+  const uint32_t top_key = key_bf16(top_bits == 0x8000u ? 0u : top_bits);
+  for (int b = threadIdx.x; b < kBins; b += blockDim.x) {
+    sh->mass_lo[b] = 0;
+    sh->mass_hi[b] = 0;
+    sh->count[b] = 0;
+  }
+  __syncthreads();
+  unsigned long long tail_count = 0, tail_mass = 0;
+  for_each_logit(row, cols, [&](int64_t, float f) {
+    if (f != f) {                                            // an unfiltered NaN weighs like the maximum (bin 0)
+      if (nan_low) {
+        ++tail_count;
+        return;
+      }
+      f = top;
+    }
+    uint32_t bits = __float_as_uint(f) >> 16;
+    if (bits == 0x8000u) bits = 0u;
+    const uint32_t d = top_key - key_bf16(bits);
+    const unsigned long long mass = mass_of(weight_of(f, top, inv_temp, nan_low));
+    if (d < (uint32_t)kBins) {
+      atomicAdd(&sh->count[d], 1u);
+      const uint32_t low = (uint32_t)mass, high = (uint32_t)(mass >> 32);
+      if (low) {
+        const uint32_t before = atomicAdd(&sh->mass_lo[d], low);
+        if (before > 0xffffffffu - low) atomicAdd(&sh->mass_hi[d], 1u);
+      }
+      if (high) atomicAdd(&sh->mass_hi[d], high);
+    } else {
+      ++tail_count;
+      tail_mass += mass;
+    }
+  });
+  __syncthreads();
+  tail_count = block_sum_u64(tail_count, sh->scratch);
+  tail_mass = block_sum_u64(tail_mass, sh->scratch);
+
+  // Thread t owns bins 4t .. 4t+3 (weights fall as the bin index grows).
+  unsigned long long count[4], mass[4], my_count = 0, my_mass = 0;
+  uint32_t wbits[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int b = 4 * (int)threadIdx.x + q;
+    count[q] = b < kBins ? sh->count[b] : 0ull;
+    mass[q] = b < kBins ? ((unsigned long long)sh->mass_hi[b] << 32) | sh->mass_lo[b] : 0ull;
+    wbits[q] = b < kBins && (uint32_t)b <= top_key ? __float_as_uint(weight_of(value_of_key_bf16(top_key - b), top, inv_temp, false)) : 0u;
+    my_count += count[q];
+    my_mass += mass[q];
+  }
+  unsigned long long binned_count, binned_mass;
+  const unsigned long long count_before = block_exclusive_scan_u64(my_count, sh->scratch, &binned_count);
+  const unsigned long long mass_before = block_exclusive_scan_u64(my_mass, sh->scratch, &binned_mass);
+
+  // top-k: the bin in which the running count first reaches k
+  uint32_t floor_bits = min_p > 0.f ? __float_as_uint(fminf(min_p, 1.0f)) : 0u;
+  const bool has_k = k >= 1 && k < cols;
+  if (threadIdx.x == 0) sh->found_prefix = 0xffffffffu;      // "not found"
+  __syncthreads();
+  if (has_k) {
+    unsigned long long run = count_before;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (run < (unsigned long long)k && (unsigned long long)k <= run + count[q]) sh->found_prefix = wbits[q];
+      run += count[q];
+    }
+  }
+  __syncthreads();
+  if (has_k) {
+    if (sh->found_prefix == 0xffffffffu) return false;       // the k-th largest lies in the tail
+    floor_bits = sh->found_prefix > floor_bits ? sh->found_prefix : floor_bits;
+  }
+  __syncthreads();
+  // What the floor leaves: whole bins, plus the tail only when there is no floor at all.
+  const uint32_t last_bin_bits =
+      top_key >= (uint32_t)kBins - 1 ? __float_as_uint(weight_of(value_of_key_bf16(top_key - (kBins - 1)), top, inv_temp, false))
+                                     : 0u;                   // fewer keys than bins below the maximum: nothing weighs in the tail
+  if (floor_bits != 0u && floor_bits < last_bin_bits && tail_count > 0) return false;   // the floor cuts inside the tail
+  if (!(top_p < 1.0f)) {
+    *floor_out = floor_bits;
+    return true;
+  }
+  unsigned long long kept_mine = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    if (wbits[q] >= floor_bits) kept_mine += mass[q];
+  unsigned long long kept;
+  const unsigned long long kept_before = block_exclusive_scan_u64(kept_mine, sh->scratch, &kept);
+  const unsigned long long kept_all = kept + (floor_bits == 0u ? tail_mass : 0ull);
+  if (kept_all == 0) {
+    *floor_out = floor_bits;
+    return true;
+  }
+  unsigned long long need = (unsigned long long)((double)kept_all * (double)fmaxf(top_p, 0.f));
+  if (need == 0) need = 1;
+  if (need > kept) return false;                             // the cut lies in the tail
+  if (threadIdx.x == 0) sh->found_prefix = 0xffffffffu;
+  __syncthreads();
+  {
+    unsigned long long run = kept_before;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const unsigned long long here = wbits[q] >= floor_bits ? mass[q] : 0ull;
+      if (run < need && need <= run + here) sh->found_prefix = wbits[q];
+      run += here;
+    }
+  }
+  __syncthreads();
+  const uint32_t cut = sh->found_prefix;
+  __syncthreads();
+  if (cut == 0xffffffffu) return false;
+  *floor_out = cut > floor_bits ? cut : floor_bits;
+  (void)mass_before;
+  (void)binned_count;
+  (void)binned_mass;
+  return true;
+}
+
+template <typename T>
+__device__ __forceinline__ bool fast_thresholds(const T*, int64_t, float, float, bool, long long, float, float, SampleShared*,
+                                                uint32_t*) {
+  return false;                                              // fp32 rows: the general path
+}
+template <>
+__device__ __forceinline__ bool fast_thresholds<unsigned short>(const unsigned short* row, int64_t cols, float top, float inv_temp,
+                                                                bool nan_low, long long k, float top_p, float min_p,
+                                                                SampleShared* sh, uint32_t* floor_out) {
+  return bf16_thresholds(row, cols, top, inv_temp, nan_low, k, top_p, min_p, sh, floor_out);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 sample_kernel(const T* __restrict__ logits, int64_t cols, int64_t row_stride, const float* __restrict__ temperatures,
@@ -393,21 +539,26 @@ sample_kernel(const T* __restrict__ logits, int64_t cols, int64_t row_stride, co
   const float min_p = min_ps[r];
   uint32_t floor_bits = min_p > 0.f ? __float_as_uint(fminf(min_p, 1.0f)) : 0u;
   const int64_t k = top_ks[r];
-  if (k >= 1 && k < cols) {
-    const uint32_t kth = select_threshold<T, false>(row, cols, top, inv_temp, nl, 0u, (unsigned long long)k, &sh);
-    floor_bits = kth > floor_bits ? kth : floor_bits;
-  }
   const float top_p = top_ps[r];
-  if (top_p < 1.0f) {
-    unsigned long long kept = 0;
-    for_each_logit(row, cols, [&](int64_t, float f) {
-      const float w = weight_of(f, top, inv_temp, nl);
-      if (__float_as_uint(w) >= floor_bits) kept += mass_of(w);
-    });
-    kept = block_sum_u64(kept, sh.scratch);
-    if (kept > 0) {
-      const unsigned long long need = (unsigned long long)((double)kept * (double)fmaxf(top_p, 0.f));
-      floor_bits = select_threshold<T, true>(row, cols, top, inv_temp, nl, floor_bits, need > 0 ? need : 1, &sh);
+  const bool filtered = (k >= 1 && k < cols) || top_p < 1.0f;
+  if (filtered && !fast_thresholds<T>(row, cols, top, inv_temp, nl, k, top_p, min_p, &sh, &floor_bits)) {
+    __syncthreads();
+    floor_bits = min_p > 0.f ? __float_as_uint(fminf(min_p, 1.0f)) : 0u;
+    if (k >= 1 && k < cols) {
+      const uint32_t kth = select_threshold<T, false>(row, cols, top, inv_temp, nl, 0u, (unsigned long long)k, &sh);
+      floor_bits = kth > floor_bits ? kth : floor_bits;
+    }
+    if (top_p < 1.0f) {
+      unsigned long long kept = 0;
+      for_each_logit(row, cols, [&](int64_t, float f) {
+        const float w = weight_of(f, top, inv_temp, nl);
+        if (__float_as_uint(w) >= floor_bits) kept += mass_of(w);
+      });
+      kept = block_sum_u64(kept, sh.scratch);
+      if (kept > 0) {
+        const unsigned long long need = (unsigned long long)((double)kept * (double)fmaxf(top_p, 0.f));
+        floor_bits = select_threshold<T, true>(row, cols, top, inv_temp, nl, floor_bits, need > 0 ? need : 1, &sh);
+      }
     }
   }
 

@@ -189,13 +189,15 @@ def test_sampler_support_on_random_rows_and_with_a_grammar_mask(rt):
     logits = (torch.randn(batch, vocab, generator=gen) * 2.5).to(torch.bfloat16)
     temps = torch.rand(batch, generator=gen) * 1.5 + 0.3
     top_ps = torch.tensor([1.0, 0.9, 0.5] * 8)
-    top_ks = torch.tensor([vocab, 50, 5, 1] * 6, dtype=torch.int32)
+    # 50 / 5 / 1 are found among the bf16 values just below the maximum; vocab - 7 and 30000 lie far down, where the
+    # kernel has to take its general selection path
+    top_ks = torch.tensor([vocab, 50, 5, 1, vocab - 7, 30000] * 4, dtype=torch.int32)
     min_ps = torch.tensor([0.0, 0.02] * 12)
     args = [t.to(DEV) for t in (logits, temps, top_ps, top_ks, min_ps)]
     # random logits leave every threshold far (in fp32 terms) from the nearest weight, so the binary64 support is exact
     supports = [set(oracle.sampling_support(logits[r], float(temps[r]), float(top_ps[r]), int(top_ks[r]), float(min_ps[r]))[0]
                     .tolist()) for r in range(batch)]
-    assert all(1 <= len(supports[r]) <= 3 for r in range(3, batch, 4))   # top_k = 1 (ties at the top stay)
+    assert all(1 <= len(supports[r]) <= 3 for r in range(3, batch, 6))   # top_k = 1 (ties at the top stay)
     seeds = torch.arange(batch, dtype=torch.int64, device=DEV) * 7919
     for step in range(25):
         tokens = sample(*args, seeds, torch.full((batch,), step, dtype=torch.int64, device=DEV), True).cpu().tolist()
