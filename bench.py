@@ -159,7 +159,8 @@ def tensor_peak():
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks_event_reasons.active,"
+              "power.draw")
 
     def __init__(self, index):
         self.index, self.rows, self.proc, self.window = index, [], None, [None, None]
@@ -190,10 +191,10 @@ class ClockSampler:
             self.thread.join(timeout=2)
 
     def samples(self):
-        return sum(1 for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit())
+        return sum(1 for r in self.rows if len(r) >= 9 and r[0].replace(".", "").isdigit())
 
     def summary(self):
-        good = [r for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        good = [r for r in self.rows if len(r) >= 9 and r[0].replace(".", "").isdigit()]
         lo, hi = self.window
         inside = [r for r in good if lo is not None and hi is not None and lo <= r[-1] <= hi + 0.02]
         # a timed region shorter than the sampling period may hold no line: the lines taken under the same load
@@ -202,8 +203,10 @@ class ClockSampler:
         sm, mx = [float(r[0]) for r in rows], [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in rows for n, v in zip(names, r[2:6]) if v == "Active"})
+        watts = [float(r[7]) for r in rows if r[7].replace(".", "").isdigit()]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm), "window": where}
+                "reasons": reasons, "samples": len(sm), "window": where,
+                "active_masks": sorted({r[6] for r in rows}), "power_w": statistics.median(watts) if watts else None}
 
 
 def workload_config(w: Workload, world: int, gather: str, oproj: bool = False):
