@@ -162,6 +162,35 @@ def norm_rotary_cases(ref_tests):
     np.savez_compressed(os.path.join(HERE, "norm_rotary.npz"), **out)
 
 
+def after_attention_cases(ref_tests):
+    """Grammar bitmask and rank-ordered sum: the reference's own CPU functions, lifted from its device tests
+    (``tests/vocab_bitmask_device_smoke.py``, ``tests/tp4_gather_reduce_smoke.py``)."""
+    env = {"torch": torch}
+    ref_mask = lift(os.path.join(ref_tests, "vocab_bitmask_device_smoke.py"), "ref_apply_bitmask", env)
+    rank_sum = lift(os.path.join(ref_tests, "tp4_gather_reduce_smoke.py"), "_canonical_rank_sum", env)
+    gen = torch.Generator().manual_seed(20261177)
+    out = {}
+    cases = [("bf16_35", torch.bfloat16, 1, 35, None, -1, False), ("bf16_1025", torch.bfloat16, 3, 1025, None, -1, False),
+             ("f32_1025_tail", torch.float32, 3, 1025, None, -1, True), ("f32_40_short", torch.float32, 2, 40, None, -1, True),
+             ("bf16_40_short", torch.bfloat16, 2, 40, None, -1, False), ("f32_rows", torch.float32, 4, 64, [2, 0, 2], -1, False),
+             ("bf16_vocab", torch.bfloat16, 3, 200, None, 150, True)]
+    for name, dtype, batch, vocab, indices, vocab_size, mask_tail in cases:
+        words = 1 if name.endswith("short") else (vocab + 31) // 32
+        logits = (torch.randn(batch, vocab, generator=gen) * 3).to(dtype)
+        mask = torch.randint(-2 ** 31, 2 ** 31 - 1, (batch, words), generator=gen, dtype=torch.int64).to(torch.int32)
+        idx = None if indices is None else torch.tensor(indices, dtype=torch.int32)
+        want = ref_mask(logits, mask, idx, vocab_size, mask_tail)
+        raw = (lambda t: bits(t)) if dtype == torch.bfloat16 else (lambda t: t.numpy().view(np.uint32).copy())
+        out[f"mask_{name}_logits"], out[f"mask_{name}_mask"], out[f"mask_{name}_out"] = raw(logits), mask.numpy(), raw(want)
+        out[f"mask_{name}_args"] = np.array([vocab_size, int(mask_tail)] + ([] if indices is None else indices), dtype=np.int64)
+    for world in (1, 2, 4, 8):
+        parts = [(torch.randn(1536, generator=gen) * 10 ** float(torch.randn((), generator=gen))).to(torch.bfloat16)
+                 for _ in range(world)]
+        out[f"sum_{world}_parts"] = np.stack([bits(t) for t in parts])
+        out[f"sum_{world}_out"] = bits(rank_sum(parts))
+    np.savez_compressed(os.path.join(HERE, "after_attention.npz"), **out)
+
+
 def main():
     if len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
@@ -173,6 +202,7 @@ def main():
     softcap_window_cases(ref_tests)
     rounding_cases()
     norm_rotary_cases(ref_tests)
+    after_attention_cases(ref_tests)
     print("golden fixtures written to", HERE)
 
 

@@ -212,3 +212,24 @@ def test_metadata_rules():
     alias = mapping.copy(); alias[1, 0] = 3
     with pytest.raises(ValueError, match="aliases"):
         oracle.validate_paged_metadata([3, 12], [0, 1], [2, 3], alias, 64)
+
+
+def test_bitmask_and_rank_sum_match_the_reference_functions():
+    """`after_attention.npz` holds inputs and outputs of the reference's own `ref_apply_bitmask` and
+    `_canonical_rank_sum`; the oracle's restatements reproduce them bit for bit."""
+    z = load("after_attention.npz")
+    names = sorted({k[len("mask_"):-len("_logits")] for k in z.files if k.startswith("mask_") and k.endswith("_logits")})
+    assert len(names) == 7
+    for name in names:
+        is_bf16 = name.startswith("bf16")
+        tensor = (lambda a: bf16(a)) if is_bf16 else (lambda a: torch.from_numpy(a.view(np.float32).copy()))
+        raw = (lambda t: t.contiguous().view(torch.int16)) if is_bf16 else (lambda t: t.contiguous().view(torch.int32))
+        args = z[f"mask_{name}_args"]
+        indices = torch.from_numpy(args[2:].astype(np.int32)) if len(args) > 2 else None
+        got = oracle.apply_vocab_bitmask(tensor(z[f"mask_{name}_logits"]), torch.from_numpy(z[f"mask_{name}_mask"]),
+                                         indices, int(args[0]), bool(args[1]))
+        assert torch.equal(raw(got), raw(tensor(z[f"mask_{name}_out"]))), name
+    for world in (1, 2, 4, 8):
+        parts = [bf16(row) for row in z[f"sum_{world}_parts"]]
+        want = bf16(z[f"sum_{world}_out"])
+        assert torch.equal(oracle.canonical_rank_sum(parts).view(torch.int16), want.view(torch.int16)), world
