@@ -215,7 +215,7 @@ def test_slot_layout_random_batches_agree_with_the_oracle():
             assert status == 5
             return
         assert status == 0 and total.value == sum(lengths)
-        free = list(range(10 ** 6, 10 ** 6 + 4000))
+        free = list(range(10 ** 6, 10 ** 6 + sum(lengths) + n + 1))  # page = 1 needs one page per token
         slots, used = oracle.allocate_paged_slots([7] * n, free, prefixes, lengths, page)
         assert pages.value == used and len(slots) == total.value
         # the first fresh page of request r, as the oracle consumed them, is where the record points
