@@ -18,7 +18,12 @@ KV block 128 tokens, pool of batch*32 blocks + 10 % spare, shuffled block tables
 
 With N > 1 ranks the KV heads are sharded over the ranks (tensor parallel) and the attention
 output is gathered along the last dimension, by default inside the attention epilogue
-(`--gather push`) or with NCCL (`--gather nccl`).  The batch is fixed: strong scaling.
+(`--gather push`) or with NCCL (`--gather nccl`).  The batch is fixed at every N: strong scaling.
+Before anything is timed, layer 0 is checked: at N > 1 the pushed gather must equal the NCCL
+gather bit for bit on every rank, and a sample of rows (all heads, gathered from all ranks) is
+held against the CPU oracle; the result is the line's `parity` object and a mismatch is fatal.
+At N > 1 the default run also measures the two tensor-parallel configurations (3 and 5) after
+the headline one and embeds their records as `tp_configs`.
 
 Inputs are synthetic (seeded); pool contents are N(0,1) bf16.  The pools together are far larger
 than L2, so consecutive launches never hit in cache.
@@ -29,6 +34,8 @@ than L2, so consecutive launches never hit in cache.
 from __future__ import annotations
 
 import argparse
+import copy
+import gc
 import json
 import math
 import os
@@ -137,6 +144,8 @@ def parse():
                          "rank-ordered sum of the partials and the residual-add RMS norm, instead of the output gather")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
+    ap.add_argument("--no-tp-configs", action="store_true",
+                    help="with N > 1: measure the chosen configuration only, not configs 3 and 5 after it")
     return ap.parse_args()
 
 
@@ -307,7 +316,7 @@ def run_reference(args):
             f"({sample.tokens} visited keys), scaled linearly by visited keys")
     line = {"impl": "reference", "metric": METRIC if w.chunk == 1 else "paged_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": w.rows / value * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(w, 1, "-"),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": text},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -318,32 +327,44 @@ def run_reference(args):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
-def run_b200(args):
+def bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def sampled_rows(ctx, chunk, count=5):
+    """Rows held against the oracle: shortest, longest and evenly spread sequences (last row of a chunk)."""
+    order = torch.argsort(ctx)
+    pick = {int(order[0]), int(order[-1])}
+    for f in range(1, count - 1):
+        pick.add(int(order[(len(order) - 1) * f // (count - 1)]))
+    return sorted(b * chunk + chunk - 1 for b in pick)
+
+
+def measure(args, config, world, rank, dev, headline):
+    """Builds the workload of `config`, checks layer 0, times the resident step, the end-to-end step and
+    the dominant kernel; returns the JSON record on rank 0 (None elsewhere)."""
     import torch.distributed as dist
     import gaudirt_b200 as rt
+    import oracle
     from gaudirt_b200 import abi, tp
     from gaudirt_b200 import raw as H
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    args = copy.copy(args)
+    args.config = config
+    if not headline:
+        args.layers = args.batch = args.ctx = 0
     w = make_workload(args)
     shard = tp.HeadShard(rank, world, w.q_heads, w.kv_heads) if args.shard_of == 1 or world > 1 else \
         tp.HeadShard(0, args.shard_of, w.q_heads, w.kv_heads)
     B, d, L, R = w.batch, HEAD_DIM, w.layers, w.rows
     hq, hkv = shard.local_q_heads, shard.local_kv_heads
+    decode = w.chunk == 1
 
     # ---- metadata (replicated on every rank): shuffled block tables, new token at ctx-1 -------
     need = (w.ctx + BLOCK - 1) // BLOCK
     n_blocks = int(int(need.sum()) * 1.1) + 1
     slots = n_blocks * BLOCK
-    gen = torch.Generator().manual_seed(20261100 + args.config)
+    gen = torch.Generator().manual_seed(20261100 + config)
     perm = torch.randperm(n_blocks, generator=gen).to(torch.int32)
     tables = torch.zeros(B, int(need.max()), dtype=torch.int32)
     cursor = 0
@@ -355,7 +376,7 @@ def run_b200(args):
     requests = torch.arange(B, dtype=torch.int32).repeat_interleave(w.chunk)
     positions = ((w.ctx - w.chunk)[:, None] + torch.arange(w.chunk)[None, :]).reshape(-1).to(torch.int32)
     locations = mapping[requests.long(), positions.long()].contiguous()
-    scale = 1.0 / math.sqrt(d)
+    scale = torch.tensor(1.0 / math.sqrt(d), dtype=torch.float32).item()
 
     # ---- pools: layer 0 is drawn N(0,1); the others are that data rotated by a layer-specific
     # offset (same distribution, distinct HBM, seconds instead of minutes to fill) ---------------
@@ -370,23 +391,27 @@ def run_b200(args):
         dst[flat0.numel() - shift:].copy_(flat0[:shift])
     views = [(pool[l, 0].transpose(0, 1), pool[l, 1].transpose(0, 1)) for l in range(L)]
 
-    hgen = torch.Generator().manual_seed(20261100 + 10 * args.config + rank)
-    host_q = (torch.randn(L, R, hq * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
-    host_k = (torch.randn(L, R, hkv * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
-    host_v = (torch.randn(L, R, hkv * d, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
-    host_out = torch.empty(L, R, hq * d * world, dtype=torch.bfloat16).pin_memory()
-    host_in = [host_q, host_k, host_v]
-    gamma = cache = None
+    # ---- step inputs in pinned host memory: one packed [q | k | v] row per token, the way a fused
+    # QKV projection leaves them (the operators read the three column slices in place) ------------
+    width = (hq + 2 * hkv) * d
+    hgen = torch.Generator().manual_seed(20261100 + 10 * config + rank)
+    host_qkv = (torch.randn(L, R, width, generator=hgen) * w.std).to(torch.bfloat16).pin_memory()
+    split = lambda t: (t[:, : hq * d], t[:, hq * d:(hq + hkv) * d], t[:, (hq + hkv) * d:])
+    host_xr = gamma = cache = None
     if w.front:
         fgen = torch.Generator().manual_seed(20261199)      # the hidden state is replicated on every rank
-        host_in += [torch.randn(L, R, w.hidden, generator=fgen).to(torch.bfloat16).pin_memory() for _ in range(2)]
+        host_xr = torch.randn(L, 2, R, w.hidden, generator=fgen).to(torch.bfloat16).pin_memory()
         gamma = (0.02 * torch.randn(w.hidden, generator=fgen)).to(torch.bfloat16).to(dev)
         inv = w.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
         ang = torch.arange(mapping.size(1), dtype=torch.float64)[:, None] * inv[None, :]   # covers the whole table
         cache = torch.cat((ang.cos(), ang.sin()), dim=-1).float().to(torch.bfloat16).to(dev)
-    resident = [h.to(dev) for h in host_in]
+    resident_qkv = host_qkv.to(dev)
+    resident_xr = host_xr.to(dev) if w.front else None
+    lo_row, hi_row = rank * R // world, (rank + 1) * R // world       # the rows this rank reads back
+    host_out = torch.empty(L, hi_row - lo_row, hq * d * world, dtype=torch.bfloat16).pin_memory()
 
-    gather = tp.OutputGather(R, hq * d, dev, mode=args.gather) if world > 1 and not args.oproj else None
+    DEPTH = 4         # ring of gathered buffers (divides every layer count): the read-back of layer l has until layer l + 3
+    gather = tp.OutputGather(R, hq * d, dev, mode=args.gather, depth=DEPTH) if world > 1 and not args.oproj else None
     lib = abi.lib()
     row_parallel = o_weight = None
     if args.oproj:
@@ -397,86 +422,103 @@ def run_b200(args):
         o_weight = [(torch.randn(w.hidden, hq * d, generator=ogen, device=dev) / (w.q_heads * d) ** 0.5).to(torch.bfloat16)
                     for _ in range(L)]
 
-    def layer(l, md, q, k, v, x=None, res=None):
-        """One layer of the step on the current stream; returns the gathered attention output."""
+    def layer(l, md, qkv, xr, exchange=None):
+        """One layer of the step on the current stream; returns the (gathered) attention output."""
+        exchange = gather if exchange is None else exchange
+        q, k, v = split(qkv)
+        kp, vp = views[l]
         if row_parallel is not None:
-            # rotary -> store + attention on this rank's heads -> o_proj, rank-ordered sum, add + norm
-            q, k = torch.ops.gaudirt.rotary_embedding(q, k, cache, md, d, d, True)
-            attn = torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], md, d, scale)
-            return row_parallel.forward(attn, o_weight[l], res, gamma, 1e-5, 1.0)[0]
+            # rotary + store -> attention on this rank's heads -> o_proj, rank-ordered sum, add + norm
+            q = torch.ops.gaudirt._rotary_kv_store(q, k, v, cache, md, kp, vp, d, d, True)
+            attn = torch.ops.gaudirt._paged_attn_stored(q, kp, vp, md, d, scale)
+            return row_parallel.forward(attn, o_weight[l], xr[1], gamma, 1e-5, 1.0)[0]
         if w.front:
-            torch.ops.gaudirt.fused_add_rms_norm(x, res, gamma, 1e-5, 1.0)
-            q, k = torch.ops.gaudirt.rotary_embedding(q, k, cache, md, d, d, True)
-        if gather is not None:
-            return gather.attention(q, k, v, views[l][0], views[l][1], md, d, scale)
-        return torch.ops.gaudirt.paged_attn(q, k, v, views[l][0], views[l][1], md, d, scale)
+            torch.ops.gaudirt.fused_add_rms_norm(xr[0], xr[1], gamma, 1e-5, 1.0)
+            q = torch.ops.gaudirt._rotary_kv_store(q, k, v, cache, md, kp, vp, d, d, True)
+            k = v = None                       # the rotary kernel stored the rows
+        if exchange is not None:
+            return exchange.attention(q, k, v, kp, vp, md, d, scale)
+        if k is None:
+            return torch.ops.gaudirt._paged_attn_stored(q, kp, vp, md, d, scale)
+        return torch.ops.gaudirt.paged_attn(q, k, v, kp, vp, md, d, scale)
 
-    md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
-    md._set_fused_combine({"auto": -1, "separate": 0, "fused": 1}[args.combine])
-    md.attention_plan(hq, hkv, d)
+    combine_mode = {"auto": -1, "separate": 0, "fused": 1}[args.combine]
 
-    def resident_step():
+    def host_metadata():
+        md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+        md._set_fused_combine(combine_mode)
+        md.attention_plan(hq, hkv, d)
+        return md
+
+    md = host_metadata()
+    xr_of = lambda t, l: t[l] if t is not None else None
+
+    # ---- parity of layer 0, before anything is timed -------------------------------------------
+    def parity_check():
+        out = layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))
+        if isinstance(out, tuple):
+            out = out[0]
+        out = out.clone()
+        record = {"push_eq_nccl": None}
+        if gather is not None and gather.mode == "push":
+            baseline = tp.OutputGather(R, hq * d, dev, mode="nccl")
+            again = layer(0, md, resident_qkv[0], xr_of(resident_xr, 0), exchange=baseline).clone()
+            same = torch.tensor([int(torch.equal(bits(out), bits(again)))], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            record["push_eq_nccl"] = bool(same.item())
+            layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))     # keeps the ring at an even count of exchanges
+            for _ in range(DEPTH - 2):
+                layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))
+        if row_parallel is not None:
+            return record
+        rows = sampled_rows(w.ctx, w.chunk)
+        q0 = split(resident_qkv[0])[0]
+        if w.front:
+            q0, _ = torch.ops.gaudirt.rotary_embedding(q0, split(resident_qkv[0])[1], cache, md, d, d, True)
+        # every rank contributes its heads of the sampled rows' queries and visible keys / values
+        keys, values, tabs, at = [], [], [], 1
+        longest = max(int(positions[r]) + 1 for r in rows)
+        for r in rows:
+            n = int(positions[r]) + 1
+            where = mapping[int(requests[r]), :n].long().to(dev)
+            keys.append(views[0][0][where])
+            values.append(views[0][1][where])
+            tab = torch.zeros(longest, dtype=torch.int32)
+            tab[:n] = torch.arange(at, at + n, dtype=torch.int32)
+            tabs.append(tab)
+            at += n
+        mine = [q0[rows].contiguous(), torch.cat(keys), torch.cat(values)]
+        if world > 1:
+            full = []
+            for t in mine:
+                parts = [torch.empty_like(t) for _ in range(world)]
+                dist.all_gather(parts, t)
+                full.append(torch.cat(parts, dim=1))
+            mine = full
+        if rank == 0:
+            pad = torch.zeros(1, w.kv_heads, d, dtype=torch.bfloat16)
+            got = out[rows].cpu().double()
+            if got.size(1) == w.q_heads * d:          # (a --shard-of run holds one rank's heads only: no full-head check)
+                ref = oracle.attend_fp32_softmax(mine[0].cpu(), torch.cat([pad, mine[1].cpu()]), torch.cat([pad, mine[2].cpu()]),
+                                                 torch.arange(len(rows)), torch.tensor([int(positions[r]) for r in rows]),
+                                                 torch.stack(tabs), w.q_heads, w.kv_heads, d, scale)
+                worst, mean = oracle.fp32_softmax_gate(got, ref)      # raises beyond 2e-2 / 2e-3
+                record.update(rows_checked=len(rows), max_abs=worst, mean_abs=mean,
+                              oracle="fp32 softmax on the CPU, all heads, layer 0; gates max-abs 2e-2, mean-abs 2e-3")
+        if record["push_eq_nccl"] is False:
+            raise SystemExit("parity: the pushed gather differs from the NCCL gather")
+        return record
+
+    parity = parity_check()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+
+    def resident_step(md_):
         last = None
         for l in range(L):
-            last = layer(l, md, *(t[l] for t in resident))
+            last = layer(l, md_, resident_qkv[l], xr_of(resident_xr, l))
         return last
-
-    # High priority for the input stream: the metadata validation kernels that run on it are tiny, and their CTAs should
-    # take the next free SM instead of queueing behind every pending CTA of the attention kernel in flight.
-    copy_in, copy_out = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
-    table_dev = md.request_mapping()
-    host_index = [locations.pin_memory(), torch.arange(B, dtype=torch.int32).pin_memory(), positions.pin_memory()]
-    prefix_list, length_list = (w.ctx - w.chunk).tolist(), [w.chunk] * B
-
-    def e2e_step():
-        """The same step from HOST buffers: metadata built from CPU tensors, per layer the inputs
-        copied in from pinned memory and the layer's result copied back, copies overlapped with compute."""
-        main = torch.cuda.current_stream()
-        if args.e2e_host_metadata:
-            step_md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
-        else:
-            # The serving form of the reference (PagedMetadata.from_device): the request-to-token table is
-            # state that lives on the device like the pool; the step's slot, request and position vectors
-            # come from pinned host memory and are validated against the table on the GPU.
-            # Validation and its read-back run on the copy stream, so the host does not wait for the previous
-            # step's layers still queued on the compute stream.
-            with torch.cuda.stream(copy_in):
-                index = [t.to(dev, non_blocking=True) for t in host_index]
-                step_md = rt.PagedMetadata.from_device(*index, table_dev, prefix_list, length_list, slots)
-            for t in index + [step_md.row_locations(), step_md.rotary_header()]:
-                t.record_stream(main)                 # allocated on the copy stream, consumed on the compute stream
-            main.wait_stream(copy_in)
-        step_md.attention_plan(hq, hkv, d)
-        staged = {}
-
-        def stage(l):
-            with torch.cuda.stream(copy_in):
-                t = tuple(h[l].to(dev, non_blocking=True) for h in host_in)
-                ev = torch.cuda.Event()
-                ev.record(copy_in)
-            staged[l] = (t, ev)
-
-        stage(0)
-        for l in range(L):
-            if l + 1 < L:
-                stage(l + 1)
-            t, ev = staged.pop(l)
-            main.wait_event(ev)
-            for x in t:
-                x.record_stream(main)
-            out = layer(l, step_md, *t)
-            done = torch.cuda.Event()
-            done.record(main)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(done)
-                out.record_stream(copy_out)
-                host_out[l].copy_(out, non_blocking=True)
-            if gather is not None and gather.mode == "push":
-                # The gathered buffer is written again by the PEERS two layers later, as soon as they pass the
-                # next barrier, which needs this rank's arrival: so this rank must not go on to the next layer
-                # (and its barrier) before its own read-back of this layer has finished.
-                main.wait_stream(copy_out)
-        main.wait_stream(copy_out)
 
     def timed(fn, steps):
         if world > 1:
@@ -499,35 +541,28 @@ def run_b200(args):
     # stream it was built on, so the graph's metadata is built on the capture stream.  The NCCL baseline
     # exchange stays eager.
     exchanges = [x for x in (gather, row_parallel) if x is not None]
-    graph = None
-    if not args.no_graph and all(x.mode == "push" or x.world == 1 for x in exchanges):
-        capture = torch.cuda.Stream()
+    use_graph = not args.no_graph and all(x.mode == "push" or x.world == 1 for x in exchanges)
+    capture = torch.cuda.Stream()
+    graph = e2e_graph = None
+    keep = []                                   # tensors the graphs' kernels and copies refer to
+    if use_graph:
         capture.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(capture):
-            md_graph = rt.PagedMetadata(locations, requests, positions, mapping, slots)
-            md_graph._set_fused_combine({"auto": -1, "separate": 0, "fused": 1}[args.combine])
-            md_graph.attention_plan(hq, hkv, d)
-
-            def graph_step():
-                last = None
-                for l in range(L):
-                    last = layer(l, md_graph, *(t[l] for t in resident))
-                return last
-
-            for _ in range(2):
-                graph_step()
+            md_graph = host_metadata()
+            for _ in range(max(2, DEPTH)):
+                resident_step(md_graph)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         if all(x.graph_safe(L) for x in exchanges):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=capture):
-                graph_out = graph_step()
+                keep.append(resident_step(md_graph))
             torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
-    run_step = graph.replay if graph is not None else resident_step
-    with ClockSampler(local) as clocks:
+    run_step = graph.replay if graph is not None else (lambda: resident_step(md))
+    with ClockSampler(dev.index) as clocks:
         for _ in range(max(args.warmup, 3)):
             run_step()
         torch.cuda.synchronize()
@@ -541,9 +576,136 @@ def run_b200(args):
             for _ in range(min(500, math.ceil((500.0 - total_ms) / (total_ms / args.steps)))):
                 run_step()
             torch.cuda.synchronize()
+
+    # ---- the same step end to end, from HOST buffers ---------------------------------------------
+    # Per step: the slot / request / position vectors come from pinned host memory and are validated on the
+    # GPU against the device-resident request-to-token table (the serving form of the reference's metadata,
+    # PagedMetadata.from_device); every layer's packed QKV rows (and hidden state) are copied in from pinned
+    # memory on a copy stream that runs ahead of the compute stream; every layer's result is copied back to
+    # pinned memory on a third stream -- under tensor parallelism each rank reads back its rows/W share of
+    # the gathered activation, so the job reads back one output, not W of them.
+    table_dev = md.request_mapping()
+    host_index = [locations.pin_memory(), torch.arange(B, dtype=torch.int32).pin_memory(), positions.pin_memory()]
+    prefix_list, length_list = (w.ctx - w.chunk).tolist(), [w.chunk] * B
+    # High priority for the input stream: the metadata validation kernels that run on it are tiny, and their CTAs should
+    # take the next free SM instead of queueing behind every pending CTA of the attention kernel in flight.
+    copy_in, copy_out = torch.cuda.Stream(priority=-1), torch.cuda.Stream()
+    share = lambda out: out[lo_row:hi_row]
+
+    def e2e_eager():
+        """Kernel by kernel through the operators; metadata rebuilt from the host vectors every step."""
+        main = torch.cuda.current_stream()
+        if args.e2e_host_metadata:
+            step_md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+        else:
+            # Validation and its read-back run on the copy stream, so the host does not wait for the previous
+            # step's layers still queued on the compute stream.
+            with torch.cuda.stream(copy_in):
+                index = [t.to(dev, non_blocking=True) for t in host_index]
+                step_md = rt.PagedMetadata.from_device(*index, table_dev, prefix_list, length_list, slots)
+            for t in index + [step_md.row_locations(), step_md.rotary_header()]:
+                t.record_stream(main)                 # allocated on the copy stream, consumed on the compute stream
+            main.wait_stream(copy_in)
+        step_md._set_fused_combine(combine_mode)
+        step_md.attention_plan(hq, hkv, d)
+        staged, done = {}, {}
+
+        def stage(l):
+            with torch.cuda.stream(copy_in):
+                t = (host_qkv[l].to(dev, non_blocking=True), host_xr[l].to(dev, non_blocking=True) if w.front else None)
+                ev = torch.cuda.Event()
+                ev.record(copy_in)
+            staged[l] = (t, ev)
+
+        stage(0)
+        for l in range(L):
+            if l + 1 < L:
+                stage(l + 1)
+            t, ev = staged.pop(l)
+            main.wait_event(ev)
+            for x in t:
+                if x is not None:
+                    x.record_stream(main)
+            if gather is not None and gather.mode == "push" and l - (DEPTH - 1) in done:
+                main.wait_event(done.pop(l - (DEPTH - 1)))       # see tp.OutputGather: the ring slot comes round again
+            out = layer(l, step_md, *t)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(ready)
+                out.record_stream(copy_out)
+                host_out[l].copy_(share(out), non_blocking=True)
+                done[l] = torch.cuda.Event()
+                done[l].record(copy_out)
+        main.wait_stream(copy_out)
+
+    e2e_mode = "eager, kernel by kernel; metadata object rebuilt every step"
+    run_e2e = e2e_eager
+    if use_graph and graph is not None and not args.e2e_host_metadata:
+        # One CUDA graph for the whole step: index vectors in, validation, per layer QKV in -> kernels -> result out.
+        # The metadata object is built once on persistent device index vectors; every replay copies the step's
+        # vectors into them and validates them again on the device (`_revalidate_`: launches only).
+        with torch.cuda.stream(capture):
+            index_dev = [t.to(dev) for t in host_index]
+            md_e2e = rt.PagedMetadata.from_device(*index_dev, table_dev, prefix_list, length_list, slots)
+            md_e2e._set_fused_combine(combine_mode)
+            md_e2e.attention_plan(hq, hkv, d)
+            dev_qkv = torch.empty_like(resident_qkv)
+            dev_xr = torch.empty_like(resident_xr) if w.front else None
+
+            def e2e_body():
+                main = torch.cuda.current_stream()
+                copy_in.wait_stream(main)
+                copy_out.wait_stream(main)
+                with torch.cuda.stream(copy_in):
+                    for t, h in zip(index_dev, host_index):
+                        t.copy_(h, non_blocking=True)
+                    got_index = torch.cuda.Event()
+                    got_index.record(copy_in)
+                    arrived = []
+                    for l in range(L):
+                        dev_qkv[l].copy_(host_qkv[l], non_blocking=True)
+                        if w.front:
+                            dev_xr[l].copy_(host_xr[l], non_blocking=True)
+                        arrived.append(torch.cuda.Event())
+                        arrived[-1].record(copy_in)
+                main.wait_event(got_index)
+                md_e2e._revalidate_(*index_dev)
+                done = []
+                for l in range(L):
+                    main.wait_event(arrived[l])
+                    if gather is not None and l >= DEPTH - 1:
+                        main.wait_event(done[l - (DEPTH - 1)])
+                    out = layer(l, md_e2e, dev_qkv[l], xr_of(dev_xr, l))
+                    keep.append(out)
+                    ready = torch.cuda.Event()
+                    ready.record(main)
+                    with torch.cuda.stream(copy_out):
+                        copy_out.wait_event(ready)
+                        host_out[l].copy_(share(out), non_blocking=True)
+                        done.append(torch.cuda.Event())
+                        done[-1].record(copy_out)
+                main.wait_stream(copy_in)
+                main.wait_stream(copy_out)
+
+            for _ in range(max(2, DEPTH)):
+                e2e_body()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        if all(x.graph_safe(L) for x in exchanges):
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph, stream=capture):
+                e2e_body()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            run_e2e = e2e_graph.replay
+            e2e_mode = ("one CUDA graph per step, replayed: index vectors H2D -> validation on the device -> per layer "
+                        "QKV H2D, kernels, result D2H (copies on side streams inside the graph)")
     for _ in range(2):
-        e2e_step()
-    e2e_ms = timed(e2e_step, args.steps)
+        run_e2e()
+    e2e_ms = timed(run_e2e, args.steps)
     status = rt._C._take_device_status()
     assert status == 0, f"device status {status}"
 
@@ -551,11 +713,11 @@ def run_b200(args):
     seq = torch.tensor(md.sequences(), dtype=torch.int32).reshape(-1, 4).numpy()
     page = md.page_tokens()
     table = md.request_mapping()
-    dq = resident[0]
+    dq = [split(resident_qkv[l])[0] for l in range(L)]
     out = torch.empty(R, hq * d, dtype=torch.bfloat16, device=dev)
     s = H.stream_ptr()
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
-    if w.chunk > 1:
+    if not decode:
         work, rest = H.prefill_plan(seq, hq, hkv)
         assert len(rest) == 0
         combine, entries = [], 0
@@ -584,16 +746,17 @@ def run_b200(args):
         torch.cuda.synchronize()
     kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
 
+    if world > 1:
+        dist.barrier()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
     ms_per_step = total_ms / args.steps
     tokens_s = R / ms_per_step * 1e3
     e2e_tokens_s = R / (e2e_ms / args.steps) * 1e3
     kv_bytes = int(w.ctx.sum()) * hkv * d * 2 * 2
     peak, which = peaks()
-    if w.chunk > 1:
+    pushed = gather is not None and gather.mode == "push"
+    if not decode:
         flops = 4.0 * d * hq * w.visible_total
         achieved = flops / kernel_ms / 1e9
         tpeak, twhich = tensor_peak()
@@ -602,42 +765,61 @@ def run_b200(args):
                     "kernel": "paged_prefill_tc_kernel (tcgen05)", "kernel_ms": kernel_ms,
                     "algorithmic_flops_per_launch": flops, "work_items": len(work),
                     "frac_of_2250_nominal": achieved / 2250.0}
-        mine_per_layer = 2
+        per_layer = {"kv_store_kernel": 1, "paged_prefill_tc_kernel": 1}
     else:
         pages = int(((w.ctx + page - 1) // page).sum())
         algo_bytes = kv_bytes + 2 * B * hq * d * 2 + pages * 4 + len(work) * 32 + entries * (d + 2) * 4
         achieved = algo_bytes / kernel_ms / 1e6
+        # the ncu capture the traffic figure comes from is a config-2 launch (no split state): other
+        # workloads get no traffic figure rather than a borrowed one
+        measured_traffic = config == 2 and len(combine) == 0
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": TRAFFIC_PER_KV_BYTE * kv_bytes, "traffic_source": TRAFFIC_SOURCE,
+                    "traffic": TRAFFIC_PER_KV_BYTE * kv_bytes if measured_traffic else None,
+                    "traffic_source": TRAFFIC_SOURCE if measured_traffic else None,
                     "peak_source": f"{which} copy bandwidth", "kernel": "paged_attn_kernel<128,4,3>",
                     "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": algo_bytes,
                     "work_items": len(work), "split_blocks": len(combine),
                     "frac_of_8TBs_nominal": achieved / 8000.0}
-        mine_per_layer = 2 + (1 if len(combine) else 0) + (1 if gather is not None and gather.mode == "push" else 0) + \
-            (2 if w.front else 0)
-        if row_parallel is not None:       # rotary, store, attention (+ combine), o_proj, (barrier), sum + add + norm
-            mine_per_layer = 5 + (1 if len(combine) else 0) + (1 if row_parallel.mode == "push" else 0)
+        # the launch sequence layer() issues; the KV store rides in the attention launch on decode steps
+        # (in the rotary launch when the layer has a front)
+        fused_combine = combine_mode == 1 or (combine_mode == -1 and 0 < len(combine) * 4 <= 148)
+        per_layer = {"paged_attn_kernel": 1}
+        if len(combine) and not fused_combine:
+            per_layer["paged_attn_combine_kernel"] = 1
+        if pushed:
+            per_layer["peer_barrier_kernel"] = 1
+        if w.front:
+            per_layer.update(rms_norm_kernel=1, rotary_vec_kernel=1)
+        if row_parallel is not None:
+            per_layer = {"rotary_vec_kernel": 1, "paged_attn_kernel": 1, "linear_tc_kernel": 1, "rms_norm_kernel": 1}
+            if len(combine) and not fused_combine:
+                per_layer["paged_attn_combine_kernel"] = 1
+            if row_parallel.mode == "push":
+                per_layer["peer_barrier_kernel"] = 1
     index_bytes = (3 * R + mapping.numel() + 1) * 4 if args.e2e_host_metadata else (2 * R + B) * 4 + B * 16
-    h2d = sum(h[0].numel() * 2 for h in host_in) * L + index_bytes + work.nbytes + \
-        (combine.nbytes if len(combine) else 0)
+    h2d_rank = host_qkv.numel() * 2 + (host_xr.numel() * 2 if w.front else 0) + index_bytes
     line = {
-        "metric": METRIC if w.chunk == 1 else "paged_prefill_tokens_per_s", "value": tokens_s, "unit": "tokens/s",
+        "metric": METRIC if decode else "paged_prefill_tokens_per_s", "value": tokens_s, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(w, world, args.gather, args.oproj),
         "kv_read_gbs_whole_step": kv_bytes * L * world / ms_per_step / 1e6,
         "roofline": roofline,
-        "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(L * R * hq * world * d * 2) + (0 if args.e2e_host_metadata else 24),
+        "e2e": {"value": e2e_tokens_s, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_rank * world),
+                "d2h_bytes_per_step": int(L * R * hq * world * d * 2) + (0 if args.e2e_host_metadata or e2e_graph else 24 * world),
+                "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode,
+                "bytes": "whole job (all ranks); each rank reads back its rows/W share of the gathered output",
                 "metadata": ("validated on the host, request-to-token table uploaded every step" if args.e2e_host_metadata
                              else "request-to-token table resident on the device; the step's slot / request / position "
-                                  "vectors copied from pinned host memory and validated on the GPU (24-byte read-back)")},
-        "gpu_launches": args.steps * L * mine_per_layer,
+                                  "vectors copied from pinned host memory and validated on the GPU")},
+        "gpu_launches": args.steps * L * sum(per_layer.values()),
+        "launches_per_layer": per_layer,
         "launch_mode": "one CUDA graph per step, replayed" if graph is not None else "eager, kernel by kernel",
+        "parity": parity,
         "clocks": clocks.summary(),
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and headline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
         sample = CpuSample(w, cpu_sample_size(w, args.cpu_seqs))
@@ -648,7 +830,38 @@ def run_b200(args):
                                           f"({sample.tokens} visited keys; store + "
                                           f"{'tiled_bf16_pv(512)' if w.chunk > 1 else 'direct_bf16_pv'}), best of 2 after a "
                                           "warm-up, scaled linearly by visited keys"}
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    line = measure(args, args.config, world, rank, dev, headline=True)
+    # The tensor-parallel configurations ride along with the default multi-GPU run, so that one scaling
+    # sweep of the headline benchmark also carries their curves.
+    plain = args.config == 2 and not (args.layers or args.batch or args.ctx or args.oproj or args.no_graph)
+    if world > 1 and plain and not args.no_tp_configs:
+        extra = {}
+        for config in (3, 5):
+            gc.collect()
+            torch.cuda.empty_cache()
+            record = measure(args, config, world, rank, dev, headline=False)
+            if record is not None:
+                extra[str(config)] = {k: record[k] for k in ("value", "unit", "ms_per_step", "roofline", "e2e", "parity",
+                                                             "config", "gpu_launches", "launches_per_layer", "clocks")}
+        if line is not None:
+            line["tp_configs"] = extra
+    if line is not None:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -75,6 +75,18 @@ def _fake_paged_attn_validated(query, key, value, key_pool, value_pool, location
     return torch.empty_like(query, memory_format=torch.contiguous_format)
 
 
+@torch.library.register_fake("gaudirt::_paged_attn_stored")
+def _fake_paged_attn_stored(query, key_pool, value_pool, metadata, head_dim, scale, softcap=0.0, sliding_window=-1):
+    return torch.empty_like(query, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake("gaudirt::_rotary_kv_store")
+def _fake_rotary_kv_store(query, key, value, cache, metadata, key_pool, value_pool, head_dim, rotary_dim, is_neox):
+    torch._check(key.shape[0] == query.shape[0])
+    torch._check(value.shape[0] == query.shape[0])
+    return torch.empty_like(query, memory_format=torch.contiguous_format)
+
+
 @torch.library.register_fake("gaudirt::rms_norm")
 def _fake_rms_norm(input, weight, epsilon, weight_offset=0.0):
     return torch.empty_like(input, memory_format=torch.contiguous_format)

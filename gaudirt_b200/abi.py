@@ -29,6 +29,10 @@ PROTOTYPES = {
     "gk_prefill_plan_build": (i32, [vp, i64, i32, i32, i32, i32, vp, i64, i64p, vp, i64p]),
     "gk_paged_prefill_tc_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, f32, f32, i32,
                                        i32, i32, i32, vp, vp]),
+    "gk_paged_prefill_tc_multi_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i32, i64, f32, f32,
+                                             i32, i32, i32, i32, vp, vp]),
+    "gk_paged_attn_store_multi_bf16": (i32, [vp, i64, vp, vp, i64, i64, vp, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp,
+                                             i32, i64, vp, vp, vp, f32, f32, i32, i32, i32, i32, vp, vp]),
     "gk_paged_attn_multi_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i32, i64, vp, vp, vp, f32,
                                        f32, i32, i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_multi_bf16": (i32, [vp, vp, vp, i64, vp, i32, i64, i32, i32, vp]),

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/gaudirt_b200.h"
 
 namespace gk {
@@ -19,6 +21,22 @@ inline int check_launch() {
     g_last_cuda_error = static_cast<int>(e);
     return GK_ERR_CUDA;
   }
+  return GK_OK;
+}
+
+// The opt-in for more than 48 KB of dynamic shared memory is per device and has to be made once
+// before the first launch there.  `done` is one flag per device ordinal; the entry points may be
+// called from several host threads, so the flags are atomics (setting the attribute twice is
+// harmless, reading a half-written flag would not be).
+template <typename Kernel>
+inline int opt_in_shared_memory(Kernel kernel, int bytes, std::atomic<bool> (&done)[64]) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
+  const bool tracked = device >= 0 && device < 64;
+  if (tracked && done[device].load(std::memory_order_acquire)) return GK_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    return check_launch();
+  if (tracked) done[device].store(true, std::memory_order_release);
   return GK_OK;
 }
 

@@ -176,11 +176,23 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
       total_span += blocks.back().hi - lo;
     }
   }
-  // How a block's KV range is cut for a given longest-range limit: equal pieces, multiples of the
-  // 64 tokens four warps eat, and no cut for ranges within 25 % of the limit.
-  auto cut = [](int64_t span, int64_t chunk, int64_t& splits, int64_t& per) {
+  // How a block's KV range is cut for a given longest-range limit.  Even cut: equal pieces, multiples
+  // of the 64 tokens four warps eat, and no cut for ranges within 25 % of the limit.  Uneven cut: pieces
+  // of exactly `chunk` tokens and the remainder as the last piece (a remainder under 64 tokens stays with
+  // the piece before it).  The uneven cut is what fills the machine when a few hundred equal ranges meet
+  // a slightly larger number of resident CTA slots: every range gives up its tail, and the tails fill
+  // the slots that would have idled for the whole launch.
+  auto cut = [](int64_t span, int64_t chunk, bool uneven, int64_t& splits, int64_t& per) {
     splits = 1;
     per = span;
+    if (uneven) {
+      if (span >= chunk + 64) {
+        per = chunk;
+        splits = (span + per - 1) / per;
+        if (span - (splits - 1) * per < 64) --splits;
+      }
+      return;
+    }
     if (span > chunk + chunk / 4) {
       splits = (span + chunk - 1) / chunk;
       per = round_up((span + splits - 1) / splits, 64);
@@ -191,11 +203,13 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
   // per SM, handed out longest first by the hardware scheduler; the cost of a candidate limit is
   // the makespan of that list schedule (a CTA costs its tokens plus a fixed prologue/epilogue)
   // plus the split-state traffic of the combine.  Candidates: the throughput heuristic (about
-  // four CTAs per resident slot) and the longest range divided by small integers.
+  // four CTAs per resident slot), the longest range divided by small integers, and uneven cuts a
+  // little below the longest range.
   int64_t chunk = split_tokens;
+  bool uneven = false;
   // The count-only call and the filling call of one plan see the same input: remember the
   // last choice per thread instead of searching twice.
-  struct Memo { uint64_t key = 0; int64_t chunk = 0; };
+  struct Memo { uint64_t key = 0; int64_t chunk = 0; bool uneven = false; };
   thread_local Memo memo;
   uint64_t key = 1469598103934665603ull;
   auto mix = [&key](uint64_t v) { key = (key ^ v) * 1099511628211ull; };
@@ -203,6 +217,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
   mix(q_heads); mix(kv_heads); mix(head_dim); mix((uint32_t)window); mix(sm_count);
   if (chunk == 0 && memo.key == key && memo.chunk > 0) {
     chunk = memo.chunk;
+    uneven = memo.uneven;
   } else if (chunk == 0) {
     const int64_t slots_resident = (int64_t)sm_count * 2;
     const int64_t want = slots_resident * 4;
@@ -212,14 +227,14 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
     if ((int64_t)blocks.size() * kv_heads < 16 * slots_resident) {
       constexpr double kCtaOverheadTokens = 150.0;    // ~3.5 us of prologue + merge at 23 ns/token
       constexpr double kCombineLaunchTokens = 130.0;  // ~3 us
-      auto estimate = [&](int64_t limit) {
+      auto estimate = [&](int64_t limit, bool odd) {
         std::vector<int32_t> pieces;
         double combine_bytes = 0.0;
         for (const Block& b : blocks) {
           int64_t splits, per;
-          cut(b.hi - b.lo, limit, splits, per);
+          cut(b.hi - b.lo, limit, odd, splits, per);
           for (int64_t i = 0; i < splits; ++i)
-            pieces.push_back((int32_t)(std::min<int64_t>(b.hi, b.lo + (i + 1) * per) - (b.lo + i * per)));
+            pieces.push_back((int32_t)((i + 1 == splits ? (int64_t)b.hi : b.lo + (i + 1) * per) - (b.lo + i * per)));
           if (splits > 1) combine_bytes += 2.0 * splits * b.n_rows * q_heads * (head_dim + 2) * 4;
         }
         std::sort(pieces.begin(), pieces.end(), std::greater<int32_t>());
@@ -236,7 +251,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
         const double token_bytes = 2.0 * head_dim * 2;
         return makespan + combine_bytes / token_bytes / slots_resident + (combine_bytes > 0 ? kCombineLaunchTokens : 0.0);
       };
-      double best = estimate(chunk);
+      double best = estimate(chunk, false);
       for (int k : {1, 2, 3, 4, 6, 8, 12, 16}) {
         const int64_t candidate = round_up((longest + k - 1) / k, 64);
         if (candidate < 256) break;
@@ -244,19 +259,33 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
         int64_t ctas = 0;
         for (const Block& b : blocks) {
           int64_t splits, per;
-          cut(b.hi - b.lo, candidate, splits, per);
+          cut(b.hi - b.lo, candidate, false, splits, per);
           ctas += splits * kv_heads;
         }
         if (ctas > 12 * slots_resident) break;
-        const double cost = estimate(candidate);
+        const double cost = estimate(candidate, false);
         if (cost < best * 0.995) {
           best = cost;
           chunk = candidate;
+          uneven = false;
         }
       }
+      // Uneven cuts: only worth a look while the whole grid is a few waves (that is where idle slots cost most).
+      if ((int64_t)blocks.size() * kv_heads <= 4 * slots_resident)
+        for (int percent : {97, 94, 91, 88, 85, 80, 75, 70, 65, 60, 55}) {
+          const int64_t candidate = round_up(longest * percent / 100, 64);
+          if (candidate < 256 || candidate >= longest) continue;
+          const double cost = estimate(candidate, true);
+          if (cost < best * 0.98) {
+            best = cost;
+            chunk = candidate;
+            uneven = true;
+          }
+        }
     }
     memo.key = key;
     memo.chunk = chunk;
+    memo.uneven = uneven;
   }
   chunk = std::max<int64_t>(chunk, 16);
 
@@ -267,7 +296,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
   for (const Block& b : blocks) {
     const int64_t span = b.hi - b.lo;
     int64_t splits, per;
-    cut(span, chunk, splits, per);
+    cut(span, chunk, uneven, splits, per);
     if (splits > 0x7fff) return GK_ERR_CAPACITY;     // the split index shares a record word with the count
     int64_t base = -1;
     if (splits > 1) {
@@ -283,7 +312,7 @@ extern "C" int gk_attention_plan_build(const int32_t* seq, int64_t n_seq, int q_
       it.w[2] = b.first_pos;
       it.w[3] = b.table_row;
       it.w[4] = (int32_t)(b.lo + s * per);
-      it.w[5] = (int32_t)std::min<int64_t>(b.hi, b.lo + (s + 1) * per);
+      it.w[5] = s + 1 == splits ? b.hi : (int32_t)(b.lo + (s + 1) * per);
       it.w[6] = base < 0 ? -1 : (int32_t)(base + s * b.n_rows * q_heads);
       it.w[7] = (int32_t)(splits | (s << 16));     // low half: splits of the block, high half: which one
       items.push_back(it);

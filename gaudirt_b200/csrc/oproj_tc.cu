@@ -295,15 +295,9 @@ bool make_matrix_map(CUtensorMap* map, const void* data, int64_t rows, int64_t c
 template <int MT, int BN>
 int launch_linear(const LinearParams& p, const CUtensorMap& map_a, const CUtensorMap& map_w, int split, cudaStream_t stream) {
   using T = LinearTile<MT, BN>;
-  static bool configured[64] = {};
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
-  if (device < 0 || device >= 64 || !configured[device]) {
-    if (cudaFuncSetAttribute(linear_tc_kernel<MT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) !=
-        cudaSuccess)
-      return check_launch();
-    if (device >= 0 && device < 64) configured[device] = true;
-  }
+  static std::atomic<bool> configured[64];
+  const int ready = opt_in_shared_memory(linear_tc_kernel<MT, BN>, T::kSmemBytes, configured);
+  if (ready != GK_OK) return ready;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((unsigned)(p.n / BN), (unsigned)((p.m + kBM * MT - 1) / (kBM * MT)), (unsigned)split);
   config.blockDim = dim3(kLinearThreads);

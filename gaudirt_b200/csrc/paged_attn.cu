@@ -33,7 +33,14 @@ struct AttnParams {
   float* part_o;
   int32_t* status;
   int32_t* counters;                     // optional: per (first_row, kv_head) arrival counts for the fused combine
+  // optional fused KV store: the step's new K/V rows and their slots.  A CTA first writes the rows whose
+  // positions lie in its own KV range to the pool, then reads them back like any other token.
+  const __nv_bfloat16* new_k;
+  const __nv_bfloat16* new_v;
+  const int32_t* locations;
+  int64_t new_k_stride, new_v_stride;
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
+  int64_t part_capacity;                 // entries part_ml / part_o hold; a record that points past it is skipped
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group, n_out;
 };
@@ -103,6 +110,33 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
   const uint32_t ring = smem_u32(smem) + warp * C::kWarpBytes;
   const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * D;
   const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * D;
+
+  // ---- fused head-major KV store (gk_kv_store_head_major_bf16_v1 inside the attention launch, as the
+  // reference's single-block recipe does, src/bridge/paged_attention.cpp:74) ----------------------------
+  // Only offered for steps in which every sequence is one query block, so no other CTA reads these rows:
+  // the KV ranges of a block's splits partition its positions and each CTA stores exactly the new rows it
+  // will read.  Bytes are copied unchanged, 16 at a time.
+  if (p.new_k != nullptr) {
+    const int r_lo = max(0, kv_begin - first_pos), r_hi = min(n_rows, kv_end - first_pos);
+    if (r_lo < r_hi) {
+      const int per_kind = (r_hi - r_lo) * C::kChunks;
+      for (int idx = threadIdx.x; idx < 2 * per_kind; idx += WARPS * 32) {
+        const int kind = idx >= per_kind, rem = idx - kind * per_kind;
+        const int row = first_row + r_lo + rem / C::kChunks, col = rem % C::kChunks;
+        const int slot = __ldg(p.locations + row);
+        if ((unsigned)slot < (unsigned)p.slots) {
+          const __nv_bfloat16* src = (kind ? p.new_v + (int64_t)row * p.new_v_stride : p.new_k + (int64_t)row * p.new_k_stride) +
+                                     (int64_t)head * D + col * 8;
+          __nv_bfloat16* dst = const_cast<__nv_bfloat16*>(kind ? vbase : kbase) + (int64_t)slot * D + col * 8;
+          *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
+        } else if (col == 0 && kind == 0 && p.status) {
+          atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+        }
+      }
+      __threadfence_block();
+      __syncthreads();                                  // uniform per CTA: the range is the CTA's
+    }
+  }
   const int32_t* trow =
       p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
   const int page_mask = (1 << p.page_shift) - 1;
@@ -316,8 +350,12 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint2*>(p.out[dst] + at) = packed;
     } else {
       const int64_t entry = (int64_t)partial_base + (int64_t)r * p.q_heads + head * G + gq;
-      *reinterpret_cast<float4*>(p.part_o + entry * D + c4 * 4) = acc;
-      if (c4 == 0) *reinterpret_cast<float2*>(p.part_ml + entry * 2) = make_float2(mstar, lsum);
+      if (entry < p.part_capacity) {
+        *reinterpret_cast<float4*>(p.part_o + entry * D + c4 * 4) = acc;
+        if (c4 == 0) *reinterpret_cast<float2*>(p.part_ml + entry * 2) = make_float2(mstar, lsum);
+      } else if (c4 == 0 && p.status) {
+        atomicOr(p.status, (int)GK_DEV_BAD_SLOT);      // the record disagrees with the declared split state
+      }
     }
   }
 
@@ -343,6 +381,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
         const int prow = idx / (D / 4), c4 = idx - prow * (D / 4);
         const int r = prow / G, gq = prow - r * G;
         const int64_t e0 = base + (int64_t)r * p.q_heads + head * G + gq;
+        if (e0 < 0 || e0 + (int64_t)(n_splits - 1) * stride >= p.part_capacity) continue;   // flagged by the writer
         float mstar = -CUDART_INF_F;
         for (int s = 0; s < n_splits; ++s) {
           const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + e0 + (int64_t)s * stride);
@@ -386,11 +425,16 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
                                                                 const float* __restrict__ part_o,
                                                                 const int32_t* __restrict__ combine,
                                                                 const OutputList outs, int64_t out_stride,
-                                                                int q_heads) {
+                                                                int q_heads, int64_t capacity, int32_t* status) {
   const int4 rec = __ldg(reinterpret_cast<const int4*>(combine) + blockIdx.x);
   const int first_row = rec.x, n_rows = rec.y, base = rec.z, n_splits = rec.w;
   const int entries = n_rows * q_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // A record whose split state would lie outside the declared array is not read at all.
+  if (base < 0 || n_splits <= 0 || n_rows <= 0 || (int64_t)base + (int64_t)n_splits * entries > capacity) {
+    if (threadIdx.x == 0 && blockIdx.y == 0 && status) atomicOr(status, (int)GK_DEV_BAD_SLOT);
+    return;
+  }
   for (int e = blockIdx.y * 4 + warp; e < entries; e += gridDim.y * 4) {
     // (m, l) of up to 32 splits at a time, one per lane: the reference maximum and the weights come
     // from warp reductions, then the O rows (independent loads) are accumulated in split order.
@@ -458,31 +502,33 @@ template <int D>
 int launch_attn(const AttnParams& p, int64_t n_work, cudaStream_t stream) {
   using C = AttnConfig<D, kWarps, kStages>;
   auto kernel = paged_attn_kernel<D, kWarps, kStages>;
-  // The opt-in for more than 48 KB of dynamic shared memory is per device.
-  static bool configured[64] = {};
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return check_launch();
-  if (device < 0 || device >= 64 || !configured[device]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-      return check_launch();
-    if (device >= 0 && device < 64) configured[device] = true;
-  }
+  static std::atomic<bool> configured[64];
+  const int ready = opt_in_shared_memory(kernel, C::kSmemBytes, configured);
+  if (ready != GK_OK) return ready;
   const int64_t blocks = n_work * p.kv_heads;
   kernel<<<(unsigned)blocks, kWarps * 32, C::kSmemBytes, stream>>>(p);
   return check_launch();
 }
 
-}  // namespace
-}  // namespace gk
-
-extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
-                                        int64_t slots, const int32_t* table, int64_t table_stride,
-                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
-                                        const int32_t* work, int64_t n_work, void* const* outs, int n_outs,
-                                        int64_t out_row_stride, float* part_ml, float* part_o,
-                                        int32_t* split_counters, float scale, float softcap, int window, int q_heads,
-                                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
+// Argument checks + launch of the attention kernel.  `part_capacity` is the number of entries the
+// split-state arrays hold (INT64_MAX when the caller sized them from the schedule itself).
+int attn_entry(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v, int64_t slots,
+               const int32_t* table, int64_t table_stride, int64_t table_entry_stride, int page_tokens,
+               const int32_t* table_rows, const int32_t* work, int64_t n_work, void* const* outs, int n_outs,
+               int64_t out_row_stride, float* part_ml, float* part_o, int64_t part_capacity, int32_t* split_counters,
+               float scale, float softcap, int window, int q_heads, int kv_heads, int head_dim, int32_t* status,
+               gk_stream_t stream, const void* new_k = nullptr, const void* new_v = nullptr, int64_t new_k_stride = 0,
+               int64_t new_v_stride = 0, const int32_t* locations = nullptr) {
   if (n_work == 0) return GK_OK;
+  if (new_k || new_v || locations) {
+    // the fused store moves whole 16-byte pieces
+    if (!new_k || !new_v || !locations || new_k_stride < (int64_t)kv_heads * head_dim ||
+        new_v_stride < (int64_t)kv_heads * head_dim)
+      return GK_ERR_INVALID_ARGUMENT;
+    if (((reinterpret_cast<uintptr_t>(new_k) | reinterpret_cast<uintptr_t>(new_v)) & 15) || (new_k_stride & 7) ||
+        (new_v_stride & 7))
+      return GK_ERR_UNSUPPORTED;
+  }
   if (!outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS) return GK_ERR_INVALID_ARGUMENT;
   for (int i = 0; i < n_outs; ++i)
     if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 7)) return GK_ERR_INVALID_ARGUMENT;
@@ -500,7 +546,7 @@ extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, con
     return GK_ERR_INVALID_ARGUMENT;
   if (part_ml && ((reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15)))
     return GK_ERR_INVALID_ARGUMENT;
-  gk::AttnParams p{};
+  AttnParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.pool_k = static_cast<const __nv_bfloat16*>(pool_k);
   p.pool_v = static_cast<const __nv_bfloat16*>(pool_v);
@@ -514,6 +560,12 @@ extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, con
   p.part_o = part_o;
   p.status = status;
   p.counters = split_counters;
+  p.part_capacity = part_ml ? part_capacity : 0;
+  p.new_k = static_cast<const __nv_bfloat16*>(new_k);
+  p.new_v = static_cast<const __nv_bfloat16*>(new_v);
+  p.locations = locations;
+  p.new_k_stride = new_k_stride;
+  p.new_v_stride = new_v_stride;
   p.q_stride = q_row_stride;
   p.out_stride = out_row_stride;
   p.slots = slots;
@@ -527,10 +579,41 @@ extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, con
   p.group = q_heads / kv_heads;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (head_dim) {
-    case 64: return gk::launch_attn<64>(p, n_work, s);
-    case 128: return gk::launch_attn<128>(p, n_work, s);
-    default: return gk::launch_attn<256>(p, n_work, s);
+    case 64: return launch_attn<64>(p, n_work, s);
+    case 128: return launch_attn<128>(p, n_work, s);
+    default: return launch_attn<256>(p, n_work, s);
   }
+}
+
+}  // namespace
+}  // namespace gk
+
+extern "C" int gk_paged_attn_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                        int64_t slots, const int32_t* table, int64_t table_stride,
+                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
+                                        const int32_t* work, int64_t n_work, void* const* outs, int n_outs,
+                                        int64_t out_row_stride, float* part_ml, float* part_o,
+                                        int32_t* split_counters, float scale, float softcap, int window, int q_heads,
+                                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream) {
+  return gk::attn_entry(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride, page_tokens,
+                        table_rows, work, n_work, outs, n_outs, out_row_stride, part_ml, part_o, INT64_MAX,
+                        split_counters, scale, softcap, window, q_heads, kv_heads, head_dim, status, stream);
+}
+
+extern "C" int gk_paged_attn_store_multi_bf16(const void* q, int64_t q_row_stride, const void* new_k, const void* new_v,
+                                              int64_t new_k_row_stride, int64_t new_v_row_stride,
+                                              const int32_t* locations, void* pool_k, void* pool_v, int64_t slots,
+                                              const int32_t* table, int64_t table_stride, int64_t table_entry_stride,
+                                              int page_tokens, const int32_t* table_rows, const int32_t* work,
+                                              int64_t n_work, void* const* outs, int n_outs, int64_t out_row_stride,
+                                              float* part_ml, float* part_o, int32_t* split_counters, float scale,
+                                              float softcap, int window, int q_heads, int kv_heads, int head_dim,
+                                              int32_t* status, gk_stream_t stream) {
+  if (!new_k || !new_v || !locations) return GK_ERR_INVALID_ARGUMENT;
+  return gk::attn_entry(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride, page_tokens,
+                        table_rows, work, n_work, outs, n_outs, out_row_stride, part_ml, part_o, INT64_MAX,
+                        split_counters, scale, softcap, window, q_heads, kv_heads, head_dim, status, stream, new_k, new_v,
+                        new_k_row_stride, new_v_row_stride, locations);
 }
 
 extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
@@ -545,34 +628,53 @@ extern "C" int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const voi
                                   scale, softcap, window, q_heads, kv_heads, head_dim, status, stream);
 }
 
-extern "C" int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
-                                                int64_t n_combine, void* const* outs, int n_outs,
-                                                int64_t out_row_stride, int q_heads, int head_dim,
-                                                gk_stream_t stream) {
+namespace gk {
+namespace {
+// Checks of the combine arguments alone, so that a caller can make them before launching anything.
+int combine_check(const float* part_ml, const float* part_o, const int32_t* combine, int64_t n_combine,
+                  void* const* outs, int n_outs, int64_t out_row_stride, int q_heads, int head_dim) {
   if (n_combine == 0) return GK_OK;
   if (!part_ml || !part_o || !combine || !outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS || n_combine < 0 ||
       n_combine > 0x7fffffffLL || q_heads <= 0)
     return GK_ERR_INVALID_ARGUMENT;
-  gk::OutputList o{};
-  o.n = n_outs;
-  for (int i = 0; i < n_outs; ++i) {
+  for (int i = 0; i < n_outs; ++i)
     if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 7)) return GK_ERR_INVALID_ARGUMENT;
-    o.ptr[i] = static_cast<__nv_bfloat16*>(outs[i]);
-  }
   if ((out_row_stride & 3) || (reinterpret_cast<uintptr_t>(combine) & 15) ||
       (reinterpret_cast<uintptr_t>(part_ml) & 7) || (reinterpret_cast<uintptr_t>(part_o) & 15))
     return GK_ERR_INVALID_ARGUMENT;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256) return GK_ERR_UNSUPPORTED;
+  return GK_OK;
+}
+
+int combine_entry(const float* part_ml, const float* part_o, int64_t capacity, const int32_t* combine,
+                  int64_t n_combine, void* const* outs, int n_outs, int64_t out_row_stride, int q_heads, int head_dim,
+                  int32_t* status, gk_stream_t stream) {
+  if (n_combine == 0) return GK_OK;
+  const int checked = combine_check(part_ml, part_o, combine, n_combine, outs, n_outs, out_row_stride, q_heads, head_dim);
+  if (checked != GK_OK) return checked;
+  OutputList o{};
+  o.n = n_outs;
+  for (int i = 0; i < n_outs; ++i) o.ptr[i] = static_cast<__nv_bfloat16*>(outs[i]);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // Four entries per CTA; a decode record (one row) is covered in one pass, records with more
   // rows loop over them.
   const dim3 grid((unsigned)n_combine, (unsigned)((q_heads + 3) / 4));
   switch (head_dim) {
-    case 64: gk::paged_attn_combine_kernel<64><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
-    case 128: gk::paged_attn_combine_kernel<128><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
-    case 256: gk::paged_attn_combine_kernel<256><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads); break;
-    default: return GK_ERR_UNSUPPORTED;
+    case 64: paged_attn_combine_kernel<64><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
+    case 128: paged_attn_combine_kernel<128><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
+    default: paged_attn_combine_kernel<256><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
   }
-  return gk::check_launch();
+  return check_launch();
+}
+}  // namespace
+}  // namespace gk
+
+extern "C" int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
+                                                int64_t n_combine, void* const* outs, int n_outs,
+                                                int64_t out_row_stride, int q_heads, int head_dim,
+                                                gk_stream_t stream) {
+  return gk::combine_entry(part_ml, part_o, INT64_MAX, combine, n_combine, outs, n_outs, out_row_stride, q_heads,
+                           head_dim, nullptr, stream);
 }
 
 extern "C" int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o, const int32_t* combine,
@@ -628,16 +730,28 @@ extern "C" int gk_paged_attn_static_scratch_bf16(const void* q, int64_t q_row_st
                                                  void* out, int64_t out_row_stride, float scale, float softcap,
                                                  int window, int q_heads, int kv_heads, int head_dim, int32_t* status,
                                                  gk_stream_t stream) {
-  if (partial_entries < 0 || n_combine < 0) return GK_ERR_INVALID_ARGUMENT;
+  // Every argument is judged before the first launch, so a refused call leaves nothing half done.
+  if (partial_entries < 0 || n_combine < 0 || n_work < 0) return GK_ERR_INVALID_ARGUMENT;
+  // Split state and combine records come from one schedule: both present or both absent, and a
+  // combine without this call's attention launch would merge what an earlier call left behind.
+  if ((n_combine > 0) != (partial_entries > 0) || (n_combine > 0 && n_work == 0)) return GK_ERR_INVALID_ARGUMENT;
   if (partial_entries > GK_STATIC_SCRATCH_MAX_ENTRIES || head_dim > GK_STATIC_SCRATCH_MAX_HEAD_DIM) return GK_ERR_CAPACITY;
   float* base = nullptr;
   const int got = gk::static_scratch_address(&base);
   if (got != GK_OK) return got;
   float* part_ml = base;
   float* part_o = base + gk::kStaticMlFloats;
-  const int rc = gk_paged_attn_bf16(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
-                                    page_tokens, table_rows, work, n_work, out, out_row_stride, part_ml, part_o, scale,
-                                    softcap, window, q_heads, kv_heads, head_dim, status, stream);
+  void* const outs[1] = {out};
+  const int checked = gk::combine_check(part_ml, part_o, combine, n_combine, outs, 1, out_row_stride, q_heads, head_dim);
+  if (checked != GK_OK) return checked;
+  // The kernels get the declared entry count: a work or combine record that points past it is
+  // skipped and GK_DEV_BAD_SLOT is raised, so a schedule that disagrees with `partial_entries`
+  // cannot write outside the array.
+  const int rc = gk::attn_entry(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
+                                page_tokens, table_rows, work, n_work, outs, 1, out_row_stride, part_ml, part_o,
+                                partial_entries, nullptr, scale, softcap, window, q_heads, kv_heads, head_dim, status,
+                                stream);
   if (rc != GK_OK) return rc;
-  return gk_paged_attn_combine_bf16(part_ml, part_o, combine, n_combine, out, out_row_stride, q_heads, head_dim, stream);
+  return gk::combine_entry(part_ml, part_o, partial_entries, combine, n_combine, outs, 1, out_row_stride, q_heads,
+                           head_dim, status, stream);
 }

@@ -52,12 +52,13 @@ struct PrefillParams {
   const int32_t* table;
   const int32_t* table_rows;
   const int32_t* work;
-  __nv_bfloat16* out;
+  __nv_bfloat16* out[GK_MAX_OUTPUTS];   // every destination receives the same rows (peers under TP)
   int32_t* status;
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group;
   int tma_rows;          // rows of a TMA box (= page_tokens), 0 = TMA path off
+  int n_out;
 };
 
 struct Shared {
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int r_q = pr / G, g = pr - r_q * G;
-      __nv_bfloat16* dst = p.out + (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile + wg * 64;
+      const int64_t at = (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile + wg * 64;
 #pragma unroll 1
       for (int cb = 0; cb < 2; ++cb) {
         uint32_t r[32];
@@ -286,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
             v.y = pack_bf16(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
             v.z = pack_bf16(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
             v.w = pack_bf16(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + cb * 32 + c * 8) = v;
+            for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint4*>(p.out[dst] + at + cb * 32 + c * 8) = v;
           }
         }
       }
@@ -426,22 +427,25 @@ constexpr int kSmemBytes = 7 * kTileBytes + 3072;   // 227 KiB: the whole opt-in
 }  // namespace
 }  // namespace gk
 
-extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
-                                        int64_t slots, const int32_t* table, int64_t table_stride,
-                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
-                                        const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
-                                        float scale, float softcap, int window, int q_heads, int kv_heads, int head_dim,
-                                        int32_t* status, gk_stream_t stream) {
+extern "C" int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                                              const void* pool_v, int64_t slots, const int32_t* table,
+                                              int64_t table_stride, int64_t table_entry_stride, int page_tokens,
+                                              const int32_t* table_rows, const int32_t* work, int64_t n_work,
+                                              void* const* outs, int n_outs, int64_t out_row_stride, float scale,
+                                              float softcap, int window, int q_heads, int kv_heads, int head_dim,
+                                              int32_t* status, gk_stream_t stream) {
   if (n_work == 0) return GK_OK;
-  if (!q || !pool_k || !pool_v || !table || !work || !out || n_work < 0 || slots <= 0 || table_stride < 0 ||
+  if (!outs || n_outs <= 0 || n_outs > GK_MAX_OUTPUTS) return GK_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < n_outs; ++i)
+    if (!outs[i] || (reinterpret_cast<uintptr_t>(outs[i]) & 15)) return GK_ERR_INVALID_ARGUMENT;
+  if (!q || !pool_k || !pool_v || !table || !work || n_work < 0 || slots <= 0 || table_stride < 0 ||
       table_entry_stride <= 0 || page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
       !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
     return GK_ERR_INVALID_ARGUMENT;
   if (head_dim != 128 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS ||
       n_work * kv_heads > 0x7fffffffLL)
     return GK_ERR_UNSUPPORTED;
-  if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(out) |
-        reinterpret_cast<uintptr_t>(work)) & 15) || (out_row_stride & 7) || (reinterpret_cast<uintptr_t>(q) & 1))
+  if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(work)) & 15) || (out_row_stride & 7) || (reinterpret_cast<uintptr_t>(q) & 1))
     return GK_ERR_INVALID_ARGUMENT;
   gk::PrefillParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -450,7 +454,8 @@ extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, con
   p.table = table;
   p.table_rows = table_rows;
   p.work = work;
-  p.out = static_cast<__nv_bfloat16*>(out);
+  for (int i = 0; i < n_outs; ++i) p.out[i] = static_cast<__nv_bfloat16*>(outs[i]);
+  p.n_out = n_outs;
   p.status = status;
   p.q_stride = q_row_stride;
   p.out_stride = out_row_stride;
@@ -464,24 +469,20 @@ extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, con
   p.q_heads = q_heads;
   p.kv_heads = kv_heads;
   p.group = q_heads / kv_heads;
-  static bool configured[64] = {};
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return gk::check_launch();
-  if (device < 0 || device >= 64 || !configured[device]) {
-    if (cudaFuncSetAttribute(gk::paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gk::kSmemBytes) !=
-        cudaSuccess)
-      return gk::check_launch();
-    if (device >= 0 && device < 64) configured[device] = true;
-  }
+  static std::atomic<bool> configured[64];
+  const int ready = gk::opt_in_shared_memory(gk::paged_prefill_tc_kernel, gk::kSmemBytes, configured);
+  if (ready != GK_OK) return ready;
   {
     // Never launch if the register pool of this build cannot satisfy the budgets (the kernel would hang).
-    static int launch_regs = -1;
-    if (launch_regs < 0) {
+    static std::atomic<int> launch_regs{-1};
+    int regs = launch_regs.load(std::memory_order_acquire);
+    if (regs < 0) {
       cudaFuncAttributes attr;
       if (cudaFuncGetAttributes(&attr, gk::paged_prefill_tc_kernel) != cudaSuccess) return gk::check_launch();
-      launch_regs = attr.numRegs;
+      regs = attr.numRegs;
+      launch_regs.store(regs, std::memory_order_release);
     }
-    if (launch_regs * gk::kThreads <
+    if (regs * gk::kThreads <
         gk::kSoftmaxThreads * gk::kSoftmaxRegs + (gk::kThreads - gk::kSoftmaxThreads) * gk::kOtherRegs)
       return GK_ERR_UNSUPPORTED;
   }
@@ -497,4 +498,16 @@ extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, con
   gk::paged_prefill_tc_kernel<<<(unsigned)(n_work * kv_heads), gk::kThreads, gk::kSmemBytes,
                                 reinterpret_cast<cudaStream_t>(stream)>>>(p, map_k, map_v);
   return gk::check_launch();
+}
+
+extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,
+                                        int64_t slots, const int32_t* table, int64_t table_stride,
+                                        int64_t table_entry_stride, int page_tokens, const int32_t* table_rows,
+                                        const int32_t* work, int64_t n_work, void* out, int64_t out_row_stride,
+                                        float scale, float softcap, int window, int q_heads, int kv_heads, int head_dim,
+                                        int32_t* status, gk_stream_t stream) {
+  void* const outs[1] = {out};
+  return gk_paged_prefill_tc_multi_bf16(q, q_row_stride, pool_k, pool_v, slots, table, table_stride, table_entry_stride,
+                                        page_tokens, table_rows, work, n_work, outs, 1, out_row_stride, scale, softcap,
+                                        window, q_heads, kv_heads, head_dim, status, stream);
 }

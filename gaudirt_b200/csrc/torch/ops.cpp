@@ -25,10 +25,16 @@ int64_t paged_attn_kv_tile(int64_t) { return GK_REFERENCE_KV_TILE; }
 // Shared body of the attention operators.  With `pushed` empty the result is a fresh tensor;
 // otherwise every tensor of `pushed` (one per tensor-parallel rank, peer-mapped, same shape and
 // strides) receives the rows and nothing is returned.
-at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
-                           at::Tensor& key_pool, at::Tensor& value_pool, const at::Tensor& locations,
-                           const at::Tensor& plan_tensor, int64_t head_dim, double scale, double softcap,
-                           int64_t sliding_window, const std::vector<at::Tensor>& pushed) {
+// Without `key` / `value` the step's rows are already in the pool (stored by the rotary kernel) and no store runs.
+at::Tensor paged_attn_impl(const at::Tensor& query, const c10::optional<at::Tensor>& key_in,
+                           const c10::optional<at::Tensor>& value_in, at::Tensor& key_pool, at::Tensor& value_pool,
+                           const at::Tensor& locations, const at::Tensor& plan_tensor, int64_t head_dim, double scale,
+                           double softcap, int64_t sliding_window, const std::vector<at::Tensor>& pushed) {
+  const bool store = key_in.has_value() && key_in->defined();
+  TORCH_CHECK(store == (value_in.has_value() && value_in->defined()),
+              "GaudiRT attention: Q/K/V must be BF16 device matrices with matching rows");
+  const at::Tensor& key = store ? *key_in : query;        // stand-ins pass the shared checks when no store runs
+  const at::Tensor& value = store ? *value_in : query;
   const auto& plan = plan_of(plan_tensor);
   const auto device = plan_tensor.device();
   c10::cuda::CUDAGuard guard(device);
@@ -44,7 +50,7 @@ at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const
     TORCH_CHECK(input.is_cuda() && input.device() == device && input.scalar_type() == at::kBFloat16 &&
                     input.dim() == 2 && input.size(0) == plan.rows,
                 "GaudiRT attention: Q/K/V must be BF16 device matrices with matching rows");
-  TORCH_CHECK(query.size(1) == plan.query_heads * head_dim && key.size(1) == plan.kv_heads * head_dim &&
+  TORCH_CHECK(query.size(1) == plan.query_heads * head_dim && (!store || key.size(1) == plan.kv_heads * head_dim) &&
                   value.size(1) == key.size(1) && locations.dim() == 1 && locations.numel() == plan.rows &&
                   locations.scalar_type() == at::kInt && locations.device() == device && locations.is_contiguous(),
               "GaudiRT attention: Q/K/V or slot dimensions do not match metadata");
@@ -61,8 +67,8 @@ at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const
               "GaudiRT attention: KV pool descriptor is not backed by combined storage");
   // Row-strided column slices are read in place; anything else is packed first.
   const at::Tensor q = query.stride(1) == 1 ? query : query.contiguous();
-  const at::Tensor k = key.stride(1) == 1 ? key : key.contiguous();
-  const at::Tensor v = value.stride(1) == 1 ? value : value.contiguous();
+  const at::Tensor k = !store || key.stride(1) == 1 ? key : key.contiguous();
+  const at::Tensor v = !store || value.stride(1) == 1 ? value : value.contiguous();
   at::Tensor output;
   std::vector<void*> outs;
   int64_t out_stride = query.size(1);
@@ -76,48 +82,60 @@ at::Tensor paged_attn_impl(const at::Tensor& query, const at::Tensor& key, const
       TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.size(0) == plan.rows &&
                       t.size(1) == query.size(1) && t.stride(1) == 1 && t.stride(0) == out_stride,
                   "GaudiRT attention: gather destinations must be BF16 [rows, q_width] column blocks of equal stride");
+      TORCH_CHECK(plan.n_prefill == 0 || (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && out_stride % 8 == 0),
+                  "GaudiRT attention: gather destinations of a prefill step must be 16-byte aligned");
       outs.push_back(t.data_ptr());
     }
   }
   int32_t* status = device_status(device.index()).data_ptr<int32_t>();
   const gk_stream_t s = stream_of(stream);
-  check_status(gk_kv_store_head_major_bf16(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
-                                           locations.data_ptr<int32_t>(), plan.rows, key_pool.data_ptr(),
-                                           value_pool.data_ptr(), plan.slots, (int)plan.kv_heads, (int)head_dim, status, s),
-               "KV store");
   const int32_t* words = plan.buffer.data_ptr<int32_t>();
-  check_status(gk_paged_attn_multi_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
-                                        plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride,
-                                        plan.page_tokens,
-                                        plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr, words,
-                                        plan.n_work, outs.data(), (int)outs.size(), out_stride,
-                                        plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
-                                        plan.counters.defined() ? plan.counters.data_ptr<int32_t>() : nullptr, scale_f,
-                                        softcap_f, (int)sliding_window, (int)plan.query_heads, (int)plan.kv_heads,
-                                        (int)head_dim, status, s),
-               "paged attention");
+  const int32_t* table_rows = plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr;
+  int32_t* counters = plan.counters.defined() ? plan.counters.data_ptr<int32_t>() : nullptr;
+  // The store rides in the attention launch when every sequence is one query block (any decode step) and
+  // the rows can be moved 16 bytes at a time; otherwise it is its own launch first, as in the reference
+  // (`separate_store`, src/bridge/paged_attention.cpp:251-263).
+  const bool fused_store = store && plan.single_block && fuse_kv_store() &&
+                           (reinterpret_cast<uintptr_t>(k.data_ptr()) | reinterpret_cast<uintptr_t>(v.data_ptr())) % 16 == 0 &&
+                           k.stride(0) % 8 == 0 && v.stride(0) % 8 == 0;
+  if (store && !fused_store)
+    check_status(gk_kv_store_head_major_bf16(k.data_ptr(), v.data_ptr(), k.stride(0), v.stride(0),
+                                             locations.data_ptr<int32_t>(), plan.rows, key_pool.data_ptr(),
+                                             value_pool.data_ptr(), plan.slots, (int)plan.kv_heads, (int)head_dim, status, s),
+                 "KV store");
+  if (fused_store)
+    check_status(gk_paged_attn_store_multi_bf16(q.data_ptr(), q.stride(0), k.data_ptr(), v.data_ptr(), k.stride(0),
+                                                v.stride(0), locations.data_ptr<int32_t>(), key_pool.data_ptr(),
+                                                value_pool.data_ptr(), plan.slots, plan.table.data_ptr<int32_t>(),
+                                                plan.table_stride, plan.entry_stride, plan.page_tokens, table_rows, words,
+                                                plan.n_work, outs.data(), (int)outs.size(), out_stride,
+                                                plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(), counters,
+                                                scale_f, softcap_f, (int)sliding_window, (int)plan.query_heads,
+                                                (int)plan.kv_heads, (int)head_dim, status, s),
+                 "paged attention");
+  else
+    check_status(gk_paged_attn_multi_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
+                                          plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride,
+                                          plan.page_tokens, table_rows, words, plan.n_work, outs.data(), (int)outs.size(),
+                                          out_stride, plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(), counters,
+                                          scale_f, softcap_f, (int)sliding_window, (int)plan.query_heads,
+                                          (int)plan.kv_heads, (int)head_dim, status, s),
+                 "paged attention");
   if (!plan.counters.defined())     // otherwise the combine ran inside: the last split to finish merged its block
     check_status(gk_paged_attn_combine_multi_bf16(plan.part_ml.data_ptr<float>(), plan.part_o.data_ptr<float>(),
                                                   words + plan.combine_offset, plan.n_combine, outs.data(),
                                                   (int)outs.size(), out_stride, (int)plan.query_heads, (int)head_dim, s),
                  "split-KV combine");
-  if (plan.n_prefill > 0) {
-    // Query tiles of multi-row sequences: tcgen05 kernel, one destination.  With several gather
-    // destinations the rows are staged once and copied to each of them.
-    at::Tensor staged = pushed.empty() ? output : at::empty({plan.rows, query.size(1)}, query.options());
-    check_status(gk_paged_prefill_tc_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(), plan.slots,
-                                          plan.table.data_ptr<int32_t>(), plan.table_stride, plan.entry_stride,
-                                          plan.page_tokens,
-                                          plan.table_rows.defined() ? plan.table_rows.data_ptr<int32_t>() : nullptr,
-                                          words + plan.prefill_offset, plan.n_prefill, staged.data_ptr(), staged.stride(0),
-                                          scale_f, softcap_f, (int)sliding_window, (int)plan.query_heads,
-                                          (int)plan.kv_heads, (int)head_dim, status, s),
+  if (plan.n_prefill > 0)
+    // Query tiles of multi-row sequences: tcgen05 kernel, same destinations (a mixed prefill + decode
+    // step is one call, as in src/bridge/paged_attention.cpp:251-345; the two kernels write disjoint rows).
+    check_status(gk_paged_prefill_tc_multi_bf16(q.data_ptr(), q.stride(0), key_pool.data_ptr(), value_pool.data_ptr(),
+                                                plan.slots, plan.table.data_ptr<int32_t>(), plan.table_stride,
+                                                plan.entry_stride, plan.page_tokens,
+                                                table_rows, words + plan.prefill_offset, plan.n_prefill, outs.data(), (int)outs.size(),
+                                                out_stride, scale_f, softcap_f, (int)sliding_window, (int)plan.query_heads,
+                                                (int)plan.kv_heads, (int)head_dim, status, s),
                  "tensor-core prefill");
-    if (!pushed.empty()) {
-      TORCH_CHECK(plan.n_work == 0, "GaudiRT attention: mixed prefill and decode rows are not supported with gather destinations");
-      for (const auto& t : pushed) const_cast<at::Tensor&>(t).copy_(staged, /*non_blocking=*/true);
-    }
-  }
   return output;
 }
 
@@ -133,7 +151,8 @@ at::Tensor paged_attn_validated(const at::Tensor& query, const at::Tensor& key, 
 // Attention whose epilogue is the tensor-parallel output gather: the rows are stored into every
 // tensor of `outputs` (this rank's column block of each rank's gathered activation).  Not in the
 // reference, which gathers with a separate collective (src/bridge/segmented_runner.cpp:170-191).
-void paged_attn_push(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, at::Tensor& key_pool,
+void paged_attn_push(const at::Tensor& query, const c10::optional<at::Tensor>& key,
+                     const c10::optional<at::Tensor>& value, at::Tensor& key_pool,
                      at::Tensor& value_pool, const at::Tensor& locations, const at::Tensor& plan_tensor,
                      at::TensorList outputs, int64_t head_dim, double scale, double softcap, int64_t sliding_window) {
   TORCH_CHECK(!outputs.empty(), "GaudiRT attention: gather destinations are required");
@@ -304,6 +323,67 @@ std::tuple<at::Tensor, at::Tensor> rotary_embedding_positions(const at::Tensor& 
                                     cache.dim() == 2 ? cache.size(0) : 0, head_dim, rotary_dim, is_neox);
 }
 
+// Rotary fused with the head-major KV store: the rotated K row and the V row go straight to slot
+// locations[row] of the pool, the rotated Q is returned; `_paged_attn_stored` then attends without
+// a store of its own.  One launch where the reference's decoder layer runs two
+// (tests/frozen_same_geometry_layer_smoke.py:22-37: rotary, then the store inside attention).
+at::Tensor rotary_kv_store(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, const at::Tensor& cache,
+                           const c10::intrusive_ptr<PagedMetadata>& metadata, at::Tensor& key_pool, at::Tensor& value_pool,
+                           int64_t head_dim, int64_t rotary_dim, bool is_neox) {
+  TORCH_CHECK(metadata, "GaudiRT rotary: metadata is required");
+  TORCH_CHECK(head_dim > 0 && head_dim <= INT32_MAX && rotary_dim > 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+              "GaudiRT rotary: invalid head or rotary dimension");
+  for (const auto& t : {query, key, value, cache})
+    TORCH_CHECK(t.is_cuda() && t.device() == query.device() && t.scalar_type() == at::kBFloat16,
+                "GaudiRT rotary: expected CUDA BF16 tensors");
+  const auto rows = query.dim() == 2 ? query.size(0) : -1;
+  TORCH_CHECK(query.dim() == 2 && key.dim() == 2 && value.dim() == 2 && rows > 0 && rows == metadata->rows() &&
+                  key.size(0) == rows && value.size(0) == rows && query.size(1) > 0 && key.size(1) > 0 &&
+                  query.size(1) % head_dim == 0 && key.size(1) % head_dim == 0 && value.size(1) == key.size(1),
+              "GaudiRT rotary: invalid query or key geometry");
+  TORCH_CHECK(cache.dim() == 2 && cache.size(0) >= metadata->context() && cache.size(0) <= INT32_MAX &&
+                  cache.size(1) == rotary_dim,
+              "GaudiRT rotary: cache does not cover validated positions");
+  const int64_t kv_heads = key.size(1) / head_dim, slots = metadata->slots();
+  for (const auto& pool : {key_pool, value_pool})
+    TORCH_CHECK(pool.is_cuda() && pool.device() == query.device() && pool.scalar_type() == at::kBFloat16 &&
+                    pool.dim() == 3 && pool.size(0) == slots && pool.size(1) == kv_heads && pool.size(2) == head_dim &&
+                    pool.stride(0) == head_dim && pool.stride(1) == slots * head_dim && pool.stride(2) == 1,
+                "GaudiRT attention: head-major combined KV pool is required");
+  c10::cuda::CUDAGuard guard(query.device());
+  const at::Tensor q = query.stride(1) == 1 ? query : query.contiguous();
+  const at::Tensor k = key.stride(1) == 1 ? key : key.contiguous();
+  const at::Tensor v = value.stride(1) == 1 ? value : value.contiguous();
+  const at::Tensor table = cache.contiguous();
+  auto q_out = at::empty({rows, query.size(1)}, query.options().memory_format(at::MemoryFormat::Contiguous));
+  check_status(gk_rotary_kv_store_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                                       table.data_ptr(), table.size(0), metadata->rotary_positions().data_ptr<int32_t>(),
+                                       metadata->row_locations().data_ptr<int32_t>(), rows, query.size(1), key.size(1),
+                                       (int)head_dim, (int)rotary_dim, is_neox ? 1 : 0, q_out.data_ptr(), nullptr,
+                                       key_pool.data_ptr(), value_pool.data_ptr(), slots,
+                                       device_status(query.device().index()).data_ptr<int32_t>(),
+                                       stream_of(at::cuda::getCurrentCUDAStream())),
+               "rotary + KV store");
+  return q_out;
+}
+
+// Attention over a pool that already holds the step's rows (after `_rotary_kv_store`).
+at::Tensor paged_attn_stored(const at::Tensor& query, at::Tensor& key_pool, at::Tensor& value_pool,
+                             const c10::intrusive_ptr<PagedMetadata>& metadata, int64_t head_dim, double scale,
+                             double softcap, int64_t sliding_window) {
+  TORCH_CHECK(metadata, "GaudiRT paged attention: metadata is required");
+  TORCH_CHECK(query.dim() == 2 && key_pool.dim() == 3 && (head_dim == 64 || head_dim == 128 || head_dim == 256),
+              "GaudiRT paged attention: invalid tensor ranks or head dimension");
+  const auto q_heads = query.size(1) / head_dim;
+  const auto kv_heads = key_pool.size(1);
+  auto plan = sliding_window > 0 ? metadata->attention_plan_for(q_heads, kv_heads, head_dim, sliding_window)
+                                 : metadata->attention_plan(q_heads, kv_heads, head_dim);
+  return paged_attn_impl(query, c10::nullopt, c10::nullopt, key_pool, value_pool, metadata->row_locations(), plan,
+                         head_dim, scale, softcap, sliding_window, {});
+}
+
+void set_fused_kv_store(bool on) { fuse_kv_store_flag().store(on); }
+
 // Reads and clears the device status word of the current device (synchronises the stream).
 int64_t take_device_status() {
   auto& word = device_status(at::cuda::current_device());
@@ -322,6 +402,7 @@ TORCH_LIBRARY(gaudirt, m) {
       .def_static("from_device_with_tokens", &PagedMetadata::from_device_with_tokens)
       .def_static("_from_scheduler", &PagedMetadata::from_scheduler)
       .def_static("_from_scheduler_fused", &PagedMetadata::from_scheduler_fused)
+      .def("_revalidate_", &PagedMetadata::revalidate_)
       .def("rows", &PagedMetadata::rows)
       .def("slots", &PagedMetadata::slots)
       .def("context", &PagedMetadata::context)
@@ -347,9 +428,16 @@ TORCH_LIBRARY(gaudirt, m) {
   m.def("_paged_attn_validated(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "Tensor locations, Tensor requests, Tensor positions, Tensor mapping, Tensor header, "
         "int head_dim, float scale, float softcap=0.0, int sliding_window=-1) -> Tensor");
-  m.def("_paged_attn_push(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+  m.def("_paged_attn_push(Tensor query, Tensor? key, Tensor? value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "Tensor locations, Tensor plan, Tensor(c!)[] outputs, int head_dim, float scale, float softcap=0.0, "
         "int sliding_window=-1) -> ()");
+  m.def("_paged_attn_stored(Tensor query, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+        "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, float scale, "
+        "float softcap=0.0, int sliding_window=-1) -> Tensor");
+  m.def("_rotary_kv_store(Tensor query, Tensor key, Tensor value, Tensor cache, "
+        "__torch__.torch.classes.gaudirt.PagedMetadata metadata, Tensor(a!) key_pool, Tensor(b!) value_pool, "
+        "int head_dim, int rotary_dim, bool is_neox) -> Tensor");
+  m.def("_set_fused_kv_store(bool on) -> ()", &gaudirt_b200::set_fused_kv_store);
   m.def("_peer_barrier(Tensor(a!)[] flags, int rank, int epoch, int max_cycles) -> ()");
   m.def("_peer_barrier_counted(Tensor(a!)[] flags, int rank, Tensor(b!) counter, int max_cycles) -> ()");
   m.def("rms_norm(Tensor input, Tensor weight, float epsilon, float weight_offset=0.0) -> Tensor");
@@ -384,6 +472,8 @@ TORCH_LIBRARY_IMPL(gaudirt, CUDA, m) {
   m.impl("paged_attn", TORCH_FN(gaudirt_b200::paged_attn));
   m.impl("_paged_attn_validated", TORCH_FN(gaudirt_b200::paged_attn_validated));
   m.impl("_paged_attn_push", TORCH_FN(gaudirt_b200::paged_attn_push));
+  m.impl("_paged_attn_stored", TORCH_FN(gaudirt_b200::paged_attn_stored));
+  m.impl("_rotary_kv_store", TORCH_FN(gaudirt_b200::rotary_kv_store));
   m.impl("_peer_barrier", TORCH_FN(gaudirt_b200::peer_barrier));
   m.impl("_peer_barrier_counted", TORCH_FN(gaudirt_b200::peer_barrier_counted));
   m.impl("rms_norm", TORCH_FN(gaudirt_b200::rms_norm));

@@ -10,6 +10,8 @@
 #include <torch/custom_class.h>
 #include <torch/library.h>
 
+#include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <memory>
@@ -45,6 +47,13 @@ inline at::Tensor& device_status(c10::DeviceIndex device) {
   return words[device];
 }
 
+// Whether the KV store may ride in the attention launch (on by default; a test and tuning switch).
+inline std::atomic<bool>& fuse_kv_store_flag() {
+  static std::atomic<bool> flag{true};
+  return flag;
+}
+inline bool fuse_kv_store() { return fuse_kv_store_flag().load(std::memory_order_relaxed); }
+
 // Clears `bits` of the device status word, in stream order: for errors that were raised on the host.
 inline void clear_status_bits(c10::DeviceIndex device, int bits) { device_status(device).bitwise_and_(~bits); }
 
@@ -67,6 +76,9 @@ struct AttentionPlan {
   int64_t n_work = 0, n_combine = 0, combine_offset = 0, table_stride = 0, entry_stride = 1;
   int64_t n_prefill = 0, prefill_offset = 0;   // query tiles for the tensor-core prefill kernel
   int page_tokens = 1;
+  // Every sequence of the step is one query block of the decode kernel (no other CTA reads a new row):
+  // the KV store may then ride in the attention launch.
+  bool single_block = false;
 };
 
 inline void release_plan(void* context) { delete static_cast<AttentionPlan*>(context); }
@@ -138,6 +150,14 @@ class PagedMetadata : public torch::CustomClassHolder {
     slots_ = slots;
     request_count_ = n_req;
     context_ = context;
+    {
+      // No sequence reads a row another sequence of this step writes iff no request occurs twice
+      // (a continuation chunk of the same request sees the earlier chunk's new rows).
+      std::vector<int32_t> seen;
+      for (int64_t i = 0; i < n_seq; ++i) seen.push_back(sequences_[static_cast<size_t>(i) * 4 + 3]);
+      std::sort(seen.begin(), seen.end());
+      rows_independent_ = std::adjacent_find(seen.begin(), seen.end()) == seen.end();
+    }
 
     const auto device = c10::Device(c10::kCUDA, at::cuda::current_device());
     const int64_t words = 3 * m + n_req * context + 1;
@@ -205,6 +225,10 @@ class PagedMetadata : public torch::CustomClassHolder {
     request_count_ = mapping.size(0);
     context_ = context;
     mapping_ = mapping;
+    // The validated form rejects (code 7) a batch in which a cached prefix names a slot this step
+    // writes, so its sequences never read each other's new rows; the scheduler-owned form skips
+    // that check and nothing is known here.
+    rows_independent_ = !scheduler_owned;
     const auto i32 = at::TensorOptions().dtype(at::kInt).device(device);
     auto seq_device = staging.to(device, /*non_blocking=*/true);
     // Strided views (a column of a scheduler's packed buffer) are packed first, like the
@@ -244,6 +268,11 @@ class PagedMetadata : public torch::CustomClassHolder {
                      reinterpret_cast<uint64_t*>(verdict.data_ptr<int64_t>()),
                      device_status(device.index()).data_ptr<int32_t>(), stream_of(stream)),
                  "device metadata");
+    dev_seq_ = seq_device;
+    dev_workspace_ = workspace;
+    dev_verdict_ = verdict;
+    dev_row_status_ = row_status;
+    table_checked_ = !scheduler_owned;
     if (!scheduler_owned) {
       const auto host = verdict.cpu();   // 24 bytes: the only read-back of the step
       const uint64_t first = static_cast<uint64_t>(host.data_ptr<int64_t>()[0]);
@@ -291,6 +320,40 @@ class PagedMetadata : public torch::CustomClassHolder {
                              slots, token_ids, vocabulary);
     md->attention_plan(query_heads, kv_heads, head_dim);
     return md;
+  }
+
+  // Validates a NEW set of index vectors for a step of the SAME shape (same sequences, prefixes and
+  // lengths) into this object's device tensors, so that everything bound to them -- the attention
+  // plan, a captured CUDA graph -- stays valid.  Only kernel launches on the current stream: no
+  // allocation, no host staging, no read-back, so the call can be captured and replayed with the
+  // index vectors refreshed in place before every replay.  A rejection sets GK_DEV_BAD_METADATA in
+  // the device status word (read it at the end of the step).  Not part of the reference surface,
+  // whose fused scheduler form (src/bridge/paged_metadata.hpp:45-64) rebuilds the object instead.
+  void revalidate_(const at::Tensor& locations, const at::Tensor& batch_requests, const at::Tensor& positions) {
+    TORCH_CHECK(dev_seq_.defined(), "GaudiRT device metadata: only device-validated metadata can be revalidated");
+    TORCH_CHECK(!token_ids_.defined(), "GaudiRT device metadata: revalidation with token IDs is not supported");
+    const auto device = locations_.device();
+    const int64_t batch = dev_seq_.numel() / 4;
+    for (const auto& t : {locations, batch_requests, positions})
+      TORCH_CHECK(t.is_cuda() && t.device() == device && t.dim() == 1 && t.is_contiguous() &&
+                      (t.scalar_type() == at::kInt || t.scalar_type() == at::kLong),
+                  "GaudiRT device metadata: expected CUDA int32 or int64 vectors");
+    TORCH_CHECK(locations.numel() == rows_ && positions.numel() == rows_ && batch_requests.numel() == batch,
+                "GaudiRT device metadata: dimensions outside supported range");
+    TORCH_CHECK(batch_requests.scalar_type() == at::kInt && batch_requests.data_ptr() == batch_requests_.data_ptr(),
+                "GaudiRT device metadata: revalidation needs the int32 request vector the metadata was built on");
+    c10::cuda::CUDAGuard guard(device);
+    const int wide = (locations.scalar_type() == at::kLong ? 1 : 0) | (positions.scalar_type() == at::kLong ? 4 : 0);
+    check_status(gk_paged_metadata_device_validate(
+                     locations.data_ptr(), batch_requests.data_ptr(), positions.data_ptr(), nullptr, wide, 0,
+                     table_checked_ ? mapping_.data_ptr<int32_t>() : nullptr, mapping_.size(0), context_,
+                     mapping_.stride(0), slots_, dev_seq_.data_ptr<int32_t>(), batch, rows_, dev_workspace_.data_ptr(),
+                     locations_.data_ptr<int32_t>(), requests_.data_ptr<int32_t>(), positions_.data_ptr<int32_t>(),
+                     nullptr, last_token_indices_.data_ptr<int32_t>(), dev_row_status_.data_ptr<int32_t>(), nullptr,
+                     reinterpret_cast<uint64_t*>(dev_verdict_.data_ptr<int64_t>()),
+                     device_status(device.index()).data_ptr<int32_t>(),
+                     stream_of(at::cuda::getCurrentCUDAStream(device.index()))),
+                 "device metadata");
   }
 
   int64_t rows() const { return rows_; }
@@ -395,6 +458,12 @@ class PagedMetadata : public torch::CustomClassHolder {
     plan->combine_offset = combine_offset;
     plan->n_prefill = n_prefill;
     plan->prefill_offset = prefill_offset;
+    {
+      const int64_t block_rows = std::max<int64_t>(1, GK_MAX_PACKED_ROWS / (query_heads / kv_heads));
+      bool single = n_prefill == 0 && n_work > 0 && rows_independent_;
+      for (int64_t i = 0; single && i < n_seq; ++i) single = sequences_[static_cast<size_t>(i) * 4 + 1] <= block_rows;
+      plan->single_block = single;
+    }
     auto tensor = wrap_plan(std::move(plan));
     plans_.emplace_back(sliding_window, tensor);
     return tensor;
@@ -427,7 +496,10 @@ class PagedMetadata : public torch::CustomClassHolder {
     fused_combine_ = static_cast<int>(mode);
   }
   int split_tokens_ = 0, prefill_min_rows_ = 0, fused_combine_ = -1;
+  bool rows_independent_ = false;   // no sequence of the step reads a row that another sequence writes
   at::Tensor locations_, requests_, positions_, mapping_, header_, batch_requests_, token_ids_, last_token_indices_;
+  at::Tensor dev_seq_, dev_workspace_, dev_verdict_, dev_row_status_;   // device-validated forms only (revalidate_)
+  bool table_checked_ = false;
   std::vector<int32_t> sequences_;   // {first_row, n_rows, first_position, table_row} per sequence
   std::vector<std::pair<int64_t, at::Tensor>> plans_;
 };

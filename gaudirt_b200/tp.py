@@ -13,11 +13,20 @@ for the plumbing:
   ``[rows, world*cols]`` buffer (plain peer stores into symmetric memory), followed by one small
   completion barrier with a bounded wait.  No collective kernel and no transpose run.
 
-Buffers are double-buffered: a buffer is written again only after one full barrier has passed, so a
-peer still reading layer L's activation never sees layer L+1's stores.  The barrier keeps its epoch
-in device memory, so a whole step (all layers) can be captured in one CUDA graph and replayed; a
-captured step must contain a multiple of `depth` exchanges so that every replay starts on the same
-buffer (`graph_safe`).
+The gathered activation lives in a ring of `depth` buffers (2 by default): the buffer of exchange L
+is written again by the peers at exchange L + depth, which they can start once the barrier of
+exchange L + depth - 1 has let them pass, and that barrier needs this rank's arrival.  So whatever
+reads exchange L's buffer on this rank (the next kernel of the stream, or a copy on a side stream)
+has to be ordered before this rank's barrier of exchange L + depth - 1; a consumer on the same
+stream is ordered automatically, a side-stream reader needs an event (`depth=3` gives it one whole
+exchange of slack).  The barrier keeps its epoch in device memory, so a whole step (all layers)
+can be captured in one CUDA graph and replayed; a captured step must contain a multiple of `depth`
+exchanges so that every replay starts on the same buffer (`graph_safe`).
+
+A bounded wait that runs out (a peer more than about a second late, or gone) does not raise by
+itself: it sets GK_DEV_WAIT_EXPIRED in the device status word and the step goes on with whatever
+arrived.  `check()` reads the word and raises; call it once per step, after the step's last
+exchange, before the results are used.
 """
 from __future__ import annotations
 
@@ -115,11 +124,16 @@ class OutputGather:
 
     def attention(self, query, key, value, key_pool, value_pool, metadata, head_dim, scale, softcap=0.0,
                   sliding_window=-1):
-        """Paged attention on this rank's heads followed by the gather; returns `[rows, world*cols]`."""
+        """Paged attention on this rank's heads followed by the gather; returns `[rows, world*cols]`.
+        With `key` and `value` None the step's rows are already in the pool (`_rotary_kv_store`)."""
         q_heads, kv_heads = query.size(1) // head_dim, key_pool.size(1)
         if self.mode == "nccl":
-            out = torch.ops.gaudirt.paged_attn(query, key, value, key_pool, value_pool, metadata, head_dim, scale,
-                                               softcap, sliding_window)
+            if key is None:
+                out = torch.ops.gaudirt._paged_attn_stored(query, key_pool, value_pool, metadata, head_dim, scale,
+                                                           softcap, sliding_window)
+            else:
+                out = torch.ops.gaudirt.paged_attn(query, key, value, key_pool, value_pool, metadata, head_dim, scale,
+                                                   softcap, sliding_window)
             return self.gather(out)
         plan = (metadata.attention_plan_for(q_heads, kv_heads, head_dim, sliding_window) if sliding_window > 0
                 else metadata.attention_plan(q_heads, kv_heads, head_dim))
@@ -140,6 +154,24 @@ class OutputGather:
         gathered = self._local[self._turn % self.depth]
         self._turn += 1
         return gathered
+
+    def check(self):
+        """Step-end check (synchronises): raises if a bounded wait ran out or a kernel met a bad slot or
+        table entry during the step, instead of handing on an incomplete activation."""
+        check_device_status(self.device)
+
+
+_STATUS_TEXT = {1: "a slot outside the KV pool", 2: "a table entry outside the KV pool",
+                4: "a bounded wait ran out (a peer is late or gone)", 8: "device-side metadata validation rejected a row"}
+
+
+def check_device_status(device) -> None:
+    """Reads and clears the status word of `device` and raises `RuntimeError` naming every bit set."""
+    with torch.cuda.device(device):
+        word = int(torch.ops.gaudirt._take_device_status())
+    if word:
+        what = "; ".join(text for bit, text in _STATUS_TEXT.items() if word & bit) or "unknown bits"
+        raise RuntimeError(f"GaudiRT: device status {word} after the step: {what}")
 
 
 class RowParallelOutput:
@@ -207,6 +239,10 @@ class RowParallelOutput:
     def graph_safe(self, exchanges_per_step: int) -> bool:
         """Whether a step of that many exchanges may be captured in a CUDA graph and replayed."""
         return self.mode == "nccl" or (exchanges_per_step % self.depth == 0 and self._turn % self.depth == 0)
+
+    def check(self):
+        """Step-end check (synchronises): raises if a bounded wait ran out during the step."""
+        check_device_status(self.device)
 
     def exchange(self, mine):
         """Baseline exchange of an already computed `[rows, hidden]` partial: all-gather, rank-major."""

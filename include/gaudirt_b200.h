@@ -208,6 +208,37 @@ GK_API int gk_paged_attn_combine_multi_bf16(const float* part_ml, const float* p
                                      const int32_t* combine, int64_t n_combine,
                                      void* const* outs, int n_outs, int64_t out_row_stride,
                                      int q_heads, int head_dim, gk_stream_t stream);
+/* gk_kv_store_head_major_bf16 fused into the attention launch, as the reference's single-block
+ * recipe does (src/bridge/paged_attention.cpp:74; `separate_store` at :251 decides): every CTA
+ * first copies the new K/V rows whose positions fall into its own KV range to their pool slots,
+ * then attends.  Valid only for a step whose sequences are ONE query block each (n_rows <=
+ * GK_MAX_PACKED_ROWS / group, e.g. any decode step) and whose work records come from
+ * gk_attention_plan_build for exactly those sequences, because then no other CTA reads the rows;
+ * the caller decides that (the operator layer does, and launches the store separately otherwise).
+ * new_k / new_v must be 16-byte aligned with row strides that are multiples of 8 elements
+ * (GK_ERR_UNSUPPORTED otherwise).  The pool ends up bit-identical to the separate store. */
+GK_API int gk_paged_attn_store_multi_bf16(const void* q, int64_t q_row_stride, const void* new_k,
+                                   const void* new_v, int64_t new_k_row_stride,
+                                   int64_t new_v_row_stride, const int32_t* locations,
+                                   void* pool_k, void* pool_v, int64_t slots, const int32_t* table,
+                                   int64_t table_stride, int64_t table_entry_stride,
+                                   int page_tokens, const int32_t* table_rows, const int32_t* work,
+                                   int64_t n_work, void* const* outs, int n_outs,
+                                   int64_t out_row_stride, float* part_ml, float* part_o,
+                                   int32_t* split_counters, float scale, float softcap, int window,
+                                   int q_heads, int kv_heads, int head_dim, int32_t* status,
+                                   gk_stream_t stream);
+/* The tensor-core prefill kernel with the same multi-destination epilogue, so that a prefill or a
+ * mixed prefill + decode step (one call in the reference, src/bridge/paged_attention.cpp:251-345)
+ * is gathered by the kernels' own stores as well; destinations must be 16-byte aligned. */
+GK_API int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_stride, const void* pool_k,
+                                   const void* pool_v, int64_t slots, const int32_t* table,
+                                   int64_t table_stride, int64_t table_entry_stride,
+                                   int page_tokens, const int32_t* table_rows, const int32_t* work,
+                                   int64_t n_work, void* const* outs, int n_outs,
+                                   int64_t out_row_stride, float scale, float softcap, int window,
+                                   int q_heads, int kv_heads, int head_dim, int32_t* status,
+                                   gk_stream_t stream);
 /* Completion barrier that follows the pushes (replaces the wait on the collective,
  * src/bridge/segmented_runner.cpp:489-506): flags[p] is rank p's int32[world] flag array as
  * mapped in this process.  Writes `epoch` to slot `rank` of every peer's array, then waits
@@ -404,11 +435,19 @@ GK_API int gk_sample_vocab(const void* logits, int is_f32, int64_t rows, int64_t
  *                     GK_STATIC_SCRATCH_MAX_ENTRIES (or head_dim above the maximum) is refused
  *                     with GK_ERR_CAPACITY before anything is launched.
  *   combine, n_combine  the schedule's combine records (may be empty).
- * The first call on each device looks up the device address of the array (a host-side query,
- * no allocation); make that first call before starting any stream capture.  All calls share the
- * one array: it keeps the previous call's contents (nothing in it needs clearing, every entry a
- * combine record reads is written by that call's attention kernel first), and two calls whose
- * kernels overlap on the GPU (different streams, or different threads) race on it. */
+ *                     A work or combine record that points past `partial_entries` is skipped on
+ *                     the device and GK_DEV_BAD_SLOT is raised in *status: a schedule that
+ *                     disagrees with the declared count cannot write outside the array.
+ * All arguments are checked before the first launch; split state without combine records (or the
+ * reverse), and combine records without work records, are GK_ERR_INVALID_ARGUMENT.
+ * The first call on each device looks up the device address of the array.  The entry point itself
+ * allocates nothing, but under CUDA's lazy module loading the first use of the library's device
+ * code on a device is also the moment the driver loads the module and gives the array its memory,
+ * so the very first call is not free of driver-side allocation: make it once per device at
+ * start-up (a schedule with n_work = 0 will do), and before starting any stream capture.  All
+ * calls share the one array: it keeps the previous call's contents (nothing in it needs clearing,
+ * every entry a combine record reads is written by that call's attention kernel first), and two
+ * calls whose kernels overlap on the GPU (different streams, or different threads) race on it. */
 #define GK_STATIC_SCRATCH_MAX_ENTRIES 8192
 #define GK_STATIC_SCRATCH_MAX_HEAD_DIM 256
 GK_API int gk_paged_attn_static_scratch_bf16(const void* q, int64_t q_row_stride, const void* pool_k,

@@ -112,3 +112,32 @@ def chunk_case(prefixes, chunk, q_heads, kv_heads, head_dim, block, seed, std=1.
     scale = torch.tensor(1.0 / math.sqrt(head_dim), dtype=torch.float32).item()
     return ChunkCase(q_heads, kv_heads, head_dim, n_blocks * block, mapping, requests, positions, locations, q, k, v,
                      pool, scale)
+
+
+def ragged_case(prefixes, lengths, q_heads, kv_heads, head_dim, block, seed, std=1.0) -> ChunkCase:
+    """A mixed step: sequence i appends `lengths[i]` new rows to a prefix of `prefixes[i]` tokens
+    already in the pool (length 1 = a decode row, more = a prefill / extend chunk)."""
+    gen = torch.Generator().manual_seed(seed)
+    prefixes = torch.as_tensor(prefixes, dtype=torch.int64)
+    lengths = torch.as_tensor(lengths, dtype=torch.int64)
+    n = len(prefixes)
+    need = (prefixes + lengths + block - 1) // block
+    n_blocks = int(int(need.sum()) * 1.1) + 1
+    perm = torch.randperm(n_blocks, generator=gen).to(torch.int32)
+    tables = torch.zeros(n, int(need.max()), dtype=torch.int32)
+    cursor = 0
+    for b in range(n):
+        tables[b, : int(need[b])] = perm[cursor:cursor + int(need[b])]
+        cursor += int(need[b])
+    pos = torch.arange(int(need.max()) * block)
+    mapping = (tables.long()[:, pos // block] * block + pos % block).to(torch.int32).contiguous()
+    requests = torch.repeat_interleave(torch.arange(n), lengths)
+    positions = torch.cat([torch.arange(int(p), int(p + l)) for p, l in zip(prefixes, lengths)])
+    locations = mapping[requests, positions].contiguous()
+    rows = int(lengths.sum())
+    mk = lambda *shape: (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+    q, k, v = mk(rows, q_heads * head_dim), mk(rows, kv_heads * head_dim), mk(rows, kv_heads * head_dim)
+    pool = mk(2, kv_heads, n_blocks * block, head_dim)
+    scale = torch.tensor(1.0 / math.sqrt(head_dim), dtype=torch.float32).item()
+    return ChunkCase(q_heads, kv_heads, head_dim, n_blocks * block, mapping, requests, positions, locations, q, k, v,
+                     pool, scale)

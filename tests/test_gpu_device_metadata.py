@@ -172,3 +172,42 @@ def test_attention_through_device_metadata_matches_host_metadata(rt):
     assert torch.equal(outs[0][0].view(torch.int16), outs[1][0].view(torch.int16))
     assert torch.equal(outs[0][1].view(torch.int16), outs[1][1].view(torch.int16))
     assert rt._C._take_device_status() == 0
+
+
+def test_revalidation_refreshes_the_same_device_tensors_and_can_be_replayed_from_a_graph(rt):
+    """`_revalidate_` checks new index vectors of a step of the same shape into the tensors the metadata (and a
+    plan, and a captured graph) already refer to: launches only, so it is capturable; a bad vector is reported
+    through the status word."""
+    locations, requests, positions, mapping, prefixes, lengths, row_requests = batch(33)
+    loc_d, req_d, pos_d = locations.to(DEV), requests.to(torch.int32).to(DEV), positions.to(DEV)
+    md = rt.PagedMetadata.from_device(loc_d, req_d, pos_d, mapping.to(DEV), prefixes, lengths, SLOTS)
+    held = md.row_locations()
+    address = held.data_ptr()
+    assert torch.equal(held.cpu().long(), locations)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        md._revalidate_(loc_d, req_d, pos_d)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            md._revalidate_(loc_d, req_d, pos_d)
+    held.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert md.row_locations().data_ptr() == address and torch.equal(held.cpu().long(), locations)
+    assert rt._C._take_device_status() == 0
+    # the step's vectors change in place: a slot that is not the table's is reported on the next replay
+    loc_d[5] += 1
+    graph.replay()
+    torch.cuda.synchronize()
+    assert rt._C._take_device_status() == 8
+    loc_d[5] -= 1
+    graph.replay()
+    torch.cuda.synchronize()
+    assert rt._C._take_device_status() == 0 and torch.equal(held.cpu().long(), locations)
+    with pytest.raises(RuntimeError, match="request vector"):
+        md._revalidate_(loc_d, req_d.clone(), pos_d)
+    host = rt.PagedMetadata(locations, row_requests, positions, mapping, SLOTS)
+    with pytest.raises(RuntimeError, match="device-validated"):
+        host._revalidate_(loc_d, req_d, pos_d)

@@ -284,3 +284,99 @@ def test_chunked_prefill_goes_to_the_tensor_core_kernel_and_matches_the_generic_
         outs.append(out.cpu().double())
     assert rt._C._take_device_status() == 0
     assert float((outs[0] - outs[1]).abs().max()) <= 2e-2
+
+
+def test_kv_store_inside_the_attention_launch_equals_the_separate_store(rt):
+    """Decode steps carry the store in the attention launch (single-block recipe of the reference,
+    src/bridge/paged_attention.cpp:74); pool and output must be the separate store's, bit for bit, with and
+    without split KV ranges; a batch in which one request appears twice falls back to the separate launch."""
+    ctx = [700, 33, 1500, 257, 64, 1023, 1, 16]
+    case = cases.decode_case(len(ctx), 32, 8, 128, 128, 48, ctx, seed=606)
+    ref_pool = case.pool.clone()
+    oracle.kv_store_head_major(ref_pool, case.k, case.v, case.locations)
+    try:
+        for split in (0, 128):
+            got = {}
+            for fused in (True, False):
+                torch.ops.gaudirt._set_fused_kv_store(fused)
+                md = rt.PagedMetadata(case.locations, case.requests, case.positions, case.mapping, case.slots)
+                if split:
+                    md._set_split_tokens(split)
+                pool = case.pool.to(DEV)
+                out = torch.ops.gaudirt.paged_attn(case.q.to(DEV), case.k.to(DEV), case.v.to(DEV), pool[0].transpose(0, 1),
+                                                   pool[1].transpose(0, 1), md, 128, case.scale)
+                assert torch.equal(bits(pool.cpu()), bits(ref_pool)), (split, fused)
+                got[fused] = out
+            assert torch.equal(bits(got[True]), bits(got[False])), split
+    finally:
+        torch.ops.gaudirt._set_fused_kv_store(True)
+    # two decode rows of ONE request (positions p, p + 1 as separate sequences cannot exist; a chunk of 2 rows
+    # followed by its continuation can): the later rows read the earlier rows' slots
+    n_req, context, slots = 2, 256, 2 * 256 + 1
+    mapping = torch.arange(1, slots, dtype=torch.int32).reshape(n_req, context)
+    requests = torch.tensor([0, 0, 1, 0, 0], dtype=torch.int64)
+    positions = torch.tensor([40, 41, 7, 42, 43], dtype=torch.int64)          # request 0: rows 0-1, then rows 3-4
+    locations = mapping[requests, positions].to(torch.int64)
+    md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
+    assert md.sequences() == [0, 2, 40, 0, 2, 1, 7, 1, 3, 2, 42, 0]
+    gen = torch.Generator().manual_seed(8)
+    q, k, v = (torch.randn(5, w, generator=gen).bfloat16() for w in (8 * 64, 2 * 64, 2 * 64))
+    kb, vb = (torch.randn(slots, 2, 64, generator=gen).bfloat16() for _ in range(2))
+    _, key_pool, value_pool = make_pools(rt, slots, 2, 64, kb, vb)
+    out = torch.ops.gaudirt.paged_attn(q.to(DEV), k.to(DEV), v.to(DEV), key_pool, value_pool, md, 64, 0.125)
+    ek, ev = kb.clone(), vb.clone()
+    ek[locations] = k.reshape(-1, 2, 64)
+    ev[locations] = v.reshape(-1, 2, 64)
+    assert torch.equal(bits(key_pool.cpu()), bits(ek)) and torch.equal(bits(value_pool.cpu()), bits(ev))
+    gates(out, (q, ek, ev, requests, positions, mapping, 8, 2, 64, 0.125))
+    assert rt._C._take_device_status() == 0
+
+
+def test_two_host_threads_call_the_operators_concurrently(rt):
+    """The boundary promises calls from several host threads (the reference keeps thread-local recipe caches for
+    that, src/bridge/paged_attention.cpp:139-151): two threads, each with its own stream, metadata, pool and head
+    geometry -- so both take the first-use set-up paths of different kernels at the same time -- must each get
+    the result a single-threaded call gives."""
+    import threading
+    specs = [(32, 8, 128, [300, 1500, 64, 900]), (8, 2, 64, [17, 700, 2000]), (4, 4, 256, [100, 130])]
+    built = []
+    for i, (hq, hkv, d, ctx) in enumerate(specs):
+        blocks = sum((c + 127) // 128 for c in ctx) + 2
+        built.append(cases.decode_case(len(ctx), hq, hkv, d, 128, blocks, ctx, seed=1200 + i))
+
+    def run(case, results, key, repeats):
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                outs = []
+                for _ in range(repeats):
+                    md = rt.PagedMetadata(case.locations, case.requests, case.positions, case.mapping, case.slots)
+                    md._set_split_tokens(256)
+                    pool = case.pool.to(DEV)
+                    outs.append(torch.ops.gaudirt.paged_attn(case.q.to(DEV), case.k.to(DEV), case.v.to(DEV),
+                                                             pool[0].transpose(0, 1), pool[1].transpose(0, 1), md,
+                                                             case.head_dim, case.scale))
+                stream.synchronize()
+            results[key] = outs
+        except Exception as exc:          # surfaced by the parent
+            results[key] = exc
+
+    results = {}
+    threads = [threading.Thread(target=run, args=(c, results, i, 6)) for i, c in enumerate(built)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    for i, case in enumerate(built):
+        assert isinstance(results.get(i), list), results.get(i)
+        alone = {}
+        run(case, alone, 0, 1)
+        for out in results[i]:
+            assert torch.equal(bits(out), bits(alone[0][0]))
+        ref_pool = case.pool.clone()
+        oracle.kv_store_head_major(ref_pool, case.k, case.v, case.locations)
+        kp, vp = oracle.pool_views(ref_pool)
+        oracle.fp32_softmax_gate(results[i][0].cpu().double(),
+                                 oracle.attend_fp32_softmax(case.q, kp, vp, case.requests, case.positions, case.mapping,
+                                                            case.q_heads, case.kv_heads, case.head_dim, case.scale))
+    assert rt._C._take_device_status() == 0
