@@ -340,7 +340,8 @@ extern "C" int gk_prefill_plan_build(const int32_t* seq, int64_t n_seq, int q_he
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS)
     return GK_ERR_UNSUPPORTED;
   const int group = q_heads / kv_heads;
-  const int tile_rows = GK_PREFILL_TILE_ROWS / group;
+  // one record feeds both query tiles of a CTA: up to 2 x (128 / group) consecutive rows
+  const int tile_rows = GK_PREFILL_TILES_PER_ITEM * (GK_PREFILL_TILE_ROWS / group);
   if (min_rows == 0) min_rows = std::max(2, (32 + group - 1) / group);
   struct Item { int32_t w[GK_WORK_WORDS]; };
   std::vector<Item> items;

@@ -2,11 +2,13 @@
 //
 // Both are HBM-bound elementwise/row kernels.  Every bf16 boundary of the reference (the updated
 // residual, the normalised output, each rotated element) is rounded ONCE from an exactly computed
-// value.  The norm's arithmetic between boundaries runs in fp64 with exact, integer-only
-// conversions from and to bf16; a rotation is evaluated in fp32 with directed roundings that
-// recover the exact result's rounding (round-to-odd), so no double rounding can occur.  That
-// reproduces the reference's binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35,
-// tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact.
+// value, which reproduces the reference's binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35,
+// tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact.  To stay on the
+// HBM roof every element first takes a short fp32 evaluation with a known error bound; only when
+// that result lies so close to a bf16 rounding boundary that the bound cannot decide the rounding
+// (a few elements in 10^4 for the norm, one in 65 536 for a sum or a rotation) is the element
+// evaluated again the exact way: directed fp32 roundings with a sticky bit for sums and rotations,
+// binary64 for the norm's scaling.
 #include "gk_common.cuh"
 
 #include <algorithm>
@@ -38,6 +40,10 @@ __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned
   const float sf = __uint_as_float((uint32_t)s << 16);
   if (subtract) yf = -yf;
   const float first = xf * cf;                                  // exact
+  // Round-to-nearest of the exact value (one rounding).  Rounding that again to bf16 can only go
+  // wrong when it sits exactly on a bf16 midpoint without being exact: that case takes the long way.
+  const float nearest = __fmaf_rn(yf, sf, first);
+  if ((__float_as_uint(nearest) & 0xffffu) != 0x8000u) return __bfloat16_as_ushort(__float2bfloat16_rn(nearest));
   const float down = __fmaf_rd(yf, sf, first), up = __fmaf_ru(yf, sf, first);
   float r = down < 0.f ? up : down;                             // toward zero
   if (down != up) r = __uint_as_float(__float_as_uint(r) | 1u);
@@ -49,11 +55,29 @@ __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned
 // nearer zero gets a sticky bit (round-to-odd) before the rounding to bf16.
 __device__ __forceinline__ unsigned short add_bf16_exact(unsigned short a, unsigned short b) {
   const float af = __uint_as_float((uint32_t)a << 16), bf = __uint_as_float((uint32_t)b << 16);
+  const float nearest = __fadd_rn(af, bf);                      // one rounding of the exact sum
+  if ((__float_as_uint(nearest) & 0xffffu) != 0x8000u) return __bfloat16_as_ushort(__float2bfloat16_rn(nearest));
   const float down = __fadd_rd(af, bf), up = __fadd_ru(af, bf);
   float r = up;                                                 // exact sum (x + -x gives +0 this way, as round-to-nearest does)
   if (down != up) r = __uint_as_float(__float_as_uint(down < 0.f ? up : down) | 1u);
   return __bfloat16_as_ushort(__float2bfloat16_rn(r));
 }
+// bf16(u * inv * (w + offset)): the norm's scaling step.  Fast evaluation in fp32: four roundings
+// (w + offset, inv to fp32, two products), so the result is within 4.1 ulp of the exact product as
+// long as nothing is subnormal; if it is more than 8 ulp away from every bf16 midpoint (bit pattern
+// ...8000 in the low half), the exact product rounds to the same bf16.  Otherwise, and for tiny or
+// non-finite values, the product is formed in binary64 and rounded once.
+__device__ __forceinline__ unsigned short scale_to_bf16(unsigned short u, unsigned short w, float inv32, double inv,
+                                                        float offset32, double offset) {
+  const float uf = __uint_as_float((uint32_t)u << 16), wf = __uint_as_float((uint32_t)w << 16);
+  const float a = uf * inv32, y = a * (wf + offset32);
+  const uint32_t bits = __float_as_uint(y);
+  const uint32_t away = ((bits & 0xffffu) - 0x8000u + 8u) & 0xffffu;      // < 17: within 8 ulp of a midpoint
+  const bool safe = away > 16u && fabsf(a) > 1e-30f && fabsf(y) > 1e-30f && fabsf(y) < 1e38f;
+  if (safe || uf == 0.f) return __bfloat16_as_ushort(__float2bfloat16_rn(y));
+  return bf16_from_double(bf16_to_double(u) * inv * (bf16_to_double(w) + offset));
+}
+
 // u * u as a double: the square of a bf16 value has 16 significant bits, exact in fp32.
 __device__ __forceinline__ double square_bf16(unsigned short u) {
   const float f = __uint_as_float((uint32_t)u << 16);
@@ -163,6 +187,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
     }
     const double total = block_sum(sumsq, partial);
     const double inv = rsqrt(total / (double)hidden + epsilon);
+    const float inv32 = (float)inv, offset32 = (float)weight_offset;
 #pragma unroll
     for (int it = 0; it < kItems; ++it) {
       const int col = (it * 256 + threadIdx.x) * 8;
@@ -171,8 +196,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
         const unsigned short* wv = reinterpret_cast<const unsigned short*>(&w);
         unsigned short out[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          out[e] = bf16_from_double(bf16_to_double(u[it][e]) * inv * (bf16_to_double(wv[e]) + weight_offset));
+        for (int e = 0; e < 8; ++e) out[e] = scale_to_bf16(u[it][e], wv[e], inv32, inv, offset32, weight_offset);
         *reinterpret_cast<uint4*>(yr + col) = *reinterpret_cast<const uint4*>(out);
       }
     }
@@ -210,6 +234,7 @@ struct RotaryParams {
   int32_t* status;
   int64_t rows, q_stride, k_stride, v_stride, cache_rows, slots;
   int q_heads, k_heads, head_dim, rotary_dim, is_neox;
+  int chunk_shift;      // log2(head_dim / 8) when that is a power of two, else -1
 };
 
 __device__ __forceinline__ unsigned short rotate_element(const unsigned short* head, const unsigned short* table,
@@ -286,12 +311,12 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
   const int chunks = p.head_dim >> 3;
   const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
   const int per_row = heads * chunks;
-  const int64_t total = p.rows * (int64_t)per_row;
   const int half = p.rotary_dim >> 1;
-  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = idx / per_row;
-    const int rem = (int)(idx - row * per_row);
-    const int head = rem / chunks, ch = rem - head * chunks;
+  // blockIdx.y walks the rows, blockIdx.x * 256 + threadIdx.x the 16-byte chunks of a row: no 64-bit
+  // division per element (it used to cost more than the rotation itself)
+  for (int64_t row = blockIdx.y; row < p.rows; row += gridDim.y)
+  for (int rem = blockIdx.x * blockDim.x + threadIdx.x; rem < per_row; rem += gridDim.x * blockDim.x) {
+    const int head = p.chunk_shift >= 0 ? rem >> p.chunk_shift : rem / chunks, ch = rem - head * chunks;
     const int kh = head - p.q_heads;
     if (STORE && kh >= p.k_heads) {                              // V: straight to its slot
       const int vh = kh - p.k_heads;
@@ -363,16 +388,20 @@ bool rotary_vectorisable(const RotaryParams& p, bool store) {
   return !(bits & 15) && !(strides & 7) && p.head_dim % 8 == 0 && p.rotary_dim % (p.is_neox ? 16 : 8) == 0;
 }
 
-int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
+int launch_rotary(const RotaryParams& params, bool store, cudaStream_t stream) {
+  RotaryParams p = params;
   if (rotary_vectorisable(p, store)) {
     const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
-    const int64_t total = p.rows * heads * (p.head_dim / 8);
-    const int64_t want = (total + 255) / 256;
-    const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    const int chunks = p.head_dim / 8, per_row = heads * chunks;
+    p.chunk_shift = (chunks & (chunks - 1)) == 0 ? __builtin_ctz((unsigned)chunks) : -1;
+    const int threads = per_row >= 256 ? 256 : (per_row + 31) / 32 * 32;
+    const unsigned across = (unsigned)((per_row + threads - 1) / threads);
+    const int64_t down = std::min<int64_t>(p.rows, std::max<int64_t>(1, 148 * 16 / across));
+    const dim3 grid(across, (unsigned)down);
     if (store)
-      rotary_vec_kernel<true><<<blocks, 256, 0, stream>>>(p);
+      rotary_vec_kernel<true><<<grid, threads, 0, stream>>>(p);
     else
-      rotary_vec_kernel<false><<<blocks, 256, 0, stream>>>(p);
+      rotary_vec_kernel<false><<<grid, threads, 0, stream>>>(p);
     return check_launch();
   }
   const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);

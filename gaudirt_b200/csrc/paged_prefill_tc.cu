@@ -1,32 +1,32 @@
 // Chunked-prefill paged attention on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
-// A work record here is a query tile of one sequence: up to 128/G consecutive rows whose G query
-// heads of one KV head are packed into the 128 rows of a UMMA tile, against the KV range
-// [kv_begin, kv_end) of the pool (prefix + the rows themselves, causal inside the chunk).
-// Q.K^T (128 x 128 x d) and P.V (128 x d x 128) are real dense contractions, so they run as
-// tcgen05.mma.kind::f16 with fp32 accumulators in tensor memory:
+// A work record is a run of up to 2 x (128/G) consecutive rows of one sequence.  The G query heads of
+// one KV head of those rows are packed into TWO query tiles of 128 rows each (tile t = rows
+// [t*128/G, (t+1)*128/G) of the record); both tiles attend to the KV range [kv_begin, kv_end) of the pool
+// (prefix + the rows themselves, causal inside the chunk), so every K/V tile is fetched once for 256
+// packed rows.  Q.K^T (128 x 128 x d) and P.V (128 x d x 128) run as tcgen05.mma.kind::f16 with fp32
+// accumulators in tensor memory:
 //
-//   warps 0-7  softmax, two warpgroups: thread (wg, row) owns columns [64 wg, 64 wg + 64) of
-//              packed row `row` (= TMEM lane).  It reads S with tcgen05.ld, the two halves of a
-//              row exchange their maxima through shared memory, O is rescaled in TMEM only when
-//              the running maximum moved by more than 2^8, P (bf16, the reference's rounding
-//              point) goes to shared memory, and at the end O is normalised and written out
-//   warps 8-11 loaders (8-9 for K, 10-11 for V) of a 128-token tile.  A tile made of whole,
-//              slot-contiguous pages of >= 8 tokens is fetched by TMA: one elected thread issues
-//              cp.async.bulk.tensor (2-D boxes of 64 columns x page rows, 128-byte swizzle, no
-//              multicast) per page and panel, completion by transaction bytes on the mbarrier.
-//              Any other tile (ragged tail, token-granular tables, window offsets) is gathered
-//              row by row with 16-byte cp.async, completion by cp.async.mbarrier.arrive.  The
-//              loaders never wait for their copies
-//   warp 12    one thread issues the MMAs: S[j&1] = Q K_j^T, then O += P_{j-1} V_{j-1}, signalling
-//              completion through tcgen05.commit -> mbarrier
+//   TMEM (512 columns)   S0 | S1 | O0 | O1, 128 columns each; P_t (bf16, 64 columns) overwrites the lower
+//                        half of S_t and is the A operand of P_t.V straight from tensor memory
+//   warps 0-3 / 4-7      softmax of query tile 0 / 1: thread = one packed row = one TMEM lane, all 128
+//                        columns, so the row maximum and the row sum need no exchange with anybody.
+//                        S comes in with tcgen05.ld, P (rounded to bf16, the reference's boundary) goes
+//                        back with tcgen05.st; O is rescaled in TMEM only when the running maximum moved
+//                        by more than 2^8; at the end the same thread normalises its O row and stores it
+//                        to every destination
+//   warps 8-11           loaders (8-9 K, 10-11 V) of 128-token tiles: whole, slot-contiguous pages by TMA
+//                        (cp.async.bulk.tensor 2-D boxes, 128-byte swizzle, no multicast), anything else
+//                        row by row with 16-byte cp.async; two K stages, three V stages
+//   warp 12              one thread issues the MMAs in the order  P0.V(j), Q0.K(j+1), P1.V(j), Q1.K(j+1):
+//                        while one tile's softmax runs, the tensor pipe works on the other tile
 //
-// Shared-memory operand tiles are [128 rows x 128 bf16] as two panels of [128 x 64] with the
-// 128-byte swizzle (16-byte chunk c of row r at chunk c ^ (r & 7)); the same bytes serve K as a
-// K-major operand and V as an MN-major operand.  S and P are double-buffered, K and V have two
-// stages each, so Q K_{j+1}^T and the loads run under softmax_j and P_j V_j under softmax_{j+1}.
-// Every mbarrier wait is bounded: on expiry the CTA raises GK_DEV_WAIT_EXPIRED, drains its
-// copies, frees its TMEM and returns.
+// The two softmax warpgroups are out of phase by construction, which is what keeps the tensor pipe
+// fed; a share of the exponentials is evaluated on the FMA pipe by a cubic polynomial (relative error
+// 8.6e-5, far below the bf16 rounding of P) because the special-function unit alone cannot produce
+// 2 x 128 x 128 exponentials in the time four 128^3 MMAs take.
+// Every mbarrier wait is bounded: on expiry the CTA raises GK_DEV_WAIT_EXPIRED, drains its copies,
+// frees its TMEM and returns.
 #include "tc_common.cuh"
 
 #include <string.h>
@@ -35,15 +35,20 @@
 namespace gk {
 namespace {
 
-constexpr int kTile = 128;             // packed query rows per CTA, KV tokens per tile, head_dim
+constexpr int kTile = 128;             // packed query rows per tile, KV tokens per tile, head_dim
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
-constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V; 4 warpgroups
+constexpr int kKStages = 2, kVStages = 3;
+constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V
 constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
-constexpr int kSoftmaxRegs = 176, kOtherRegs = 80;
-static_assert(kSoftmaxThreads * kSoftmaxRegs + (kThreads - kSoftmaxThreads) * kOtherRegs <= kThreads * kLaunchRegs,
+constexpr int kSoftmaxRegs = 176, kLoaderRegs = 96, kIssueRegs = 64;
+static_assert(kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueRegs <= kThreads * kLaunchRegs,
               "register budgets exceed the pool the launch allocates");
 constexpr float kLog2e = 1.4426950408889634f;
+// Of every 8 exponentials, this many go to the FMA pipe (polynomial) instead of the special-function unit.
+#ifndef GK_PREFILL_POLY_OF_8
+#define GK_PREFILL_POLY_OF_8 2
+#endif
 
 struct PrefillParams {
   const __nv_bfloat16* q;
@@ -57,15 +62,15 @@ struct PrefillParams {
   int64_t q_stride, out_stride, slots, table_stride, entry_stride;
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group;
-  int tma_rows;          // rows of a TMA box (= page_tokens), 0 = TMA path off
+  int tma_rows;          // rows of a TMA box, 0 = TMA path off
   int n_out;
 };
 
 struct Shared {
-  uint64_t k_full[2], v_full[2], s_full[2], p_full[2], pv_done[2], swap[3];   // swap: row-half exchanges
+  uint64_t k_full[kKStages], k_free[kKStages], v_full[kVStages], v_free[kVStages];
+  uint64_t s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort;
-  float exchange[2][2][kTile];     // [tile parity][warpgroup][row]: row maxima, finally row sums
 };
 
 __device__ __forceinline__ uint32_t tile_off(int r, int c) {
@@ -76,15 +81,46 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);   // A, B K-major
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P, bf16, two per 32-bit column) is read from tensor memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// 2^x for x <= 8 or so on the FMA pipe: x = n + f with n = floor(x), 2^f by a cubic that is exact at
+// f = 0 (max relative error 8.6e-5 on [0, 1)), n added into the exponent field.  Arguments below -126
+// give 0 like ex2.approx.ftz does for them.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -127.f);
+  const float shifted = __fadd_rd(x, 12582912.f);                 // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (shifted - 12582912.f);                     // [0, 1)
+  float p = fmaf(f, 0.0770658627152443f, 0.22764626145362854f);
+  p = fmaf(f, p, 0.6951165199279785f);
+  p = fmaf(f, p, 1.f);
+  const float r = __uint_as_float(__float_as_uint(p) + (__float_as_uint(shifted) << 23));
+  return x <= -127.f ? 0.f : r;                                   // masked keys (-inf) stay exactly 0
+}
+
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p,
                                                                        const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t tiles[];     // swizzle atoms need 1 KiB alignment
-  uint8_t* s_q = tiles;
-  uint8_t* s_p = tiles + kTileBytes;                     // two P buffers
-  uint8_t* s_k = tiles + 3 * kTileBytes;                 // two K stages
-  uint8_t* s_v = tiles + 5 * kTileBytes;                 // two V stages
-  Shared* sh = reinterpret_cast<Shared*>(tiles + 7 * kTileBytes);
+  uint8_t* s_q = tiles;                                  // two query tiles
+  uint8_t* s_k = tiles + 2 * kTileBytes;                 // K stages
+  uint8_t* s_v = tiles + (2 + kKStages) * kTileBytes;    // V stages
+  Shared* sh = reinterpret_cast<Shared*>(tiles + (2 + kKStages + kVStages) * kTileBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(tiles) & 1023) {                          // cannot build valid descriptors: report, leave
@@ -97,18 +133,28 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   const int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, table_row = w0.w;
   const int kv_begin = w1.x, kv_end = w1.y;
   const int G = p.group;
-  const int mv = n_rows * G;                            // packed rows in use (<= 128)
-  const int n_tiles = (kv_end - kv_begin + kTile - 1) / kTile;
+  const int tile_rows = kTile / G;                          // rows of the record per query tile
+  const int rows0 = min(n_rows, tile_rows), rows1 = n_rows - rows0;
+  // KV tiles each query tile needs: tile 0 stops at its own last row (causal), tile 1 at the record's end
+  const int nt1_all = (kv_end - kv_begin + kTile - 1) / kTile;
+  const int nt0 = min(nt1_all, (first_pos + rows0 - kv_begin + kTile - 1) / kTile);
+  const int nt1 = rows1 > 0 ? nt1_all : 0;
+  const int n_tiles = max(nt0, nt1);
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kKStages; ++i) {
       bar_init(&sh->k_full[i], kLoaderThreads);
+      bar_init(&sh->k_free[i], 1);
+    }
+    for (int i = 0; i < kVStages; ++i) {
       bar_init(&sh->v_full[i], kLoaderThreads);
+      bar_init(&sh->v_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       bar_init(&sh->s_full[i], 1);
-      bar_init(&sh->p_full[i], kSoftmaxThreads);
+      bar_init(&sh->p_full[i], kTile);
       bar_init(&sh->pv_done[i], 1);
     }
-    for (int i = 0; i < 3; ++i) bar_init(&sh->swap[i], kSoftmaxThreads);
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -116,12 +162,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  // Q tile: packed row pr = (row pr / G, query head pr % G) of this KV head; unused rows are zero.
-  for (int i = tid; i < kTile * 16; i += kThreads) {
-    const int pr = i >> 4, c = i & 15;
+  // Q tiles: packed row pr of tile t = (row t*tile_rows + pr / G, query head pr % G) of this KV head; unused rows are zero.
+  for (int i = tid; i < 2 * kTile * 16; i += kThreads) {
+    const int t = i >> 11, pr = (i >> 4) & 127, c = i & 15;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (pr < mv) {
-      const int r = pr / G, g = pr - r * G;
+    const int r = t * tile_rows + pr / G, g = pr % G;
+    if (pr < tile_rows * G && r < n_rows) {
       const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * kTile + c * 8;
       if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
         v = __ldg(reinterpret_cast<const uint4*>(src));
@@ -133,87 +179,92 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         v = *reinterpret_cast<const uint4*>(e);
       }
     }
-    *reinterpret_cast<uint4*>(s_q + tile_off(pr, c)) = v;
+    *reinterpret_cast<uint4*>(s_q + t * kTileBytes + tile_off(pr, c)) = v;
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  const uint32_t tmem_o = tmem + 256;
 
-  // Registers move from the loader/MMA warpgroups (which need few) to the softmax warpgroups.
+  // Registers move from the loader / issue warpgroups (which need few) to the softmax warpgroups.
   // setmaxnreg.inc blocks until the CTA's register pool can satisfy it, and the pool is what the
-  // launch allocated (kThreads x kLaunchRegs): the two budgets must fit in it or the softmax warps
+  // launch allocated (kThreads x kLaunchRegs): the budgets must fit in it or the softmax warps
   // would never start (checked at compile time and again on the host before every launch).
   if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kSoftmaxRegs));
+  } else if (warp < 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kLoaderRegs));
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kOtherRegs));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kIssueRegs));
   }
+
   if (warp < 8) {
-    // ================================ softmax ============================================
-    const int wg = warp >> 2;                                    // which 64 columns of the row
+    // ================================ softmax of query tile t ===============================
+    const int t = warp >> 2;
     const int pr = tid & 127;                                    // packed row == TMEM lane
-    const int lim = pr < mv ? first_pos + pr / G : 0x7fffffff;   // last visible key of this row
+    const int my_rows = t == 0 ? rows0 : rows1;
+    const int mv = my_rows * G;                                  // packed rows of this tile in use
+    const int my_tiles = t == 0 ? nt0 : nt1;
+    const int tile_first_pos = first_pos + t * tile_rows;
+    const int lim = pr < mv ? tile_first_pos + pr / G : 0x7fffffff;   // last visible key of this row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem + t * kTile + lane_base;        // S_t; P_t overwrites its lower 64 columns
+    const uint32_t p_addr = s_addr;
+    const uint32_t o_addr = tmem + 256 + t * kTile + lane_base;
     const bool capped = p.softcap > 0.f;
     const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
     float m = -CUDART_INF_F, l = 0.f;                            // m: exponent reference of this row
     bool alive = true;
-    for (int j = 0; j < n_tiles && alive; ++j) {
-      const int st = j & 1;
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[st], (j >> 1) & 1, &sh->abort));
+    for (int j = 0; j < my_tiles && alive; ++j) {
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[t], j & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
-      const uint32_t s_addr = tmem + st * kTile + wg * 64 + lane_base;
-      const int tok0 = kv_begin + j * kTile + wg * 64;
-      float sc[64];
+      const int tok0 = kv_begin + j * kTile;
+      const int tile_end = tok0 + kTile;
+      const bool ragged = tile_end > kv_end || tile_end > tile_first_pos + 1 ||
+                          (p.window > 0 && tok0 <= tile_first_pos + my_rows - 1 - p.window);
+      const bool plain = !(capped || ragged);
+      // A score in log2 units: the common case is one multiply; softcap and masked tiles take the long way.
+      auto adjusted = [&](float raw, int e) {
+        float v = raw;
+        if (capped) v = p.softcap * tanhf(v * cap_in);
+        v *= to_log2;
+        const int tok = tok0 + e;
+        const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
+        return seen ? v : -CUDART_INF_F;
+      };
+      // ---- pass 1: row maximum over all 128 columns (the registers are free again afterwards) ----
+      float mx;
       {
-        uint32_t r0[32], r1[32];
+        uint32_t r0[32], r1[32], r2[32], r3[32];
         tmem_ld32_nowait(s_addr, r0);
         tmem_ld32_nowait(s_addr + 32, r1);
+        tmem_ld32_nowait(s_addr + 64, r2);
+        tmem_ld32_nowait(s_addr + 96, r3);
         tmem_ld_wait();
+        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        if (plain) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          sc[e] = __uint_as_float(r0[e]);
-          sc[32 + e] = __uint_as_float(r1[e]);
+          for (int e = 0; e < 32; e += 2) {
+            mx4[0] = fmaxf(mx4[0], fmaxf(__uint_as_float(r0[e]), __uint_as_float(r0[e + 1])));
+            mx4[1] = fmaxf(mx4[1], fmaxf(__uint_as_float(r1[e]), __uint_as_float(r1[e + 1])));
+            mx4[2] = fmaxf(mx4[2], fmaxf(__uint_as_float(r2[e]), __uint_as_float(r2[e + 1])));
+            mx4[3] = fmaxf(mx4[3], fmaxf(__uint_as_float(r3[e]), __uint_as_float(r3[e + 1])));
+          }
+          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * to_log2;       // to_log2 > 0
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            mx4[0] = fmaxf(mx4[0], adjusted(__uint_as_float(r0[e]), e));
+            mx4[1] = fmaxf(mx4[1], adjusted(__uint_as_float(r1[e]), 32 + e));
+            mx4[2] = fmaxf(mx4[2], adjusted(__uint_as_float(r2[e]), 64 + e));
+            mx4[3] = fmaxf(mx4[3], adjusted(__uint_as_float(r3[e]), 96 + e));
+          }
+          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         }
       }
-      const int tile_end = kv_begin + (j + 1) * kTile;
-      const bool ragged = tile_end > kv_end || tile_end > first_pos + 1 ||
-                          (p.window > 0 && kv_begin + j * kTile <= first_pos + n_rows - 1 - p.window);
-      // After this block sc[] holds raw scores and `mult` the factor that takes them to log2
-      // units; the uncommon cases (softcap, tiles that need masking) rewrite sc[] in place.
-      float mult = to_log2;
-      if (capped || ragged) {
-#pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          float v = sc[e];
-          if (capped) v = p.softcap * tanhf(v * cap_in);
-          v *= to_log2;
-          const int tok = tok0 + e;
-          const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
-          sc[e] = seen ? v : -CUDART_INF_F;
-        }
-        mult = 1.f;
-      }
-      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-      for (int e = 0; e < 64; e += 4) {
-        mx4[0] = fmaxf(mx4[0], sc[e]);
-        mx4[1] = fmaxf(mx4[1], sc[e + 1]);
-        mx4[2] = fmaxf(mx4[2], sc[e + 2]);
-        mx4[3] = fmaxf(mx4[3], sc[e + 3]);
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;     // mult > 0
-      // the two halves of a row meet through an mbarrier (a bounded wait, unlike bar.sync)
-      sh->exchange[st][wg][pr] = mx;
-      bar_arrive(&sh->swap[st]);
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[st], (j >> 1) & 1, &sh->abort));
-      if (!alive) break;
-      mx = fmaxf(mx, sh->exchange[st][wg ^ 1][pr]);
       // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
       // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
       float alpha = 1.f;
@@ -225,69 +276,77 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       }
       const float mu = m == -CUDART_INF_F ? 0.f : m;
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st ^ 1], ((j - 1) >> 1) & 1, &sh->abort));
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[t], (j - 1) & 1, &sh->abort));
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int cb = 0; cb < 2; ++cb) {
+        for (int cb = 0; cb < 4; ++cb) {
           uint32_t r[32];
-          tmem_ld32(tmem_o + lane_base + wg * 64 + cb * 32, r);
+          tmem_ld32(o_addr + cb * 32, r);
 #pragma unroll
           for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tmem_st32(tmem_o + lane_base + wg * 64 + cb * 32, r);
+          tmem_st32(o_addr + cb * 32, r);
         }
-        tc_fence_before();
       }
-      if (j >= 2) {                                                // P[st] was last read by P.V of tile j-2
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[st], ((j - 2) >> 1) & 1, &sh->abort));
-        if (!alive) break;
-      }
-      // probabilities, rounded to bf16 for the second product; l from the fp32 values
+      // ---- pass 2: probabilities, 32 columns at a time, the next chunk requested before this one is
+      // worked on.  P (bf16, the reference's rounding point before the second product) overwrites the
+      // LOWER half of S: chunk c writes columns [16c, 16c+16), all of which were read by then.
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* p_tile = s_p + st * kTileBytes;
       const float neg_mu = -mu;
+      uint32_t cur[32], nxt[32];
+      tmem_ld32_nowait(s_addr, cur);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t packed[4];
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c < 3) tmem_ld32_nowait(s_addr + (c + 1) * 32, nxt);
+        uint32_t packed[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = fast_exp2(fmaf(sc[c * 8 + 2 * e], mult, neg_mu));
-          const float b = fast_exp2(fmaf(sc[c * 8 + 2 * e + 1], mult, neg_mu));
-          sum4[e] += a + b;
-          packed[e] = pack_bf16(a, b);
+        for (int i = 0; i < 16; ++i) {
+          float xa, xb;
+          if (plain) {
+            xa = fmaf(__uint_as_float(cur[2 * i]), to_log2, neg_mu);
+            xb = fmaf(__uint_as_float(cur[2 * i + 1]), to_log2, neg_mu);
+          } else {
+            xa = adjusted(__uint_as_float(cur[2 * i]), c * 32 + 2 * i) + neg_mu;
+            xb = adjusted(__uint_as_float(cur[2 * i + 1]), c * 32 + 2 * i + 1) + neg_mu;
+          }
+          // of every 8 consecutive exponentials, the first GK_PREFILL_POLY_OF_8 run on the FMA pipe
+          const float a = ((2 * i) & 7) < GK_PREFILL_POLY_OF_8 ? exp2_poly(xa) : fast_exp2(xa);
+          const float b = ((2 * i + 1) & 7) < GK_PREFILL_POLY_OF_8 ? exp2_poly(xb) : fast_exp2(xb);
+          sum4[i & 3] += a + b;
+          packed[i] = pack_bf16(a, b);
         }
-        *reinterpret_cast<uint4*>(p_tile + tile_off(pr, wg * 8 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        tmem_st16_nowait(p_addr + c * 16, packed);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) cur[e] = nxt[e];
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      fence_async_smem();
+      tmem_st_wait();
       tc_fence_before();
-      bar_arrive(&sh->p_full[st]);
+      bar_arrive(&sh->p_full[t]);
     }
     // epilogue: O / l -> bf16 rows of the output
-    const int last = n_tiles - 1;
-    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[last & 1], (last >> 1) & 1, &sh->abort));
-    sh->exchange[n_tiles & 1][wg][pr] = l;
-    bar_arrive(&sh->swap[2]);
-    if (alive) alive = __all_sync(0xffffffffu, bar_wait(&sh->swap[2], 0, &sh->abort));
-    l += sh->exchange[n_tiles & 1][wg ^ 1][pr];
-    if (alive) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int r_q = pr / G, g = pr - r_q * G;
-      const int64_t at = (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile + wg * 64;
+    if (alive && my_tiles > 0) {
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[t], (my_tiles - 1) & 1, &sh->abort));
+      if (alive) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int r_q = t * tile_rows + pr / G, g = pr % G;
+        const int64_t at = (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile;
 #pragma unroll 1
-      for (int cb = 0; cb < 2; ++cb) {
-        uint32_t r[32];
-        tmem_ld32(tmem_o + lane_base + wg * 64 + cb * 32, r);
-        if (pr < mv) {
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + cb * 32, r);
+          if (pr < mv) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[c * 8 + 0]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
-            for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint4*>(p.out[dst] + at + cb * 32 + c * 8) = v;
+            for (int c = 0; c < 4; ++c) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[c * 8 + 0]) * inv, __uint_as_float(r[c * 8 + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(r[c * 8 + 2]) * inv, __uint_as_float(r[c * 8 + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(r[c * 8 + 4]) * inv, __uint_as_float(r[c * 8 + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(r[c * 8 + 6]) * inv, __uint_as_float(r[c * 8 + 7]) * inv);
+              for (int dst = 0; dst < p.n_out; ++dst) *reinterpret_cast<uint4*>(p.out[dst] + at + cb * 32 + c * 8) = v;
+            }
           }
         }
       }
@@ -296,13 +355,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     // ================================ K/V loaders =========================================
     const bool is_v = warp >= 10;
     const int lwarp = (warp - 8) & 1;
-    const __nv_bfloat16* kbase = p.pool_k + (int64_t)head * p.slots * kTile;
-    const __nv_bfloat16* vbase = p.pool_v + (int64_t)head * p.slots * kTile;
+    const int stages = is_v ? kVStages : kKStages;
+    const __nv_bfloat16* base = (is_v ? p.pool_v : p.pool_k) + (int64_t)head * p.slots * kTile;
     const int32_t* trow = p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
     const int page_mask = (1 << p.page_shift) - 1;
-    bool alive = true;
+    const CUtensorMap* map = is_v ? &map_v : &map_k;
+    const int head_row = head * (int)p.slots;
+    int st = 0, round = 0;                                   // ring position of tile j: stage j % stages, round j / stages
     for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
       // each loader warp stages 64 rows, 32 at a time: lanes resolve one slot each, then the
       // warp copies two 256-byte rows per instruction (16 lanes x 16 bytes each)
       int slot[2];
@@ -318,33 +378,18 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           }
         }
       }
-      auto stage_rows = [&](const __nv_bfloat16* base, uint32_t dst) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int rr = 2 * i + (lane >> 4), c = lane & 15;
-            const int s = __shfl_sync(0xffffffffu, slot[half], rr);
-            cp_async_16(dst + tile_off(lwarp * 64 + half * 32 + rr, c), base + (int64_t)(s < 0 ? 0 : s) * kTile + c * 8,
-                        s < 0 ? 0 : 16);
-          }
-        }
-      };
       // This warp's 64 rows go by TMA when they are whole, in-range boxes of tma_rows slot-contiguous
       // tokens; the two warps of a tile decide independently (every thread arrives once either way).
       const int tok_first = kv_begin + j * kTile + lwarp * 64;
       bool by_tma = p.tma_rows > 0 && (tok_first & (p.tma_rows - 1)) == 0 && tok_first + 64 <= kv_end;
       by_tma = __all_sync(0xffffffffu, by_tma && slot[0] >= 0 && slot[1] >= 0);
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
-      if (j >= 2) {   // stage free: K once Q.K^T of tile j-2 completed, V once P.V of tile j-2 completed
-        uint64_t* freed = is_v ? &sh->pv_done[st] : &sh->s_full[st];
-        alive = __all_sync(0xffffffffu, bar_wait_patient(freed, ((j - 2) >> 1) & 1, &sh->abort));
-        if (!alive) break;
+      if (round > 0) {   // stage free: K once both Q.K^T of the tile that used it completed, V once both P.V did
+        uint64_t* freed = is_v ? &sh->v_free[st] : &sh->k_free[st];
+        if (!__all_sync(0xffffffffu, bar_wait_patient(freed, (round - 1) & 1, &sh->abort))) break;
       }
       const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
       if (by_tma) {
-        const CUtensorMap* map = is_v ? &map_v : &map_k;
-        const int head_row = head * (int)p.slots;
         if (lane == 0) bar_arrive_expect_tx(full, 64 * 256);
         else bar_arrive(full);
         __syncwarp();
@@ -359,48 +404,85 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           }
         }
       } else {
-        stage_rows(is_v ? vbase : kbase, dst);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rr = 2 * i + (lane >> 4), c = lane & 15;
+            const int s = __shfl_sync(0xffffffffu, slot[half], rr);
+            cp_async_16(dst + tile_off(lwarp * 64 + half * 32 + rr, c), base + (int64_t)(s < 0 ? 0 : s) * kTile + c * 8,
+                        s < 0 ? 0 : 16);
+          }
+        }
         bar_arrive_on_copies(full);
+      }
+      if (++st == stages) {
+        st = 0;
+        ++round;
       }
     }
     asm volatile("cp.async.wait_all;\n" ::: "memory");
   } else if (warp == 12 && lane == 0) {
     // ================================ MMA issue ===========================================
-    const uint32_t q_addr = smem_u32(s_q), p_addr = smem_u32(s_p), k_base = smem_u32(s_k), v_base = smem_u32(s_v);
+    const uint32_t q_addr = smem_u32(s_q), k_base = smem_u32(s_k), v_base = smem_u32(s_v);
+    const int nt[2] = {nt0, nt1};
     bool alive = true;
-    auto issue_pv = [&](int i) {
-      const int st = i & 1;
-      if (!bar_wait(&sh->p_full[st], (i >> 1) & 1, &sh->abort)) return false;
-      if (!bar_wait(&sh->v_full[st], (i >> 1) & 1, &sh->abort)) return false;
-      fence_async_smem();
-      tc_fence_after();
-      const uint32_t v_addr = v_base + st * kTileBytes, pa = p_addr + st * kTileBytes;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step
-        const uint64_t da = umma_desc(pa + (k >> 2) * kPanelBytes + (k & 3) * 32, 16, 1024);
-        const uint64_t db = umma_desc(v_addr + k * 2048, kPanelBytes, 1024);
-        umma_bf16(tmem_o, da, db, kIdescPV, (i > 0 || k > 0) ? 1u : 0u);
-      }
-      umma_commit(&sh->pv_done[st]);
-      return true;
-    };
-    for (int j = 0; j < n_tiles && alive; ++j) {
-      const int st = j & 1;
-      alive = bar_wait(&sh->k_full[st], (j >> 1) & 1, &sh->abort);
-      if (!alive) break;
-      fence_async_smem();
-      tc_fence_after();
-      const uint32_t k_addr = k_base + st * kTileBytes;
+    auto issue_qk = [&](int t, int j, uint32_t k_addr) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {                    // 16 elements of head_dim per step
         const uint32_t koff = (k >> 2) * kPanelBytes + (k & 3) * 32;
-        umma_bf16(tmem + st * kTile, umma_desc(q_addr + koff, 16, 1024), umma_desc(k_addr + koff, 16, 1024), kIdescQK,
-                  k > 0 ? 1u : 0u);
+        umma_bf16(tmem + t * kTile, umma_desc(q_addr + t * kTileBytes + koff, 16, 1024), umma_desc(k_addr + koff, 16, 1024),
+                  kIdescQK, k > 0 ? 1u : 0u);
       }
-      umma_commit(&sh->s_full[st]);
-      if (j > 0) alive = issue_pv(j - 1);
+      umma_commit(&sh->s_full[t]);
+    };
+    auto issue_pv = [&](int t, int j, uint32_t v_addr) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step: 8 columns of P, 16 rows of V
+        umma_bf16_ts(tmem + 256 + t * kTile, tmem + t * kTile + k * 8, umma_desc(v_addr + k * 2048, kPanelBytes, 1024),
+                     kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&sh->pv_done[t]);
+    };
+    if (n_tiles > 0) {
+      alive = bar_wait(&sh->k_full[0], 0, &sh->abort);
+      if (alive) {
+        fence_async_smem();
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (nt[t] > 0) issue_qk(t, 0, k_base);
+        umma_commit(&sh->k_free[0]);
+      }
     }
-    if (alive) issue_pv(n_tiles - 1);
+    int ks = 1 % kKStages, kround = 1 / kKStages, vs = 0, vround = 0;     // ring positions of K tile j+1 and V tile j
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const bool more = j + 1 < n_tiles;
+      alive = bar_wait(&sh->v_full[vs], vround & 1, &sh->abort);
+      if (alive && more) alive = bar_wait(&sh->k_full[ks], kround & 1, &sh->abort);
+      if (!alive) break;
+      fence_async_smem();
+      tc_fence_after();
+      for (int t = 0; t < 2 && alive; ++t) {
+        if (j < nt[t]) {
+          alive = bar_wait(&sh->p_full[t], j & 1, &sh->abort);
+          if (!alive) break;
+          tc_fence_after();
+          issue_pv(t, j, v_base + vs * kTileBytes);
+        }
+        if (j + 1 < nt[t]) issue_qk(t, j + 1, k_base + ks * kTileBytes);
+      }
+      if (!alive) break;
+      umma_commit(&sh->v_free[vs]);
+      if (more) umma_commit(&sh->k_free[ks]);
+      if (++vs == kVStages) {
+        vs = 0;
+        ++vround;
+      }
+      if (++ks == kKStages) {
+        ks = 0;
+        ++kround;
+      }
+    }
   }
 
   tc_fence_before();
@@ -422,7 +504,7 @@ bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_row
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr int kSmemBytes = 7 * kTileBytes + 3072;   // 227 KiB: the whole opt-in shared memory of an SM
+constexpr int kSmemBytes = (2 + kKStages + kVStages) * kTileBytes + 3072;   // 227 KiB: the whole opt-in shared memory of an SM
 
 }  // namespace
 }  // namespace gk
@@ -445,7 +527,8 @@ extern "C" int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_strid
   if (head_dim != 128 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS ||
       n_work * kv_heads > 0x7fffffffLL)
     return GK_ERR_UNSUPPORTED;
-  if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(work)) & 15) || (out_row_stride & 7) || (reinterpret_cast<uintptr_t>(q) & 1))
+  if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(work)) & 15) ||
+      (out_row_stride & 7) || (reinterpret_cast<uintptr_t>(q) & 1))
     return GK_ERR_INVALID_ARGUMENT;
   gk::PrefillParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -482,8 +565,7 @@ extern "C" int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_strid
       regs = attr.numRegs;
       launch_regs.store(regs, std::memory_order_release);
     }
-    if (regs * gk::kThreads <
-        gk::kSoftmaxThreads * gk::kSoftmaxRegs + (gk::kThreads - gk::kSoftmaxThreads) * gk::kOtherRegs)
+    if (regs * gk::kThreads < gk::kSoftmaxThreads * gk::kSoftmaxRegs + 128 * gk::kLoaderRegs + 128 * gk::kIssueRegs)
       return GK_ERR_UNSUPPORTED;
   }
   // TMA boxes need slot-contiguous pages of at least 8 tokens and 32-bit row coordinates.

@@ -161,16 +161,21 @@ GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o,
 /* ---- chunked prefill on the tensor cores -----------------------------------------------------
  * The multi-row half of the same reference recipes (src/bridge/paged_attention_tiles.cpp:57-195:
  * prefill / extend blocks of up to 256-512 rows against 512-key tiles on the MME): query tiles of
- * GK_PREFILL_TILE_ROWS packed rows (rows x query heads of one KV head) against 128-key tiles,
- * Q K^T and P V as tcgen05 UMMA contractions with fp32 accumulators in tensor memory, online
- * softmax between them, causal inside the chunk.  Same arithmetic contract as gk_paged_attn_bf16
- * (P rounded to bf16 before P V, fp32 accumulation, out = bf16(O / l)).  head_dim must be 128.
+ * GK_PREFILL_TILE_ROWS packed rows (rows x query heads of one KV head), GK_PREFILL_TILES_PER_ITEM
+ * of them per work record, against 128-key tiles that are fetched once for all tiles of the
+ * record; Q K^T and P V as tcgen05 UMMA contractions with fp32 accumulators in tensor memory (P is
+ * the A operand straight from tensor memory), online softmax between them, causal inside the
+ * chunk.  Same arithmetic contract as gk_paged_attn_bf16 (P rounded to bf16 before P V, fp32
+ * accumulation, out = bf16(O / l)); part of the exponentials is a cubic polynomial on the FMA pipe
+ * whose relative error (8.6e-5) is far below the bf16 rounding of P.  head_dim must be 128.
  *
  * gk_prefill_plan_build splits a step's sequences: those with at least min_rows rows
  * (0 = default, ceil(32 / (q_heads/kv_heads)) but at least 2) become tensor-core work records
- * {first_row, n_rows <= GK_PREFILL_TILE_ROWS / group, first_position, table_row, kv_begin,
- * kv_end, -1, 1}, longest KV range first; the others are copied to rest_seq_out ([n_seq*4]) for
- * gk_attention_plan_build.  Pass work_out == NULL to obtain the counts only. */
+ * {first_row, n_rows <= GK_PREFILL_TILES_PER_ITEM * (GK_PREFILL_TILE_ROWS / group), first_position,
+ * table_row, kv_begin, kv_end, -1, 1}, longest KV range first; the others are copied to
+ * rest_seq_out ([n_seq*4]) for gk_attention_plan_build.  Pass work_out == NULL to obtain the
+ * counts only. */
+#define GK_PREFILL_TILES_PER_ITEM 2
 #define GK_PREFILL_TILE_ROWS 128
 GK_API int gk_prefill_plan_build(const int32_t* seq, int64_t n_seq, int q_heads, int kv_heads,
                           int window, int min_rows, int32_t* work_out, int64_t work_cap,

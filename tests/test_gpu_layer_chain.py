@@ -37,7 +37,7 @@ def test_fused_decode_layer_step_chain_matches_the_oracle_chain(rt):
     x = torch.randn(batch, hidden, generator=gen).bfloat16()
     residual = torch.randn(batch, hidden, generator=gen).bfloat16()
     gamma = (0.02 * torch.randn(hidden, generator=gen)).bfloat16()                 # applied as 1 + gamma
-    cache = oracle.rotary_cache(int(ctx.max()) + 1, d, theta)
+    cache = oracle.rotary_cache(case.mapping.size(1), d, theta)          # one row per position of the request table
 
     # ---- oracle chain ------------------------------------------------------------------------
     want_y, want_u = oracle.fused_add_rms_norm(x, residual, gamma, 1e-5, 1.0, dtype=torch.float64)

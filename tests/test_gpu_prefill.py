@@ -71,7 +71,16 @@ def run_case(seqs, q_heads, kv_heads, page, seed, softcap=0.0, window=-1, min_ro
 
 def test_single_short_chunk_without_prefix():
     n_tc, n_rest = run_case([(0, 40)], 8, 2, 128, seed=1)
-    assert n_tc == 2 and n_rest == 0            # 32 rows x 4 heads per tile
+    assert n_tc == 1 and n_rest == 0            # one record: a full tile of 32 rows x 4 heads and a tile of 8 rows
+
+
+def test_records_of_one_and_two_query_tiles():
+    """One record feeds two query tiles of 128 packed rows: exactly two full tiles, one tile only, a second
+    tile of a single row, and a chunk whose tiles need different numbers of KV tiles (the causal limit of the
+    first tile ends one KV tile earlier)."""
+    for seqs, records in (([(300, 64)], 1), ([(5, 32)], 1), ([(0, 33)], 1), ([(96, 64)], 1), ([(1000, 65), (0, 129)], 5)):
+        n_tc, n_rest = run_case(seqs, 8, 2, 128, seed=sum(p + l for p, l in seqs))
+        assert n_tc == records and n_rest == 0
 
 
 @pytest.mark.parametrize("q_heads,kv_heads", [(8, 2), (4, 4), (16, 2), (9, 3)])
