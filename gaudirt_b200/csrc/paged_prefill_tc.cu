@@ -41,13 +41,13 @@ constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] 
 constexpr int kKStages = 2, kVStages = 3;
 constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V
 constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
-constexpr int kSoftmaxRegs = 176, kLoaderRegs = 96, kIssueRegs = 64;
+constexpr int kSoftmaxRegs = 184, kLoaderRegs = 80, kIssueRegs = 64;
 static_assert(kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueRegs <= kThreads * kLaunchRegs,
               "register budgets exceed the pool the launch allocates");
 constexpr float kLog2e = 1.4426950408889634f;
-// Of every 8 exponentials, this many go to the FMA pipe (polynomial) instead of the special-function unit.
-#ifndef GK_PREFILL_POLY_OF_8
-#define GK_PREFILL_POLY_OF_8 2
+// Of every 4 pairs of exponentials, this many go to the FMA pipe (polynomial) instead of the special-function unit.
+#ifndef GK_PREFILL_POLY_PAIRS_OF_4
+#define GK_PREFILL_POLY_PAIRS_OF_4 1
 #endif
 
 struct PrefillParams {
@@ -99,18 +99,27 @@ __device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t 
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// 2^x for x <= 8 or so on the FMA pipe: x = n + f with n = floor(x), 2^f by a cubic that is exact at
-// f = 0 (max relative error 8.6e-5 on [0, 1)), n added into the exponent field.  Arguments below -126
-// give 0 like ex2.approx.ftz does for them.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -127.f);
-  const float shifted = __fadd_rd(x, 12582912.f);                 // 1.5 * 2^23: the integer part lands in the low mantissa bits
-  const float f = x - (shifted - 12582912.f);                     // [0, 1)
-  float p = fmaf(f, 0.0770658627152443f, 0.22764626145362854f);
-  p = fmaf(f, p, 0.6951165199279785f);
-  p = fmaf(f, p, 1.f);
-  const float r = __uint_as_float(__float_as_uint(p) + (__float_as_uint(shifted) << 23));
-  return x <= -127.f ? 0.f : r;                                   // masked keys (-inf) stay exactly 0
+// 2^x for a pair of arguments on the FMA pipe (packed fp32x2 arithmetic): x = n + f with n = floor(x),
+// 2^f by a cubic that is exact at f = 0 (max relative error 8.6e-5 on [0, 1)), n added into the
+// exponent field.  Arguments are clamped at -127, where f = 0, the cubic is exactly 1 and the
+// exponent arithmetic yields exactly +0: masked keys (-inf) contribute nothing.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -127.f);
+  x.y = fmaxf(x.y, -127.f);
+  const float2 shifted = __fadd2_rd(x, make_float2(12582912.f, 12582912.f));   // 1.5 * 2^23: integer part in the low mantissa bits
+  const float2 whole = __fadd2_rn(shifted, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(whole, make_float2(-1.f, -1.f), x);              // [0, 1), exact
+  float2 p = __ffma2_rn(f, make_float2(0.0770658627152443f, 0.0770658627152443f),
+                        make_float2(0.22764626145362854f, 0.22764626145362854f));
+  p = __ffma2_rn(f, p, make_float2(0.6951165199279785f, 0.6951165199279785f));
+  p = __ffma2_rn(f, p, make_float2(1.f, 1.f));
+  return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(shifted.x) << 23)),
+                     __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(shifted.y) << 23)));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p,
@@ -225,16 +234,29 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       const int tile_end = tok0 + kTile;
       const bool ragged = tile_end > kv_end || tile_end > tile_first_pos + 1 ||
                           (p.window > 0 && tok0 <= tile_first_pos + my_rows - 1 - p.window);
-      const bool plain = !(capped || ragged);
-      // A score in log2 units: the common case is one multiply; softcap and masked tiles take the long way.
-      auto adjusted = [&](float raw, int e) {
-        float v = raw;
-        if (capped) v = p.softcap * tanhf(v * cap_in);
-        v *= to_log2;
-        const int tok = tok0 + e;
-        const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
-        return seen ? v : -CUDART_INF_F;
-      };
+      // Softcap and tiles that need masking are uncommon: they first rewrite S in tensor memory (scores in
+      // log2 units, masked keys at -inf), 32 columns at a time in a loop that is NOT unrolled, so that
+      // the two passes below stay one short piece of code (the instruction cache is what this kernel
+      // runs out of first when every variant is unrolled 128 times).
+      float mult = to_log2;
+      if (capped || ragged) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + c * 32, r);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float v = __uint_as_float(r[e]);
+            if (capped) v = p.softcap * tanhf(v * cap_in);
+            v *= to_log2;
+            const int tok = tok0 + c * 32 + e;
+            const bool seen = tok < kv_end && tok <= lim && (p.window <= 0 || tok > lim - p.window);
+            r[e] = __float_as_uint(seen ? v : -CUDART_INF_F);
+          }
+          tmem_st32(s_addr + c * 32, r);
+        }
+        mult = 1.f;
+      }
       // ---- pass 1: row maximum over all 128 columns (the registers are free again afterwards) ----
       float mx;
       {
@@ -245,25 +267,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         tmem_ld32_nowait(s_addr + 96, r3);
         tmem_ld_wait();
         float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-        if (plain) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            mx4[0] = fmaxf(mx4[0], fmaxf(__uint_as_float(r0[e]), __uint_as_float(r0[e + 1])));
-            mx4[1] = fmaxf(mx4[1], fmaxf(__uint_as_float(r1[e]), __uint_as_float(r1[e + 1])));
-            mx4[2] = fmaxf(mx4[2], fmaxf(__uint_as_float(r2[e]), __uint_as_float(r2[e + 1])));
-            mx4[3] = fmaxf(mx4[3], fmaxf(__uint_as_float(r3[e]), __uint_as_float(r3[e + 1])));
-          }
-          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * to_log2;       // to_log2 > 0
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            mx4[0] = fmaxf(mx4[0], adjusted(__uint_as_float(r0[e]), e));
-            mx4[1] = fmaxf(mx4[1], adjusted(__uint_as_float(r1[e]), 32 + e));
-            mx4[2] = fmaxf(mx4[2], adjusted(__uint_as_float(r2[e]), 64 + e));
-            mx4[3] = fmaxf(mx4[3], adjusted(__uint_as_float(r3[e]), 96 + e));
-          }
-          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        for (int e = 0; e < 32; e += 2) {
+          mx4[0] = max3(mx4[0], __uint_as_float(r0[e]), __uint_as_float(r0[e + 1]));
+          mx4[1] = max3(mx4[1], __uint_as_float(r1[e]), __uint_as_float(r1[e + 1]));
+          mx4[2] = max3(mx4[2], __uint_as_float(r2[e]), __uint_as_float(r2[e + 1]));
+          mx4[3] = max3(mx4[3], __uint_as_float(r3[e]), __uint_as_float(r3[e + 1]));
         }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;            // mult > 0
       }
       // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
       // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
@@ -291,8 +302,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       // ---- pass 2: probabilities, 32 columns at a time, the next chunk requested before this one is
       // worked on.  P (bf16, the reference's rounding point before the second product) overwrites the
       // LOWER half of S: chunk c writes columns [16c, 16c+16), all of which were read by then.
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_mu = -mu;
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 mult2 = make_float2(mult, mult), neg_mu2 = make_float2(-mu, -mu);
       uint32_t cur[32], nxt[32];
       tmem_ld32_nowait(s_addr, cur);
 #pragma unroll
@@ -302,25 +313,17 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float xa, xb;
-          if (plain) {
-            xa = fmaf(__uint_as_float(cur[2 * i]), to_log2, neg_mu);
-            xb = fmaf(__uint_as_float(cur[2 * i + 1]), to_log2, neg_mu);
-          } else {
-            xa = adjusted(__uint_as_float(cur[2 * i]), c * 32 + 2 * i) + neg_mu;
-            xb = adjusted(__uint_as_float(cur[2 * i + 1]), c * 32 + 2 * i + 1) + neg_mu;
-          }
-          // of every 8 consecutive exponentials, the first GK_PREFILL_POLY_OF_8 run on the FMA pipe
-          const float a = ((2 * i) & 7) < GK_PREFILL_POLY_OF_8 ? exp2_poly(xa) : fast_exp2(xa);
-          const float b = ((2 * i + 1) & 7) < GK_PREFILL_POLY_OF_8 ? exp2_poly(xb) : fast_exp2(xb);
-          sum4[i & 3] += a + b;
-          packed[i] = pack_bf16(a, b);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])), mult2, neg_mu2);
+          // of every 4 consecutive pairs, the first GK_PREFILL_POLY_PAIRS_OF_4 run on the FMA pipe
+          const float2 pr2 = (i & 3) < GK_PREFILL_POLY_PAIRS_OF_4 ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr2);
+          packed[i] = pack_bf16(pr2.x, pr2.y);
         }
         tmem_st16_nowait(p_addr + c * 16, packed);
 #pragma unroll
         for (int e = 0; e < 32; ++e) cur[e] = nxt[e];
       }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
       tmem_st_wait();
       tc_fence_before();
       bar_arrive(&sh->p_full[t]);
