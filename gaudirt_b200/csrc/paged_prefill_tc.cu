@@ -38,7 +38,10 @@ namespace {
 constexpr int kTile = 128;             // packed query rows per tile, KV tokens per tile, head_dim
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
-constexpr int kKStages = 2, kVStages = 3;
+#ifndef GK_PREFILL_K_STAGES
+#define GK_PREFILL_K_STAGES 2
+#endif
+constexpr int kKStages = GK_PREFILL_K_STAGES, kVStages = 5 - GK_PREFILL_K_STAGES;
 constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V
 constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
 constexpr int kSoftmaxRegs = 184, kLoaderRegs = 80, kIssueRegs = 64;
@@ -46,8 +49,33 @@ static_assert(kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueR
               "register budgets exceed the pool the launch allocates");
 constexpr float kLog2e = 1.4426950408889634f;
 // Of every 4 pairs of exponentials, this many go to the FMA pipe (polynomial) instead of the special-function unit.
+// 1: a softmax thread reads its 128 scores from tensor memory once and keeps them in registers; 0: it reads them
+// twice (maximum, then 32 at a time), which needs far fewer registers but exposes five load latencies per tile.
+#ifndef GK_PREFILL_ONE_PASS
+#define GK_PREFILL_ONE_PASS 1
+#endif
+// 1: the softmax threads signal after the first 64 probabilities are in tensor memory, so the first half of
+// P.V is issued while the second half of the row is still being exponentiated.
+// Which waits poll without suspending (bit 0: the softmax threads' wait for S, bit 1: the issuing thread's waits for P).
+#ifndef GK_PREFILL_HOT_WAITS
+#define GK_PREFILL_HOT_WAITS 0
+#endif
+#ifndef GK_PREFILL_EARLY_PV
+#define GK_PREFILL_EARLY_PV 0
+#endif
+// Bit c set: the whole 32-column chunk c of a row takes the polynomial (in addition to the per-pair share below).
+#ifndef GK_PREFILL_POLY_CHUNKS
+#define GK_PREFILL_POLY_CHUNKS 0
+#endif
+// How the loader warps wait for a free stage: 0 = try_wait with a 1 us suspend hint, 1 = plain try_wait, 2 = test_wait.
+#ifndef GK_PREFILL_LOADER_WAIT
+#define GK_PREFILL_LOADER_WAIT 0
+#endif
+#ifndef GK_DBG_SKIP
+#define GK_DBG_SKIP 0
+#endif
 #ifndef GK_PREFILL_POLY_PAIRS_OF_4
-#define GK_PREFILL_POLY_PAIRS_OF_4 1
+#define GK_PREFILL_POLY_PAIRS_OF_4 0
 #endif
 
 struct PrefillParams {
@@ -68,7 +96,7 @@ struct PrefillParams {
 
 struct Shared {
   uint64_t k_full[kKStages], k_free[kKStages], v_full[kVStages], v_free[kVStages];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_half[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -81,13 +109,24 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);   // A, B K-major
 constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
 
-// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P, bf16, two per 32-bit column) is read from tensor memory.
-__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t accumulate) {
+// The MMAs take each 64-bit shared-memory descriptor as its two halves: the upper half (strides, swizzle mode)
+// is the same for every tile of one operand kind, the lower half is the address field plus the
+// leading-dimension stride, so stepping through a tile or a ring is a 32-bit add.  The second form reads its
+// A operand (P, bf16, two per 32-bit column) from tensor memory.
+__device__ __forceinline__ void umma_bf16_ss_split(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                   uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts_split(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 db;\nsetp.ne.b32 p, %5, 0;\nmov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -113,8 +152,8 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
                         make_float2(0.22764626145362854f, 0.22764626145362854f));
   p = __ffma2_rn(f, p, make_float2(0.6951165199279785f, 0.6951165199279785f));
   p = __ffma2_rn(f, p, make_float2(1.f, 1.f));
-  return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(shifted.x) << 23)),
-                     __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(shifted.y) << 23)));
+  return make_float2(__uint_as_float(__float_as_uint(shifted.x) * 0x800000u + __float_as_uint(p.x)),
+                     __uint_as_float(__float_as_uint(shifted.y) * 0x800000u + __float_as_uint(p.y)));
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -161,7 +200,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     }
     for (int i = 0; i < 2; ++i) {
       bar_init(&sh->s_full[i], 1);
-      bar_init(&sh->p_full[i], kTile);
+      bar_init(&sh->p_half[i], 4);      // one arrival per softmax warp of the tile
+      bar_init(&sh->p_full[i], 4);
       bar_init(&sh->pv_done[i], 1);
     }
     sh->abort = 0;
@@ -171,29 +211,35 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  // Q tiles: packed row pr of tile t = (row t*tile_rows + pr / G, query head pr % G) of this KV head; unused rows are zero.
-  for (int i = tid; i < 2 * kTile * 16; i += kThreads) {
-    const int t = i >> 11, pr = (i >> 4) & 127, c = i & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    const int r = t * tile_rows + pr / G, g = pr % G;
-    if (pr < tile_rows * G && r < n_rows) {
-      const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * kTile + c * 8;
-      if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        v = __ldg(reinterpret_cast<const uint4*>(src));
-      } else {
-        const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
-        unsigned short e[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) e[k] = __ldg(s16 + k);
-        v = *reinterpret_cast<const uint4*>(e);
-      }
-    }
-    *reinterpret_cast<uint4*>(s_q + t * kTileBytes + tile_off(pr, c)) = v;
-  }
-  fence_async_smem();
   tc_fence_before();
-  __syncthreads();
+  __syncthreads();                                       // barriers and the TMEM allocation are in place
   tc_fence_after();
+  const bool is_loader = warp >= 8 && warp < 12;
+  if (!is_loader) {
+    // Q tiles: packed row pr of tile t = (row t*tile_rows + pr / G, query head pr % G) of this KV head; unused rows
+    // are zero.  The loader warps do not take part: their first K/V tiles are already on the way meanwhile.
+    const int filler = warp < 8 ? tid : tid - 128;       // 0..383
+    for (int i = filler; i < 2 * kTile * 16; i += kThreads - 128) {
+      const int t = i >> 11, pr = (i >> 4) & 127, c = i & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      const int r = t * tile_rows + pr / G, g = pr % G;
+      if (pr < tile_rows * G && r < n_rows) {
+        const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * kTile + c * 8;
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+          v = __ldg(reinterpret_cast<const uint4*>(src));
+        } else {
+          const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
+          unsigned short e[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) e[k] = __ldg(s16 + k);
+          v = *reinterpret_cast<const uint4*>(e);
+        }
+      }
+      *reinterpret_cast<uint4*>(s_q + t * kTileBytes + tile_off(pr, c)) = v;
+    }
+    fence_async_smem();
+    asm volatile("bar.sync 1, %0;\n" ::"n"(kThreads - 128) : "memory");      // the 384 threads that filled Q
+  }
   const uint32_t tmem = sh->tmem_base;
 
   // Registers move from the loader / issue warpgroups (which need few) to the softmax warpgroups.
@@ -214,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const int pr = tid & 127;                                    // packed row == TMEM lane
     const int my_rows = t == 0 ? rows0 : rows1;
     const int mv = my_rows * G;                                  // packed rows of this tile in use
-    const int my_tiles = t == 0 ? nt0 : nt1;
+    const int my_tiles = (GK_DBG_SKIP & 16) ? 0 : t == 0 ? nt0 : nt1;
     const int tile_first_pos = first_pos + t * tile_rows;
     const int lim = pr < mv ? tile_first_pos + pr / G : 0x7fffffff;   // last visible key of this row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -227,7 +273,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     float m = -CUDART_INF_F, l = 0.f;                            // m: exponent reference of this row
     bool alive = true;
     for (int j = 0; j < my_tiles && alive; ++j) {
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[t], j & 1, &sh->abort));
+      alive = __all_sync(0xffffffffu, (GK_PREFILL_HOT_WAITS & 1) ? bar_wait_hot(&sh->s_full[t], j & 1, &sh->abort)
+                                                                 : bar_wait(&sh->s_full[t], j & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
       const int tok0 = kv_begin + j * kTile;
@@ -257,6 +304,86 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         }
         mult = 1.f;
       }
+#if GK_PREFILL_ONE_PASS
+      // ---- the whole row comes in once (128 registers) and stays until it has become P ----
+      uint32_t sr[4][32];
+      if (!(GK_DBG_SKIP & 8)) {
+      tmem_ld32_nowait(s_addr, sr[0]);
+      tmem_ld32_nowait(s_addr + 32, sr[1]);
+      tmem_ld32_nowait(s_addr + 64, sr[2]);
+      tmem_ld32_nowait(s_addr + 96, sr[3]);
+      tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) sr[c][e] = __float_as_uint((float)(lane + e + c + j));
+      }
+      float mx;
+      if (GK_DBG_SKIP & 2) mx = 1.f; else
+      {
+        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          mx4[0] = max3(mx4[0], __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
+          mx4[1] = max3(mx4[1], __uint_as_float(sr[1][e]), __uint_as_float(sr[1][e + 1]));
+          mx4[2] = max3(mx4[2], __uint_as_float(sr[2][e]), __uint_as_float(sr[2][e + 1]));
+          mx4[3] = max3(mx4[3], __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
+        }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;            // mult > 0
+      }
+      // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
+      // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
+      float alpha = 1.f;
+      if (mx > m + 8.f || m == -CUDART_INF_F) {
+        if (mx > m) {
+          alpha = fast_exp2(m - mx);                               // 0 on the first finite maximum
+          m = mx;
+        }
+      }
+      const float mu = m == -CUDART_INF_F ? 0.f : m;
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[t], (j - 1) & 1, &sh->abort));
+        if (!alive) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t r[32];
+          tmem_ld32(o_addr + cb * 32, r);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+          tmem_st32(o_addr + cb * 32, r);
+        }
+      }
+      // ---- probabilities, 32 columns at a time.  P (bf16, the reference's rounding point before the
+      // second product) overwrites the LOWER half of S; every column of S is in registers by now.
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 mult2 = make_float2(mult, mult), neg_mu2 = make_float2(-mu, -mu);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), mult2, neg_mu2);
+          // of every 4 consecutive pairs, the first GK_PREFILL_POLY_PAIRS_OF_4 run on the FMA pipe
+          const bool poly = ((GK_PREFILL_POLY_CHUNKS >> c) & 1) || (i & 3) < GK_PREFILL_POLY_PAIRS_OF_4;
+          const float2 pr2 = (GK_DBG_SKIP & 1) ? x : poly ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr2);
+          packed[i] = pack_bf16(pr2.x, pr2.y);
+        }
+        if (!(GK_DBG_SKIP & 4)) tmem_st16_nowait(p_addr + c * 16, packed);
+        else if (packed[3] == 0x12345u && packed[7] == 77u && packed[11] == 5u && packed[15] == 9u) l += 1.f;
+#if GK_PREFILL_EARLY_PV
+        if (c == 1) {
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) bar_arrive(&sh->p_half[t]);
+        }
+#endif
+      }
+      l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+#else
       // ---- pass 1: row maximum over all 128 columns (the registers are free again afterwards) ----
       float mx;
       {
@@ -324,9 +451,11 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         for (int e = 0; e < 32; ++e) cur[e] = nxt[e];
       }
       l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+#endif
       tmem_st_wait();
       tc_fence_before();
-      bar_arrive(&sh->p_full[t]);
+      __syncwarp();                                      // every lane's P is in tensor memory: one arrival per warp
+      if (lane == 0) bar_arrive(&sh->p_full[t]);
     }
     // epilogue: O / l -> bf16 rows of the output
     if (alive && my_tiles > 0) {
@@ -389,7 +518,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
       if (round > 0) {   // stage free: K once both Q.K^T of the tile that used it completed, V once both P.V did
         uint64_t* freed = is_v ? &sh->v_free[st] : &sh->k_free[st];
-        if (!__all_sync(0xffffffffu, bar_wait_patient(freed, (round - 1) & 1, &sh->abort))) break;
+        const bool got = GK_PREFILL_LOADER_WAIT == 0 ? bar_wait_patient(freed, (round - 1) & 1, &sh->abort)
+                         : GK_PREFILL_LOADER_WAIT == 1 ? bar_wait(freed, (round - 1) & 1, &sh->abort)
+                                                       : bar_wait_hot(freed, (round - 1) & 1, &sh->abort);
+        if (!__all_sync(0xffffffffu, got)) break;
       }
       const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
       if (by_tma) {
@@ -430,22 +562,34 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const uint32_t q_addr = smem_u32(s_q), k_base = smem_u32(s_k), v_base = smem_u32(s_v);
     const int nt[2] = {nt0, nt1};
     bool alive = true;
-    auto issue_qk = [&](int t, int j, uint32_t k_addr) {
+    // Operand descriptors are built once; a k-step or a ring stage only moves the 14-bit address field (units of
+    // 16 bytes) in the lower half, so the issue loop is one 32-bit add per operand and the MMA itself.
+    const uint64_t q_desc = umma_desc(q_addr, 16, 1024), k_desc = umma_desc(k_base, 16, 1024);
+    const uint64_t v_desc = umma_desc(v_base, kPanelBytes, 1024);
+    const uint32_t q_lo = (uint32_t)q_desc, k_lo = (uint32_t)k_desc, v_lo = (uint32_t)v_desc;
+    const uint32_t qk_hi = (uint32_t)(q_desc >> 32), v_hi = (uint32_t)(v_desc >> 32);      // K's upper half equals Q's
+    constexpr uint32_t kStageStep = kTileBytes >> 4;
+    auto issue_qk = [&](int t, int stage) {
+      const uint32_t a = q_lo + t * kStageStep, b = k_lo + stage * kStageStep;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {                    // 16 elements of head_dim per step
-        const uint32_t koff = (k >> 2) * kPanelBytes + (k & 3) * 32;
-        umma_bf16(tmem + t * kTile, umma_desc(q_addr + t * kTileBytes + koff, 16, 1024), umma_desc(k_addr + koff, 16, 1024),
-                  kIdescQK, k > 0 ? 1u : 0u);
+        const uint32_t step = ((k >> 2) * kPanelBytes + (k & 3) * 32) >> 4;
+        umma_bf16_ss_split(tmem + t * kTile, a + step, qk_hi, b + step, qk_hi, kIdescQK, k > 0 ? 1u : 0u);
       }
       umma_commit(&sh->s_full[t]);
     };
-    auto issue_pv = [&](int t, int j, uint32_t v_addr) {
+    auto wait_p = [&](uint64_t* bar, uint32_t parity) {
+      if (GK_DBG_SKIP & 16) return true;
+      return (GK_PREFILL_HOT_WAITS & 2) ? bar_wait_hot(bar, parity, &sh->abort) : bar_wait(bar, parity, &sh->abort);
+    };
+    auto issue_pv = [&](int t, int j, int stage, int k_from, int k_to) {
+      const uint32_t b = v_lo + stage * kStageStep;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step: 8 columns of P, 16 rows of V
-        umma_bf16_ts(tmem + 256 + t * kTile, tmem + t * kTile + k * 8, umma_desc(v_addr + k * 2048, kPanelBytes, 1024),
-                     kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+      for (int k = k_from; k < k_to; ++k) {            // 16 tokens per step: 8 columns of P, 16 rows of V
+        umma_bf16_ts_split(tmem + 256 + t * kTile, tmem + t * kTile + k * 8, b + k * (2048 >> 4), v_hi, kIdescPV,
+                           (j > 0 || k > 0) ? 1u : 0u);
       }
-      umma_commit(&sh->pv_done[t]);
+      if (k_to == 8) umma_commit(&sh->pv_done[t]);
     };
     if (n_tiles > 0) {
       alive = bar_wait(&sh->k_full[0], 0, &sh->abort);
@@ -453,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         fence_async_smem();
         tc_fence_after();
         for (int t = 0; t < 2; ++t)
-          if (nt[t] > 0) issue_qk(t, 0, k_base);
+          if (nt[t] > 0) issue_qk(t, 0);
         umma_commit(&sh->k_free[0]);
       }
     }
@@ -467,12 +611,23 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       tc_fence_after();
       for (int t = 0; t < 2 && alive; ++t) {
         if (j < nt[t]) {
-          alive = bar_wait(&sh->p_full[t], j & 1, &sh->abort);
+#if GK_PREFILL_EARLY_PV && GK_PREFILL_ONE_PASS
+          alive = wait_p(&sh->p_half[t], j & 1);
           if (!alive) break;
           tc_fence_after();
-          issue_pv(t, j, v_base + vs * kTileBytes);
+          issue_pv(t, j, vs, 0, 4);
+          alive = wait_p(&sh->p_full[t], j & 1);
+          if (!alive) break;
+          tc_fence_after();
+          issue_pv(t, j, vs, 4, 8);
+#else
+          alive = wait_p(&sh->p_full[t], j & 1);
+          if (!alive) break;
+          tc_fence_after();
+          issue_pv(t, j, vs, 0, 8);
+#endif
         }
-        if (j + 1 < nt[t]) issue_qk(t, j + 1, k_base + ks * kTileBytes);
+        if (j + 1 < nt[t]) issue_qk(t, ks);
       }
       if (!alive) break;
       umma_commit(&sh->v_free[vs]);
