@@ -21,10 +21,10 @@
 //   warp 12              one thread issues the MMAs in the order  P0.V(j), Q0.K(j+1), P1.V(j), Q1.K(j+1):
 //                        while one tile's softmax runs, the tensor pipe works on the other tile
 //
-// The two softmax warpgroups are out of phase by construction, which is what keeps the tensor pipe
-// fed; a share of the exponentials is evaluated on the FMA pipe by a cubic polynomial (relative error
-// 8.6e-5, far below the bf16 rounding of P) because the special-function unit alone cannot produce
-// 2 x 128 x 128 exponentials in the time four 128^3 MMAs take.
+// While one tile's softmax runs, the tensor pipe has the other tile's two products to do.  The softmax
+// arithmetic is packed (fma.f32x2 / add.f32x2, three-input maxima) and the uncommon cases (softcap, tiles
+// that need masking) rewrite S in tensor memory in a short loop first, so the common path stays small:
+// the instruction cache is the first thing this kernel ran out of when every case was unrolled in place.
 // Every mbarrier wait is bounded: on expiry the CTA raises GK_DEV_WAIT_EXPIRED, drains its copies,
 // frees its TMEM and returns.
 #include "tc_common.cuh"
@@ -38,45 +38,13 @@ namespace {
 constexpr int kTile = 128;             // packed query rows per tile, KV tokens per tile, head_dim
 constexpr int kPanelBytes = kTile * 128;
 constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
-#ifndef GK_PREFILL_K_STAGES
-#define GK_PREFILL_K_STAGES 2
-#endif
-constexpr int kKStages = GK_PREFILL_K_STAGES, kVStages = 5 - GK_PREFILL_K_STAGES;
+constexpr int kKStages = 2, kVStages = 3;
 constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V
 constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
 constexpr int kSoftmaxRegs = 184, kLoaderRegs = 80, kIssueRegs = 64;
 static_assert(kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueRegs <= kThreads * kLaunchRegs,
               "register budgets exceed the pool the launch allocates");
 constexpr float kLog2e = 1.4426950408889634f;
-// Of every 4 pairs of exponentials, this many go to the FMA pipe (polynomial) instead of the special-function unit.
-// 1: a softmax thread reads its 128 scores from tensor memory once and keeps them in registers; 0: it reads them
-// twice (maximum, then 32 at a time), which needs far fewer registers but exposes five load latencies per tile.
-#ifndef GK_PREFILL_ONE_PASS
-#define GK_PREFILL_ONE_PASS 1
-#endif
-// 1: the softmax threads signal after the first 64 probabilities are in tensor memory, so the first half of
-// P.V is issued while the second half of the row is still being exponentiated.
-// Which waits poll without suspending (bit 0: the softmax threads' wait for S, bit 1: the issuing thread's waits for P).
-#ifndef GK_PREFILL_HOT_WAITS
-#define GK_PREFILL_HOT_WAITS 0
-#endif
-#ifndef GK_PREFILL_EARLY_PV
-#define GK_PREFILL_EARLY_PV 0
-#endif
-// Bit c set: the whole 32-column chunk c of a row takes the polynomial (in addition to the per-pair share below).
-#ifndef GK_PREFILL_POLY_CHUNKS
-#define GK_PREFILL_POLY_CHUNKS 0
-#endif
-// How the loader warps wait for a free stage: 0 = try_wait with a 1 us suspend hint, 1 = plain try_wait, 2 = test_wait.
-#ifndef GK_PREFILL_LOADER_WAIT
-#define GK_PREFILL_LOADER_WAIT 0
-#endif
-#ifndef GK_DBG_SKIP
-#define GK_DBG_SKIP 0
-#endif
-#ifndef GK_PREFILL_POLY_PAIRS_OF_4
-#define GK_PREFILL_POLY_PAIRS_OF_4 0
-#endif
 
 struct PrefillParams {
   const __nv_bfloat16* q;
@@ -96,7 +64,7 @@ struct PrefillParams {
 
 struct Shared {
   uint64_t k_full[kKStages], k_free[kKStages], v_full[kVStages], v_free[kVStages];
-  uint64_t s_full[2], p_half[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -138,23 +106,6 @@ __device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t 
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// 2^x for a pair of arguments on the FMA pipe (packed fp32x2 arithmetic): x = n + f with n = floor(x),
-// 2^f by a cubic that is exact at f = 0 (max relative error 8.6e-5 on [0, 1)), n added into the
-// exponent field.  Arguments are clamped at -127, where f = 0, the cubic is exactly 1 and the
-// exponent arithmetic yields exactly +0: masked keys (-inf) contribute nothing.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  x.x = fmaxf(x.x, -127.f);
-  x.y = fmaxf(x.y, -127.f);
-  const float2 shifted = __fadd2_rd(x, make_float2(12582912.f, 12582912.f));   // 1.5 * 2^23: integer part in the low mantissa bits
-  const float2 whole = __fadd2_rn(shifted, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(whole, make_float2(-1.f, -1.f), x);              // [0, 1), exact
-  float2 p = __ffma2_rn(f, make_float2(0.0770658627152443f, 0.0770658627152443f),
-                        make_float2(0.22764626145362854f, 0.22764626145362854f));
-  p = __ffma2_rn(f, p, make_float2(0.6951165199279785f, 0.6951165199279785f));
-  p = __ffma2_rn(f, p, make_float2(1.f, 1.f));
-  return make_float2(__uint_as_float(__float_as_uint(shifted.x) * 0x800000u + __float_as_uint(p.x)),
-                     __uint_as_float(__float_as_uint(shifted.y) * 0x800000u + __float_as_uint(p.y)));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -200,8 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     }
     for (int i = 0; i < 2; ++i) {
       bar_init(&sh->s_full[i], 1);
-      bar_init(&sh->p_half[i], 4);      // one arrival per softmax warp of the tile
-      bar_init(&sh->p_full[i], 4);
+      bar_init(&sh->p_full[i], 4);      // one arrival per softmax warp of the tile
       bar_init(&sh->pv_done[i], 1);
     }
     sh->abort = 0;
@@ -260,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const int pr = tid & 127;                                    // packed row == TMEM lane
     const int my_rows = t == 0 ? rows0 : rows1;
     const int mv = my_rows * G;                                  // packed rows of this tile in use
-    const int my_tiles = (GK_DBG_SKIP & 16) ? 0 : t == 0 ? nt0 : nt1;
+    const int my_tiles = t == 0 ? nt0 : nt1;
     const int tile_first_pos = first_pos + t * tile_rows;
     const int lim = pr < mv ? tile_first_pos + pr / G : 0x7fffffff;   // last visible key of this row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -273,8 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     float m = -CUDART_INF_F, l = 0.f;                            // m: exponent reference of this row
     bool alive = true;
     for (int j = 0; j < my_tiles && alive; ++j) {
-      alive = __all_sync(0xffffffffu, (GK_PREFILL_HOT_WAITS & 1) ? bar_wait_hot(&sh->s_full[t], j & 1, &sh->abort)
-                                                                 : bar_wait(&sh->s_full[t], j & 1, &sh->abort));
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[t], j & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
       const int tok0 = kv_begin + j * kTile;
@@ -304,23 +253,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         }
         mult = 1.f;
       }
-#if GK_PREFILL_ONE_PASS
       // ---- the whole row comes in once (128 registers) and stays until it has become P ----
       uint32_t sr[4][32];
-      if (!(GK_DBG_SKIP & 8)) {
       tmem_ld32_nowait(s_addr, sr[0]);
       tmem_ld32_nowait(s_addr + 32, sr[1]);
       tmem_ld32_nowait(s_addr + 64, sr[2]);
       tmem_ld32_nowait(s_addr + 96, sr[3]);
       tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int e = 0; e < 32; ++e) sr[c][e] = __float_as_uint((float)(lane + e + c + j));
-      }
       float mx;
-      if (GK_DBG_SKIP & 2) mx = 1.f; else
       {
         float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -365,93 +305,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), mult2, neg_mu2);
-          // of every 4 consecutive pairs, the first GK_PREFILL_POLY_PAIRS_OF_4 run on the FMA pipe
-          const bool poly = ((GK_PREFILL_POLY_CHUNKS >> c) & 1) || (i & 3) < GK_PREFILL_POLY_PAIRS_OF_4;
-          const float2 pr2 = (GK_DBG_SKIP & 1) ? x : poly ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
-          sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr2);
-          packed[i] = pack_bf16(pr2.x, pr2.y);
-        }
-        if (!(GK_DBG_SKIP & 4)) tmem_st16_nowait(p_addr + c * 16, packed);
-        else if (packed[3] == 0x12345u && packed[7] == 77u && packed[11] == 5u && packed[15] == 9u) l += 1.f;
-#if GK_PREFILL_EARLY_PV
-        if (c == 1) {
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) bar_arrive(&sh->p_half[t]);
-        }
-#endif
-      }
-      l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
-#else
-      // ---- pass 1: row maximum over all 128 columns (the registers are free again afterwards) ----
-      float mx;
-      {
-        uint32_t r0[32], r1[32], r2[32], r3[32];
-        tmem_ld32_nowait(s_addr, r0);
-        tmem_ld32_nowait(s_addr + 32, r1);
-        tmem_ld32_nowait(s_addr + 64, r2);
-        tmem_ld32_nowait(s_addr + 96, r3);
-        tmem_ld_wait();
-        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          mx4[0] = max3(mx4[0], __uint_as_float(r0[e]), __uint_as_float(r0[e + 1]));
-          mx4[1] = max3(mx4[1], __uint_as_float(r1[e]), __uint_as_float(r1[e + 1]));
-          mx4[2] = max3(mx4[2], __uint_as_float(r2[e]), __uint_as_float(r2[e + 1]));
-          mx4[3] = max3(mx4[3], __uint_as_float(r3[e]), __uint_as_float(r3[e + 1]));
-        }
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;            // mult > 0
-      }
-      // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
-      // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
-      float alpha = 1.f;
-      if (mx > m + 8.f || m == -CUDART_INF_F) {
-        if (mx > m) {
-          alpha = fast_exp2(m - mx);                               // 0 on the first finite maximum
-          m = mx;
-        }
-      }
-      const float mu = m == -CUDART_INF_F ? 0.f : m;
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        alive = __all_sync(0xffffffffu, bar_wait(&sh->pv_done[t], (j - 1) & 1, &sh->abort));
-        if (!alive) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t r[32];
-          tmem_ld32(o_addr + cb * 32, r);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tmem_st32(o_addr + cb * 32, r);
-        }
-      }
-      // ---- pass 2: probabilities, 32 columns at a time, the next chunk requested before this one is
-      // worked on.  P (bf16, the reference's rounding point before the second product) overwrites the
-      // LOWER half of S: chunk c writes columns [16c, 16c+16), all of which were read by then.
-      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      const float2 mult2 = make_float2(mult, mult), neg_mu2 = make_float2(-mu, -mu);
-      uint32_t cur[32], nxt[32];
-      tmem_ld32_nowait(s_addr, cur);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c < 3) tmem_ld32_nowait(s_addr + (c + 1) * 32, nxt);
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])), mult2, neg_mu2);
-          // of every 4 consecutive pairs, the first GK_PREFILL_POLY_PAIRS_OF_4 run on the FMA pipe
-          const float2 pr2 = (i & 3) < GK_PREFILL_POLY_PAIRS_OF_4 ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          const float2 pr2 = make_float2(fast_exp2(x.x), fast_exp2(x.y));
           sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr2);
           packed[i] = pack_bf16(pr2.x, pr2.y);
         }
         tmem_st16_nowait(p_addr + c * 16, packed);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) cur[e] = nxt[e];
       }
       l = l * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
-#endif
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();                                      // every lane's P is in tensor memory: one arrival per warp
@@ -518,10 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
       if (round > 0) {   // stage free: K once both Q.K^T of the tile that used it completed, V once both P.V did
         uint64_t* freed = is_v ? &sh->v_free[st] : &sh->k_free[st];
-        const bool got = GK_PREFILL_LOADER_WAIT == 0 ? bar_wait_patient(freed, (round - 1) & 1, &sh->abort)
-                         : GK_PREFILL_LOADER_WAIT == 1 ? bar_wait(freed, (round - 1) & 1, &sh->abort)
-                                                       : bar_wait_hot(freed, (round - 1) & 1, &sh->abort);
-        if (!__all_sync(0xffffffffu, got)) break;
+        if (!__all_sync(0xffffffffu, bar_wait_patient(freed, (round - 1) & 1, &sh->abort))) break;
       }
       const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
       if (by_tma) {
@@ -578,18 +435,14 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       }
       umma_commit(&sh->s_full[t]);
     };
-    auto wait_p = [&](uint64_t* bar, uint32_t parity) {
-      if (GK_DBG_SKIP & 16) return true;
-      return (GK_PREFILL_HOT_WAITS & 2) ? bar_wait_hot(bar, parity, &sh->abort) : bar_wait(bar, parity, &sh->abort);
-    };
-    auto issue_pv = [&](int t, int j, int stage, int k_from, int k_to) {
+    auto issue_pv = [&](int t, int j, int stage) {
       const uint32_t b = v_lo + stage * kStageStep;
 #pragma unroll
-      for (int k = k_from; k < k_to; ++k) {            // 16 tokens per step: 8 columns of P, 16 rows of V
+      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step: 8 columns of P, 16 rows of V
         umma_bf16_ts_split(tmem + 256 + t * kTile, tmem + t * kTile + k * 8, b + k * (2048 >> 4), v_hi, kIdescPV,
                            (j > 0 || k > 0) ? 1u : 0u);
       }
-      if (k_to == 8) umma_commit(&sh->pv_done[t]);
+      umma_commit(&sh->pv_done[t]);
     };
     if (n_tiles > 0) {
       alive = bar_wait(&sh->k_full[0], 0, &sh->abort);
@@ -611,21 +464,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       tc_fence_after();
       for (int t = 0; t < 2 && alive; ++t) {
         if (j < nt[t]) {
-#if GK_PREFILL_EARLY_PV && GK_PREFILL_ONE_PASS
-          alive = wait_p(&sh->p_half[t], j & 1);
+          alive = bar_wait(&sh->p_full[t], j & 1, &sh->abort);
           if (!alive) break;
           tc_fence_after();
-          issue_pv(t, j, vs, 0, 4);
-          alive = wait_p(&sh->p_full[t], j & 1);
-          if (!alive) break;
-          tc_fence_after();
-          issue_pv(t, j, vs, 4, 8);
-#else
-          alive = wait_p(&sh->p_full[t], j & 1);
-          if (!alive) break;
-          tc_fence_after();
-          issue_pv(t, j, vs, 0, 8);
-#endif
+          issue_pv(t, j, vs);
         }
         if (j + 1 < nt[t]) issue_qk(t, ks);
       }

@@ -64,22 +64,6 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, int* ab
   atomicExch(abort, 1);
   return false;
 }
-// The same bounded wait with mbarrier.test_wait, which never suspends the thread: lowest wake-up latency, for
-// the few waits that sit on a kernel's critical chain (it spends issue slots while it polls).
-__device__ __forceinline__ bool bar_wait_hot(uint64_t* bar, uint32_t parity, int* abort) {
-  const uint32_t addr = smem_u32(bar);
-  for (int i = 0; i < kSpinLimit * 8; ++i) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.test_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok)
-                 : "r"(addr), "r"(parity)
-                 : "memory");
-    if (ok) return true;
-    if ((i & 4095) == 4095 && *reinterpret_cast<volatile int*>(abort)) return false;
-  }
-  atomicExch(abort, 1);
-  return false;
-}
 __device__ __forceinline__ bool bar_wait_patient(uint64_t* bar, uint32_t parity, int* abort) {
   const uint32_t addr = smem_u32(bar);
   for (int i = 0; i < kPatientLimit; ++i) {
