@@ -3,12 +3,15 @@
 // Both are HBM-bound elementwise/row kernels.  Every bf16 boundary of the reference (the updated
 // residual, the normalised output, each rotated element) is rounded ONCE from an exactly computed
 // value, which reproduces the reference's binary64 truth (tests/fused_norm_midpoint_smoke.py:32-35,
-// tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact.  To stay on the
-// HBM roof every element first takes a short fp32 evaluation with a known error bound; only when
-// that result lies so close to a bf16 rounding boundary that the bound cannot decide the rounding
-// (a few elements in 10^4 for the norm, one in 65 536 for a sum or a rotation) is the element
-// evaluated again the exact way: directed fp32 roundings with a sticky bit for sums and rotations,
-// binary64 for the norm's scaling.
+// tests/rotary_runtime_smoke.py:28-40) bit for bit wherever fp64 itself is exact:
+//   * the residual add: the fp32 sum of two bf16 values, rounded again to bf16, is always the rounding
+//     of the exact sum (argument at add_bf16_exact);
+//   * the norm's scaling u * inv * (w + offset): a packed fp32 evaluation with a 4.1-ulp error bound
+//     first; only a result within 8 ulp of a bf16 rounding boundary (a few elements in 10^4) is
+//     evaluated again in binary64.  The sum of squares is exact: squares of bf16 values are exact in
+//     fp32 and are added in binary64;
+//   * a rotation a*cos - b*sin: an exact fp32 product plus one fused multiply-add evaluated toward -inf
+//     and toward +inf, with a sticky bit when the two differ (round-to-odd), then one rounding to bf16.
 #include "gk_common.cuh"
 
 #include <algorithm>
@@ -40,27 +43,20 @@ __device__ __forceinline__ unsigned short rotate_pair(unsigned short x, unsigned
   const float sf = __uint_as_float((uint32_t)s << 16);
   if (subtract) yf = -yf;
   const float first = xf * cf;                                  // exact
-  // Round-to-nearest of the exact value (one rounding).  Rounding that again to bf16 can only go
-  // wrong when it sits exactly on a bf16 midpoint without being exact: that case takes the long way.
-  const float nearest = __fmaf_rn(yf, sf, first);
-  if ((__float_as_uint(nearest) & 0xffffu) != 0x8000u) return __bfloat16_as_ushort(__float2bfloat16_rn(nearest));
   const float down = __fmaf_rd(yf, sf, first), up = __fmaf_ru(yf, sf, first);
   float r = down < 0.f ? up : down;                             // toward zero
   if (down != up) r = __uint_as_float(__float_as_uint(r) | 1u);
   return __bfloat16_as_ushort(__float2bfloat16_rn(r));
 }
 
-// bf16(a + b) of two bf16 values, rounded once from the exact sum, without leaving fp32: the add is
-// evaluated toward -inf and toward +inf; if the two differ the sum is inexact in fp32 and the one
-// nearer zero gets a sticky bit (round-to-odd) before the rounding to bf16.
+// bf16(a + b) of two bf16 values, rounded once from the exact sum: the fp32 sum rounded to nearest, rounded
+// again to bf16, IS that.  Two 8-bit significands more than 16 binary places apart are the only way the fp32 sum
+// is inexact, and then the small operand lies entirely below bit 7 of the 24-bit result, so the low half of the
+// result can never read 1000...0 (the one pattern where a second rounding could go the other way); whenever it
+// does read 1000...0 the fp32 sum was exact and ties-to-even is the right answer.  (Checked against the exact
+// sum over 5 x 10^9 pairs covering every finite bf16 value.)
 __device__ __forceinline__ unsigned short add_bf16_exact(unsigned short a, unsigned short b) {
-  const float af = __uint_as_float((uint32_t)a << 16), bf = __uint_as_float((uint32_t)b << 16);
-  const float nearest = __fadd_rn(af, bf);                      // one rounding of the exact sum
-  if ((__float_as_uint(nearest) & 0xffffu) != 0x8000u) return __bfloat16_as_ushort(__float2bfloat16_rn(nearest));
-  const float down = __fadd_rd(af, bf), up = __fadd_ru(af, bf);
-  float r = up;                                                 // exact sum (x + -x gives +0 this way, as round-to-nearest does)
-  if (down != up) r = __uint_as_float(__float_as_uint(down < 0.f ? up : down) | 1u);
-  return __bfloat16_as_ushort(__float2bfloat16_rn(r));
+  return __bfloat16_as_ushort(__float2bfloat16_rn(__fadd_rn(__uint_as_float((uint32_t)a << 16), __uint_as_float((uint32_t)b << 16))));
 }
 // bf16(u * inv * (w + offset)): the norm's scaling step.  Fast evaluation in fp32: four roundings
 // (w + offset, inv to fp32, two products), so the result is within 4.1 ulp of the exact product as
@@ -82,6 +78,73 @@ __device__ __forceinline__ unsigned short scale_to_bf16(unsigned short u, unsign
 __device__ __forceinline__ double square_bf16(unsigned short u) {
   const float f = __uint_as_float((uint32_t)u << 16);
   return (double)(f * f);
+}
+
+// ---- word-wise forms: two bf16 per 32-bit word, packed fp32x2 arithmetic, no branch per element ------------
+// A chunk of 8 elements is evaluated the short way as straight-line code while a flag collects "some
+// element sits where the short way cannot decide its rounding"; only then is the chunk done again the
+// exact way, element by element.  That is one rarely taken branch per 16 bytes instead of one per element.
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t pack2(float2 v) {
+  const __nv_bfloat162 b = __float22bfloat162_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+// u = bf16(a + b) for the 4 words of a chunk (see add_bf16_exact for why one fp32 rounding is enough)
+__device__ __forceinline__ uint4 add_chunk(uint4 a, uint4 b) {
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t out[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) out[w] = pack2(__fadd2_rn(unpack2(aw[w]), unpack2(bw[w])));
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// sum of the 8 squares of a chunk, exact: every square of a bf16 value is exact in fp32, the sum runs in binary64
+__device__ __forceinline__ double square_chunk(uint4 u) {
+  const uint32_t uw[4] = {u.x, u.y, u.z, u.w};
+  double sum = 0.0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const float2 f = unpack2(uw[w]);
+    const float2 q = __fmul2_rn(f, f);
+    sum += (double)q.x + (double)q.y;
+  }
+  return sum;
+}
+
+// y = bf16(u * inv * (w + offset)) for a chunk: the bounded fp32 evaluation of scale_to_bf16, word-wise
+__device__ __forceinline__ uint4 scale_chunk(uint4 u, uint4 w, float inv32, double inv, float offset32, double offset) {
+  const uint32_t uw[4] = {u.x, u.y, u.z, u.w}, ww[4] = {w.x, w.y, w.z, w.w};
+  uint32_t out[4];
+  bool hard = false;
+  const float2 inv2 = make_float2(inv32, inv32), off2 = make_float2(offset32, offset32);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 uf = unpack2(uw[i]);
+    const float2 a = __fmul2_rn(uf, inv2);
+    const float2 y = __fmul2_rn(a, __fadd2_rn(unpack2(ww[i]), off2));
+    const float av[2] = {a.x, a.y}, yv[2] = {y.x, y.y};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t bits = __float_as_uint(yv[h]);
+      const bool near_midpoint = (((bits & 0xffffu) - 0x7ff8u) & 0xffffu) <= 16u;             // within 8 ulp
+      // exponent fields of y and of the intermediate product in [32, 254): nothing subnormal, nothing infinite
+      const bool sized = ((bits & 0x7f800000u) - 0x10000000u) < 0x6f000000u &&
+                         ((__float_as_uint(av[h]) & 0x7f800000u) - 0x10000000u) < 0x6f000000u;
+      const bool zero = ((uw[i] >> (16 * h)) & 0x7fffu) == 0u;                                // u = +-0 gives y = +-0 exactly
+      hard |= !zero && (near_midpoint || !sized);
+    }
+    out[i] = pack2(y);
+  }
+  if (hard) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      out[i] = (uint32_t)scale_to_bf16((unsigned short)uw[i], (unsigned short)ww[i], inv32, inv, offset32, offset) |
+               (uint32_t)scale_to_bf16((unsigned short)(uw[i] >> 16), (unsigned short)(ww[i] >> 16), inv32, inv, offset32, offset) << 16;
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 __device__ __forceinline__ double block_sum(double v, double* shared) {
@@ -157,7 +220,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
   double sumsq = 0.0;
   if (VEC == 8) {
     constexpr int kItems = 4;
-    unsigned short u[kItems][8];
+    uint4 u[kItems];
 #pragma unroll
     for (int it = 0; it < kItems; ++it) {
       const int col = (it * 256 + threadIdx.x) * 8;
@@ -170,19 +233,13 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
         } else {
           a = __ldg(reinterpret_cast<const uint4*>(xr + col));
         }
-        const unsigned short* av = reinterpret_cast<const unsigned short*>(&a);
         if (FUSED) {
-          uint4 b = __ldg(reinterpret_cast<const uint4*>(rr + col));
-          const unsigned short* bv = reinterpret_cast<const unsigned short*>(&b);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) u[it][e] = add_bf16_exact(av[e], bv[e]);
-          *reinterpret_cast<uint4*>(ur + col) = *reinterpret_cast<const uint4*>(u[it]);
+          u[it] = add_chunk(a, __ldg(reinterpret_cast<const uint4*>(rr + col)));
+          *reinterpret_cast<uint4*>(ur + col) = u[it];
         } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) u[it][e] = av[e];
+          u[it] = a;
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sumsq += square_bf16(u[it][e]);
+        sumsq += square_chunk(u[it]);
       }
     }
     const double total = block_sum(sumsq, partial);
@@ -191,14 +248,9 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
 #pragma unroll
     for (int it = 0; it < kItems; ++it) {
       const int col = (it * 256 + threadIdx.x) * 8;
-      if (col < hidden) {
-        uint4 w = __ldg(reinterpret_cast<const uint4*>(weight + col));
-        const unsigned short* wv = reinterpret_cast<const unsigned short*>(&w);
-        unsigned short out[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) out[e] = scale_to_bf16(u[it][e], wv[e], inv32, inv, offset32, weight_offset);
-        *reinterpret_cast<uint4*>(yr + col) = *reinterpret_cast<const uint4*>(out);
-      }
+      if (col < hidden)
+        *reinterpret_cast<uint4*>(yr + col) =
+            scale_chunk(u[it], __ldg(reinterpret_cast<const uint4*>(weight + col)), inv32, inv, offset32, weight_offset);
     }
   } else {
     for (int col = threadIdx.x; col < hidden; col += 256) {
@@ -234,7 +286,6 @@ struct RotaryParams {
   int32_t* status;
   int64_t rows, q_stride, k_stride, v_stride, cache_rows, slots;
   int q_heads, k_heads, head_dim, rotary_dim, is_neox;
-  int chunk_shift;      // log2(head_dim / 8) when that is a power of two, else -1
 };
 
 __device__ __forceinline__ unsigned short rotate_element(const unsigned short* head, const unsigned short* table,
@@ -311,12 +362,12 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
   const int chunks = p.head_dim >> 3;
   const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
   const int per_row = heads * chunks;
+  const int64_t total = p.rows * (int64_t)per_row;
   const int half = p.rotary_dim >> 1;
-  // blockIdx.y walks the rows, blockIdx.x * 256 + threadIdx.x the 16-byte chunks of a row: no 64-bit
-  // division per element (it used to cost more than the rotation itself)
-  for (int64_t row = blockIdx.y; row < p.rows; row += gridDim.y)
-  for (int rem = blockIdx.x * blockDim.x + threadIdx.x; rem < per_row; rem += gridDim.x * blockDim.x) {
-    const int head = p.chunk_shift >= 0 ? rem >> p.chunk_shift : rem / chunks, ch = rem - head * chunks;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = idx / per_row;
+    const int rem = (int)(idx - row * per_row);
+    const int head = rem / chunks, ch = rem - head * chunks;
     const int kh = head - p.q_heads;
     if (STORE && kh >= p.k_heads) {                              // V: straight to its slot
       const int vh = kh - p.k_heads;
@@ -388,20 +439,16 @@ bool rotary_vectorisable(const RotaryParams& p, bool store) {
   return !(bits & 15) && !(strides & 7) && p.head_dim % 8 == 0 && p.rotary_dim % (p.is_neox ? 16 : 8) == 0;
 }
 
-int launch_rotary(const RotaryParams& params, bool store, cudaStream_t stream) {
-  RotaryParams p = params;
+int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
   if (rotary_vectorisable(p, store)) {
     const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
-    const int chunks = p.head_dim / 8, per_row = heads * chunks;
-    p.chunk_shift = (chunks & (chunks - 1)) == 0 ? __builtin_ctz((unsigned)chunks) : -1;
-    const int threads = per_row >= 256 ? 256 : (per_row + 31) / 32 * 32;
-    const unsigned across = (unsigned)((per_row + threads - 1) / threads);
-    const int64_t down = std::min<int64_t>(p.rows, std::max<int64_t>(1, 148 * 16 / across));
-    const dim3 grid(across, (unsigned)down);
+    const int64_t total = p.rows * heads * (p.head_dim / 8);
+    const int64_t want = (total + 255) / 256;
+    const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
     if (store)
-      rotary_vec_kernel<true><<<grid, threads, 0, stream>>>(p);
+      rotary_vec_kernel<true><<<blocks, 256, 0, stream>>>(p);
     else
-      rotary_vec_kernel<false><<<grid, threads, 0, stream>>>(p);
+      rotary_vec_kernel<false><<<blocks, 256, 0, stream>>>(p);
     return check_launch();
   }
   const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);

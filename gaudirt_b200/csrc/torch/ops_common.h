@@ -437,7 +437,11 @@ class PagedMetadata : public torch::CustomClassHolder {
     // when only a few blocks are split: it saves a launch whose grid would be tiny.  With many split
     // blocks the merges are better spread over the whole GPU by the separate combine kernel
     // (measured: 2-5 % faster fused at 4-23 split blocks, 2-9 % slower at 64-256).
-    const bool fuse = fused_combine_ > 0 || (fused_combine_ < 0 && n_combine * 4 <= sm_count);
+    // Blocks cut in two (the uneven cut that fills a tensor-parallel shard's single wave) merge so little state
+    // that the fused form costs nothing even with hundreds of them, and it saves the launch.
+    int32_t most_splits = 0;
+    for (int64_t i = 0; i < n_combine; ++i) most_splits = std::max(most_splits, host[combine_offset + i * GK_COMBINE_WORDS + 3]);
+    const bool fuse = fused_combine_ > 0 || (fused_combine_ < 0 && (n_combine * 4 <= sm_count || most_splits <= 2));
     if (n_combine > 0 && fuse)
       plan->counters = at::zeros({rows_ * kv_heads}, at::TensorOptions().dtype(at::kInt).device(device));
     plan->table = mapping_;
