@@ -228,3 +228,39 @@ def test_slot_layout_random_batches_agree_with_the_oracle():
             at += lengths[r]
 
     check()
+
+
+def test_plan_cuts_partition_every_range_including_uneven_cuts():
+    """Whatever cut the schedule search picks (even pieces, or pieces of the limit with the remainder last, which
+    it may pick when the grid is a few waves), the pieces of a block tile its KV range exactly, in split order,
+    and the split state is sized for them."""
+    shapes = [
+        (np.array([[i, 1, 4095, i] for i in range(256)], dtype=np.int32), 4, 1),      # one KV head of config 2: one wave
+        (np.array([[i, 1, 4095, i] for i in range(256)], dtype=np.int32), 8, 2),
+        (np.array([[i, 1, 4095, i] for i in range(256)], dtype=np.int32), 32, 8),     # the whole GPU: no cut
+        (np.array([[i, 1, 300 + 97 * i, i] for i in range(40)], dtype=np.int32), 8, 1),
+    ]
+    saw_uneven = False
+    for seq, hq, hkv in shapes:
+        work, combine, entries = H.plan(seq, hq, hkv, 128, sm_count=148)
+        by_row = {}
+        for w in work:
+            by_row.setdefault(int(w[0]), []).append(w)
+        total = 0
+        for first_row, n_rows, first_pos, table_row in seq:
+            pieces = sorted(by_row[int(first_row)], key=lambda w: int(w[7]) >> 16)
+            n_splits = int(pieces[0][7]) & 0xffff
+            assert len(pieces) == n_splits and [int(p[7]) >> 16 for p in pieces] == list(range(n_splits))
+            assert int(pieces[0][4]) == 0 and int(pieces[-1][5]) == first_pos + n_rows
+            for a, b in zip(pieces, pieces[1:]):
+                assert int(a[5]) == int(b[4]) and int(a[5]) > int(a[4])
+            lengths = [int(p[5]) - int(p[4]) for p in pieces]
+            saw_uneven |= n_splits > 1 and len(set(lengths[:-1] + [lengths[-1]])) > 1 and lengths[-1] < lengths[0] // 2
+            if n_splits > 1:
+                bases = [int(p[6]) for p in pieces]
+                assert bases == [bases[0] + s * n_rows * hq for s in range(n_splits)]
+                total += n_splits * n_rows * hq
+            else:
+                assert int(pieces[0][6]) == -1
+        assert total == entries and len(combine) == sum(1 for r in by_row.values() if len(r) > 1)
+    assert saw_uneven, "the one-wave shard of equal ranges is where the uneven cut is chosen"
