@@ -92,8 +92,11 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       q1 = reinterpret_cast<const unsigned short*>(p.q) + (int64_t)(first_row + r) * p.q_stride +
            (int64_t)(head * G + gq) * D;
     }
+    // two consecutive bf16 of a query row: one 32-bit load when the row is 4-byte aligned (col is even), else
+    // two 16-bit loads (the reference's one-element-offset views are only 2-byte aligned)
     auto pair = [](const unsigned short* base, int col) -> uint32_t {
       if (base == nullptr) return 0u;
+      if ((reinterpret_cast<uintptr_t>(base) & 3) == 0) return __ldg(reinterpret_cast<const uint32_t*>(base + col));
       return (uint32_t)__ldg(base + col) | ((uint32_t)__ldg(base + col + 1) << 16);
     };
 #pragma unroll

@@ -49,3 +49,15 @@ def test_counted_form_keeps_its_epoch_on_the_device(rt):
     assert counter.item() == 3 and rt._C._take_device_status() == 4
     with pytest.raises(RuntimeError, match="epoch counter"):
         torch.ops.gaudirt._peer_barrier_counted([mine, peer], 0, torch.zeros(2, dtype=torch.int32, device=DEV), SHORT)
+
+
+def test_step_end_check_raises_when_a_wait_ran_out(rt):
+    """The exchanges hand out their buffers even when the bounded wait expired (the kernel only sets a status bit);
+    the step-end check is what turns that into an error instead of an incomplete activation."""
+    from gaudirt_b200 import tp
+    mine, peer = torch.zeros(8, dtype=torch.int32, device=DEV), torch.zeros(8, dtype=torch.int32, device=DEV)
+    tp.check_device_status(DEV)                                          # clean: no raise
+    torch.ops.gaudirt._peer_barrier([mine, peer], 0, 1, SHORT)           # the peer never signals
+    with pytest.raises(RuntimeError, match="bounded wait ran out"):
+        tp.check_device_status(DEV)
+    tp.check_device_status(DEV)                                          # the word was cleared by the failed check
