@@ -54,11 +54,14 @@ def build_abi(force: bool = False, verbose: bool = False) -> str:
     deps = sources + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
     if force or _stale(ABI_SO, deps):
         os.makedirs(LIB, exist_ok=True)
+        # built beside the target and moved into place, so that a reader never sees a half-written library
+        fresh = ABI_SO + ".new"
         cmd = [_nvcc(), *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
-               "-shared", "-o", ABI_SO, *sources]
+               "-shared", "-o", fresh, *sources]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd)
+        os.replace(fresh, ABI_SO)
     return ABI_SO
 
 
@@ -82,9 +85,11 @@ def build_ops(force: bool = False) -> str:
                 _run(["g++", "-O2", "-std=c++17", "-fPIC", abi_flag, "-DTORCH_API_INCLUDE_EXTENSION_H", *inc,
                       f"-I{os.path.join(ROOT, 'include')}", "-c", src, "-o", obj])
             objs.append(obj)
-        _run(["g++", "-shared", "-o", OPS_SO, *objs, f"-L{LIB}", "-lgaudirt_b200", f"-L{torch_lib}",
+        fresh = OPS_SO + ".new"
+        _run(["g++", "-shared", "-o", fresh, *objs, f"-L{LIB}", "-lgaudirt_b200", f"-L{torch_lib}",
               "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
               "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"])
+        os.replace(fresh, OPS_SO)
     return OPS_SO
 
 

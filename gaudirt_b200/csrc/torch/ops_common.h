@@ -18,6 +18,7 @@
 #include <mutex>
 #include <random>
 #include <tuple>
+#include <unordered_set>
 #include <utility>
 #include <vector>
 
@@ -282,8 +283,32 @@ class PagedMetadata : public torch::CustomClassHolder {
       const uint64_t page = static_cast<uint64_t>(host.data_ptr<int64_t>()[2]);
       page_tokens_ = static_cast<int64_t>(std::min<uint64_t>(page, 128));
       if (first != UINT64_MAX || token != UINT64_MAX) clear_status_bits(device.index(), GK_DEV_BAD_METADATA);
-      TORCH_CHECK(first == UINT64_MAX, "GaudiRT device metadata: invalid scheduler metadata at row ", first >> 8,
-                  ", code ", first & 255);
+      uint64_t bad_row = first >> 8, bad_code = first & 255;
+      if (first != UINT64_MAX && bad_code == 4) {
+        // Two rows write one slot: on the device, which of them met the other's mark depends on arrival
+        // order.  The error path can afford a walk on the host over the per-row codes: a duplicate is charged
+        // to the later row of the pair, as the reference's host constructor does
+        // (src/bridge/paged_metadata.cpp:104-140), and the first row in row order that carries any code is
+        // the one reported.
+        const auto slots_host = loc.to(at::kLong).cpu();
+        const auto codes_host = row_status.cpu();
+        const int64_t* sl = slots_host.data_ptr<int64_t>();
+        const int32_t* codes = codes_host.data_ptr<int32_t>();
+        std::unordered_set<int64_t> seen;
+        for (int64_t r = 0; r < m; ++r) {
+          // only a row that passed its own range and table checks marks its slot (as on the device)
+          const bool passed = codes[r] == 0 || codes[r] == 4;
+          const bool duplicate = passed && !seen.insert(sl[r]).second;
+          const int32_t code = duplicate ? 4 : (passed ? 0 : codes[r]);
+          if (code != 0) {
+            bad_row = static_cast<uint64_t>(r);
+            bad_code = static_cast<uint64_t>(code);
+            break;
+          }
+        }
+      }
+      TORCH_CHECK(first == UINT64_MAX, "GaudiRT device metadata: invalid scheduler metadata at row ", bad_row,
+                  ", code ", bad_code);
       TORCH_CHECK(token == UINT64_MAX, "GaudiRT device metadata: token ID outside vocabulary at row ", token);
     }
   }
