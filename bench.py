@@ -144,6 +144,8 @@ def parse():
                          "rank-ordered sum of the partials and the residual-add RMS norm, instead of the output gather")
     ap.add_argument("--shard-of", type=int, default=1,
                     help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
+    ap.add_argument("--split-tokens", type=int, default=0,
+                    help="experiments only: longest KV range of one work item (0 = chosen by the schedule search)")
     ap.add_argument("--no-tp-configs", action="store_true",
                     help="with N > 1: measure the chosen configuration only, not configs 3 and 5 after it")
     return ap.parse_args()
@@ -447,6 +449,7 @@ def measure(args, config, world, rank, dev, headline):
     def host_metadata():
         md = rt.PagedMetadata(locations, requests, positions, mapping, slots)
         md._set_fused_combine(combine_mode)
+        md._set_split_tokens(args.split_tokens)
         md.attention_plan(hq, hkv, d)
         return md
 
@@ -607,6 +610,7 @@ def measure(args, config, world, rank, dev, headline):
                 t.record_stream(main)                 # allocated on the copy stream, consumed on the compute stream
             main.wait_stream(copy_in)
         step_md._set_fused_combine(combine_mode)
+        step_md._set_split_tokens(args.split_tokens)
         step_md.attention_plan(hq, hkv, d)
         staged, done = {}, {}
 
@@ -649,6 +653,7 @@ def measure(args, config, world, rank, dev, headline):
             index_dev = [t.to(dev) for t in host_index]
             md_e2e = rt.PagedMetadata.from_device(*index_dev, table_dev, prefix_list, length_list, slots)
             md_e2e._set_fused_combine(combine_mode)
+            md_e2e._set_split_tokens(args.split_tokens)
             md_e2e.attention_plan(hq, hkv, d)
             dev_qkv = torch.empty_like(resident_qkv)
             dev_xr = torch.empty_like(resident_xr) if w.front else None
@@ -729,7 +734,8 @@ def measure(args, config, world, rank, dev, headline):
                                                    len(work), out.data_ptr(), out.stride(0), scale, 0.0, -1, hq, hkv, d,
                                                    None, s), "gk_paged_prefill_tc_bf16")
     else:
-        work, combine, entries = H.plan(seq, hq, hkv, d, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
+        work, combine, entries = H.plan(seq, hq, hkv, d, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count,
+                                        split_tokens=args.split_tokens)
         work_d = torch.from_numpy(work).to(dev)
         pml, po = torch.empty(max(entries, 1) * 2, device=dev), torch.empty(max(entries, 1) * d, device=dev)
 
@@ -849,7 +855,7 @@ def run_b200(args):
     line = measure(args, args.config, world, rank, dev, headline=True)
     # The tensor-parallel configurations ride along with the default multi-GPU run, so that one scaling
     # sweep of the headline benchmark also carries their curves.
-    plain = args.config == 2 and not (args.layers or args.batch or args.ctx or args.oproj or args.no_graph)
+    plain = args.config == 2 and not (args.layers or args.batch or args.ctx or args.oproj or args.no_graph or args.split_tokens)
     if world > 1 and plain and not args.no_tp_configs:
         extra = {}
         for config in (3, 5):

@@ -4,8 +4,11 @@
 // one KV head of those rows are packed into TWO query tiles of 128 rows each (tile t = rows
 // [t*128/G, (t+1)*128/G) of the record); both tiles attend to the KV range [kv_begin, kv_end) of the pool
 // (prefix + the rows themselves, causal inside the chunk), so every K/V tile is fetched once for 256
-// packed rows.  Q.K^T (128 x 128 x d) and P.V (128 x d x 128) run as tcgen05.mma.kind::f16 with fp32
-// accumulators in tensor memory:
+// packed rows.  Q.K^T (128 x T x d) and P.V (128 x d x T) run as tcgen05.mma.kind::f16 with fp32
+// accumulators in tensor memory.  The description below is head_dim 128 (KV tiles of T = 128 tokens);
+// head_dim 64 is the same with 64-column accumulators, and head_dim 256, whose two 256-column accumulators
+// would not fit beside the scores, runs ONE query tile per CTA (the record's two tiles go to two CTAs)
+// against KV tiles of 64 tokens, so that two K and three V stages still fit in shared memory:
 //
 //   TMEM (512 columns)   S0 | S1 | O0 | O1, 128 columns each; P_t (bf16, 64 columns) overwrites the lower
 //                        half of S_t and is the A operand of P_t.V straight from tensor memory
@@ -35,15 +38,31 @@
 namespace gk {
 namespace {
 
-constexpr int kTile = 128;             // packed query rows per tile, KV tokens per tile, head_dim
-constexpr int kPanelBytes = kTile * 128;
-constexpr int kTileBytes = 2 * kPanelBytes;          // 32 KiB: one [128 x 128] bf16 operand
+constexpr int kRows = 128;             // packed query rows per tile = lanes of tensor memory
 constexpr int kKStages = 2, kVStages = 3;
 constexpr int kSoftmaxThreads = 256, kLoaderThreads = 64, kThreads = 512;   // loaders: 64 threads for K, 64 for V
 constexpr int kLaunchRegs = 128;     // what __launch_bounds__(512, 1) lets ptxas allocate per thread
 constexpr int kSoftmaxRegs = 184, kLoaderRegs = 80, kIssueRegs = 64;
 static_assert(kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueRegs <= kThreads * kLaunchRegs,
               "register budgets exceed the pool the launch allocates");
+
+// Shapes that follow from head_dim D.  Operand tiles are stored as D/64 panels of [rows x 128 bytes] with the
+// 128-byte swizzle; a query tile has 128 rows, a K or V tile kKv rows.
+template <int D>
+struct Geo {
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim");
+  static constexpr int kKv = D == 256 ? 64 : 128;          // KV tokens per tile
+  static constexpr int kTiles = D == 256 ? 1 : 2;          // query tiles per CTA
+  static constexpr int kPanels = D / 64, kChunks = D / 8;  // 128-byte panels, 16-byte chunks per row
+  static constexpr int kQPanelBytes = kRows * 128, kQTileBytes = kPanels * kQPanelBytes;
+  static constexpr int kKvPanelBytes = kKv * 128, kKvTileBytes = kPanels * kKvPanelBytes;
+  static constexpr int kSmemBytes = kTiles * kQTileBytes + (kKStages + kVStages) * kKvTileBytes + 3072;
+  // kind::f16 instruction descriptors: fp32 accumulate, bf16 x bf16, M = 128; N = kKv (A, B K-major) for the
+  // scores, N = D with B (= V) MN-major for the second product.
+  static constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kKv >> 3) << 17) | (8u << 24);
+  static constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | (8u << 24);
+};
+static_assert(Geo<128>::kSmemBytes <= 227 * 1024 && Geo<256>::kSmemBytes <= 227 * 1024, "shared memory of an SM");
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct PrefillParams {
@@ -69,13 +88,10 @@ struct Shared {
   int abort;
 };
 
-__device__ __forceinline__ uint32_t tile_off(int r, int c) {
-  return (c >> 3) * kPanelBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+// Byte offset of 16-byte chunk c of row r inside a tile whose panels are panel_bytes apart.
+__device__ __forceinline__ uint32_t tile_off(int r, int c, int panel_bytes) {
+  return (c >> 3) * panel_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
 }
-
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = 128.
-constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);   // A, B K-major
-constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);                                            // B (= V) MN-major
 
 // The MMAs take each 64-bit shared-memory descriptor as its two halves: the upper half (strides, swizzle mode)
 // is the same for every tile of one operand kind, the lower half is the address field plus the
@@ -112,31 +128,48 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const PrefillParams p,
                                                                        const __grid_constant__ CUtensorMap map_k,
                                                                        const __grid_constant__ CUtensorMap map_v) {
+  using G_ = Geo<D>;
+  constexpr int kKv = G_::kKv, kTiles = G_::kTiles, kChunks = G_::kChunks;
+  constexpr int kQPanelBytes = G_::kQPanelBytes, kQTileBytes = G_::kQTileBytes;
+  constexpr int kKvPanelBytes = G_::kKvPanelBytes, kKvTileBytes = G_::kKvTileBytes;
+  constexpr int kScoreChunks = kKv / 32;                 // 32-column pieces of a row of S
   extern __shared__ __align__(1024) uint8_t tiles[];     // swizzle atoms need 1 KiB alignment
-  uint8_t* s_q = tiles;                                  // two query tiles
-  uint8_t* s_k = tiles + 2 * kTileBytes;                 // K stages
-  uint8_t* s_v = tiles + (2 + kKStages) * kTileBytes;    // V stages
-  Shared* sh = reinterpret_cast<Shared*>(tiles + (2 + kKStages + kVStages) * kTileBytes);
+  uint8_t* s_q = tiles;                                  // the query tiles
+  uint8_t* s_k = s_q + kTiles * kQTileBytes;             // K stages
+  uint8_t* s_v = s_k + kKStages * kKvTileBytes;          // V stages
+  Shared* sh = reinterpret_cast<Shared*>(s_v + kVStages * kKvTileBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(tiles) & 1023) {                          // cannot build valid descriptors: report, leave
     if (tid == 0 && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
     return;
   }
-  const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
+  // With one query tile per CTA the record's two tiles go to two consecutive CTAs.
+  const int unit = kTiles == 2 ? blockIdx.x : blockIdx.x >> 1, half = kTiles == 2 ? 0 : blockIdx.x & 1;
+  const int item = unit / p.kv_heads, head = unit - item * p.kv_heads;
   const int4 w0 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item);
   const int4 w1 = __ldg(reinterpret_cast<const int4*>(p.work) + 2 * item + 1);
-  const int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, table_row = w0.w;
-  const int kv_begin = w1.x, kv_end = w1.y;
   const int G = p.group;
-  const int tile_rows = kTile / G;                          // rows of the record per query tile
+  const int tile_rows = kRows / G;                          // rows of the record per query tile
+  int first_row = w0.x, n_rows = w0.y, first_pos = w0.z, kv_begin = w1.x, kv_end = w1.y;
+  const int table_row = w0.w;
+  if (kTiles == 1) {                                        // this CTA's tile of the record, as a record of its own
+    const int skip = half * tile_rows;
+    n_rows = min(n_rows - skip, tile_rows);
+    if (n_rows <= 0) return;                                // the whole CTA: nothing is allocated yet
+    first_row += skip;
+    first_pos += skip;
+    kv_end = min(kv_end, first_pos + n_rows);               // causal: nothing after this tile's last row
+    if (p.window > 0) kv_begin = max(kv_begin, first_pos - p.window + 1);
+  }
   const int rows0 = min(n_rows, tile_rows), rows1 = n_rows - rows0;
   // KV tiles each query tile needs: tile 0 stops at its own last row (causal), tile 1 at the record's end
-  const int nt1_all = (kv_end - kv_begin + kTile - 1) / kTile;
-  const int nt0 = min(nt1_all, (first_pos + rows0 - kv_begin + kTile - 1) / kTile);
+  const int nt1_all = (kv_end - kv_begin + kKv - 1) / kKv;
+  const int nt0 = min(nt1_all, (first_pos + rows0 - kv_begin + kKv - 1) / kKv);
   const int nt1 = rows1 > 0 ? nt1_all : 0;
   const int n_tiles = max(nt0, nt1);
 
@@ -169,12 +202,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     // Q tiles: packed row pr of tile t = (row t*tile_rows + pr / G, query head pr % G) of this KV head; unused rows
     // are zero.  The loader warps do not take part: their first K/V tiles are already on the way meanwhile.
     const int filler = warp < 8 ? tid : tid - 128;       // 0..383
-    for (int i = filler; i < 2 * kTile * 16; i += kThreads - 128) {
-      const int t = i >> 11, pr = (i >> 4) & 127, c = i & 15;
+    for (int i = filler; i < kTiles * kRows * kChunks; i += kThreads - 128) {
+      const int t = i / (kRows * kChunks), pr = (i / kChunks) & (kRows - 1), c = i & (kChunks - 1);
       uint4 v = make_uint4(0, 0, 0, 0);
       const int r = t * tile_rows + pr / G, g = pr % G;
       if (pr < tile_rows * G && r < n_rows) {
-        const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * kTile + c * 8;
+        const __nv_bfloat16* src = p.q + (int64_t)(first_row + r) * p.q_stride + (int64_t)(head * G + g) * D + c * 8;
         if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
           v = __ldg(reinterpret_cast<const uint4*>(src));
         } else {
@@ -185,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           v = *reinterpret_cast<const uint4*>(e);
         }
       }
-      *reinterpret_cast<uint4*>(s_q + t * kTileBytes + tile_off(pr, c)) = v;
+      *reinterpret_cast<uint4*>(s_q + t * kQTileBytes + tile_off(pr, c, kQPanelBytes)) = v;
     }
     fence_async_smem();
     asm volatile("bar.sync 1, %0;\n" ::"n"(kThreads - 128) : "memory");      // the 384 threads that filled Q
@@ -214,9 +247,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const int tile_first_pos = first_pos + t * tile_rows;
     const int lim = pr < mv ? tile_first_pos + pr / G : 0x7fffffff;   // last visible key of this row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem + t * kTile + lane_base;        // S_t; P_t overwrites its lower 64 columns
+    const uint32_t s_addr = tmem + t * 128 + lane_base;          // S_t; P_t overwrites its lower half
     const uint32_t p_addr = s_addr;
-    const uint32_t o_addr = tmem + 256 + t * kTile + lane_base;
+    const uint32_t o_addr = tmem + 256 + t * D + lane_base;
     const bool capped = p.softcap > 0.f;
     const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
@@ -226,8 +259,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[t], j & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
-      const int tok0 = kv_begin + j * kTile;
-      const int tile_end = tok0 + kTile;
+      const int tok0 = kv_begin + j * kKv;
+      const int tile_end = tok0 + kKv;
       const bool ragged = tile_end > kv_end || tile_end > tile_first_pos + 1 ||
                           (p.window > 0 && tok0 <= tile_first_pos + my_rows - 1 - p.window);
       // Softcap and tiles that need masking are uncommon: they first rewrite S in tensor memory (scores in
@@ -237,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       float mult = to_log2;
       if (capped || ragged) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kScoreChunks; ++c) {
           uint32_t r[32];
           tmem_ld32(s_addr + c * 32, r);
 #pragma unroll
@@ -253,24 +286,25 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         }
         mult = 1.f;
       }
-      // ---- the whole row comes in once (128 registers) and stays until it has become P ----
-      uint32_t sr[4][32];
-      tmem_ld32_nowait(s_addr, sr[0]);
-      tmem_ld32_nowait(s_addr + 32, sr[1]);
-      tmem_ld32_nowait(s_addr + 64, sr[2]);
-      tmem_ld32_nowait(s_addr + 96, sr[3]);
+      // ---- the whole row comes in once (up to 128 registers) and stays until it has become P ----
+      uint32_t sr[kScoreChunks][32];
+#pragma unroll
+      for (int c = 0; c < kScoreChunks; ++c) tmem_ld32_nowait(s_addr + c * 32, sr[c]);
       tmem_ld_wait();
       float mx;
       {
-        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        float part[kScoreChunks];
+#pragma unroll
+        for (int c = 0; c < kScoreChunks; ++c) part[c] = -CUDART_INF_F;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          mx4[0] = max3(mx4[0], __uint_as_float(sr[0][e]), __uint_as_float(sr[0][e + 1]));
-          mx4[1] = max3(mx4[1], __uint_as_float(sr[1][e]), __uint_as_float(sr[1][e + 1]));
-          mx4[2] = max3(mx4[2], __uint_as_float(sr[2][e]), __uint_as_float(sr[2][e + 1]));
-          mx4[3] = max3(mx4[3], __uint_as_float(sr[3][e]), __uint_as_float(sr[3][e + 1]));
+#pragma unroll
+          for (int c = 0; c < kScoreChunks; ++c)
+            part[c] = max3(part[c], __uint_as_float(sr[c][e]), __uint_as_float(sr[c][e + 1]));
         }
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mult;            // mult > 0
+        mx = fmaxf(part[0], part[1]);
+        if (kScoreChunks == 4) mx = fmaxf(mx, fmaxf(part[2], part[3]));
+        mx *= mult;                                                                 // mult > 0
       }
       // The exponent reference only moves when the maximum grew by more than 2^8: P stays within
       // bf16/fp32 range and O needs rescaling (and the wait for the previous P.V) only then.
@@ -287,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         if (!alive) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
+        for (int cb = 0; cb < D / 32; ++cb) {
           uint32_t r[32];
           tmem_ld32(o_addr + cb * 32, r);
 #pragma unroll
@@ -300,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       const float2 mult2 = make_float2(mult, mult), neg_mu2 = make_float2(-mu, -mu);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kScoreChunks; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -324,9 +358,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         tc_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int r_q = t * tile_rows + pr / G, g = pr % G;
-        const int64_t at = (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * kTile;
+        const int64_t at = (int64_t)(first_row + r_q) * p.out_stride + (int64_t)(head * G + g) * D;
 #pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
+        for (int cb = 0; cb < D / 32; ++cb) {
           uint32_t r[32];
           tmem_ld32(o_addr + cb * 32, r);
           if (pr < mv) {
@@ -348,19 +382,20 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const bool is_v = warp >= 10;
     const int lwarp = (warp - 8) & 1;
     const int stages = is_v ? kVStages : kKStages;
-    const __nv_bfloat16* base = (is_v ? p.pool_v : p.pool_k) + (int64_t)head * p.slots * kTile;
+    const __nv_bfloat16* base = (is_v ? p.pool_v : p.pool_k) + (int64_t)head * p.slots * D;
     const int32_t* trow = p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
     const int page_mask = (1 << p.page_shift) - 1;
     const CUtensorMap* map = is_v ? &map_v : &map_k;
     const int head_row = head * (int)p.slots;
     int st = 0, round = 0;                                   // ring position of tile j: stage j % stages, round j / stages
     for (int j = 0; j < n_tiles; ++j) {
-      // each loader warp stages 64 rows, 32 at a time: lanes resolve one slot each, then the
-      // warp copies two 256-byte rows per instruction (16 lanes x 16 bytes each)
-      int slot[2];
+      // each loader warp stages half a tile, 32 rows at a time: lanes resolve one slot each, then the
+      // warp copies 512 bytes of consecutive rows per instruction (16 bytes a lane)
+      constexpr int kWarpRows = kKv / 2, kHalves = kWarpRows / 32;
+      int slot[kHalves];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int tok = kv_begin + j * kTile + lwarp * 64 + half * 32 + lane;
+      for (int half = 0; half < kHalves; ++half) {
+        const int tok = kv_begin + j * kKv + lwarp * kWarpRows + half * 32 + lane;
         slot[half] = -1;
         if (tok < kv_end) {
           slot[half] = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
@@ -370,40 +405,41 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           }
         }
       }
-      // This warp's 64 rows go by TMA when they are whole, in-range boxes of tma_rows slot-contiguous
+      // This warp's rows go by TMA when they are whole, in-range boxes of tma_rows slot-contiguous
       // tokens; the two warps of a tile decide independently (every thread arrives once either way).
-      const int tok_first = kv_begin + j * kTile + lwarp * 64;
-      bool by_tma = p.tma_rows > 0 && (tok_first & (p.tma_rows - 1)) == 0 && tok_first + 64 <= kv_end;
-      by_tma = __all_sync(0xffffffffu, by_tma && slot[0] >= 0 && slot[1] >= 0);
+      const int tok_first = kv_begin + j * kKv + lwarp * kWarpRows;
+      bool by_tma = p.tma_rows > 0 && (tok_first & (p.tma_rows - 1)) == 0 && tok_first + kWarpRows <= kv_end;
+      by_tma = __all_sync(0xffffffffu, by_tma && slot[0] >= 0 && slot[kHalves - 1] >= 0);
       uint64_t* full = is_v ? &sh->v_full[st] : &sh->k_full[st];
       if (round > 0) {   // stage free: K once both Q.K^T of the tile that used it completed, V once both P.V did
         uint64_t* freed = is_v ? &sh->v_free[st] : &sh->k_free[st];
         if (!__all_sync(0xffffffffu, bar_wait_patient(freed, (round - 1) & 1, &sh->abort))) break;
       }
-      const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kTileBytes;
+      const uint32_t dst = smem_u32(is_v ? s_v : s_k) + st * kKvTileBytes;
       if (by_tma) {
-        if (lane == 0) bar_arrive_expect_tx(full, 64 * 256);
+        if (lane == 0) bar_arrive_expect_tx(full, kWarpRows * D * 2);
         else bar_arrive(full);
         __syncwarp();
-        // the lane that holds the first row of a box issues its two panels
+        // the lane that holds the first row of a box issues its panels
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int row = half * 32 + lane;                       // row within this warp's 64
+        for (int half = 0; half < kHalves; ++half) {
+          const int row = half * 32 + lane;                       // row within this warp's share
           if ((row & (p.tma_rows - 1)) == 0) {
-            const uint32_t at = dst + (lwarp * 64 + row) * 128;
-            tma_load_box(at, map, 0, head_row + slot[half], full);
-            tma_load_box(at + kPanelBytes, map, 64, head_row + slot[half], full);
+            const uint32_t at = dst + (lwarp * kWarpRows + row) * 128;
+#pragma unroll
+            for (int panel = 0; panel < G_::kPanels; ++panel)
+              tma_load_box(at + panel * kKvPanelBytes, map, panel * 64, head_row + slot[half], full);
           }
         }
       } else {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < kHalves; ++half) {
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int rr = 2 * i + (lane >> 4), c = lane & 15;
+          for (int i = 0; i < kChunks; ++i) {                     // 32 rows x kChunks chunks over 32 lanes
+            const int at = i * 32 + lane, rr = at / kChunks, c = at & (kChunks - 1);
             const int s = __shfl_sync(0xffffffffu, slot[half], rr);
-            cp_async_16(dst + tile_off(lwarp * 64 + half * 32 + rr, c), base + (int64_t)(s < 0 ? 0 : s) * kTile + c * 8,
-                        s < 0 ? 0 : 16);
+            cp_async_16(dst + tile_off(lwarp * kWarpRows + half * 32 + rr, c, kKvPanelBytes),
+                        base + (int64_t)(s < 0 ? 0 : s) * D + c * 8, s < 0 ? 0 : 16);
           }
         }
         bar_arrive_on_copies(full);
@@ -422,24 +458,25 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     // Operand descriptors are built once; a k-step or a ring stage only moves the 14-bit address field (units of
     // 16 bytes) in the lower half, so the issue loop is one 32-bit add per operand and the MMA itself.
     const uint64_t q_desc = umma_desc(q_addr, 16, 1024), k_desc = umma_desc(k_base, 16, 1024);
-    const uint64_t v_desc = umma_desc(v_base, kPanelBytes, 1024);
+    const uint64_t v_desc = umma_desc(v_base, kKvPanelBytes, 1024);
     const uint32_t q_lo = (uint32_t)q_desc, k_lo = (uint32_t)k_desc, v_lo = (uint32_t)v_desc;
     const uint32_t qk_hi = (uint32_t)(q_desc >> 32), v_hi = (uint32_t)(v_desc >> 32);      // K's upper half equals Q's
-    constexpr uint32_t kStageStep = kTileBytes >> 4;
+    constexpr uint32_t kStageStep = kKvTileBytes >> 4;
     auto issue_qk = [&](int t, int stage) {
-      const uint32_t a = q_lo + t * kStageStep, b = k_lo + stage * kStageStep;
+      const uint32_t a = q_lo + t * (kQTileBytes >> 4), b = k_lo + stage * kStageStep;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {                    // 16 elements of head_dim per step
-        const uint32_t step = ((k >> 2) * kPanelBytes + (k & 3) * 32) >> 4;
-        umma_bf16_ss_split(tmem + t * kTile, a + step, qk_hi, b + step, qk_hi, kIdescQK, k > 0 ? 1u : 0u);
+      for (int k = 0; k < D / 16; ++k) {               // 16 elements of head_dim per step
+        const uint32_t a_step = ((k >> 2) * kQPanelBytes + (k & 3) * 32) >> 4;
+        const uint32_t b_step = ((k >> 2) * kKvPanelBytes + (k & 3) * 32) >> 4;
+        umma_bf16_ss_split(tmem + t * 128, a + a_step, qk_hi, b + b_step, qk_hi, G_::kIdescQK, k > 0 ? 1u : 0u);
       }
       umma_commit(&sh->s_full[t]);
     };
     auto issue_pv = [&](int t, int j, int stage) {
       const uint32_t b = v_lo + stage * kStageStep;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {                    // 16 tokens per step: 8 columns of P, 16 rows of V
-        umma_bf16_ts_split(tmem + 256 + t * kTile, tmem + t * kTile + k * 8, b + k * (2048 >> 4), v_hi, kIdescPV,
+      for (int k = 0; k < kKv / 16; ++k) {             // 16 tokens per step: 8 columns of P, 16 rows of V
+        umma_bf16_ts_split(tmem + 256 + t * D, tmem + t * 128 + k * 8, b + k * (2048 >> 4), v_hi, G_::kIdescPV,
                            (j > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(&sh->pv_done[t]);
@@ -491,12 +528,12 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
 }
 
-// 2-D view [kv_heads*slots rows, 128 bf16] of one pool half; boxes of 64 columns x box_rows rows.
-bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_rows) {
+// 2-D view [kv_heads*slots rows, head_dim bf16] of one pool half; boxes of 64 columns x box_rows rows.
+bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_rows, int head_dim) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)kTile, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)kTile * 2};
+  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
   const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
@@ -504,7 +541,39 @@ bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_row
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr int kSmemBytes = (2 + kKStages + kVStages) * kTileBytes + 3072;   // 227 KiB: the whole opt-in shared memory of an SM
+template <int D>
+int launch_prefill(PrefillParams& p, int64_t n_work, int page_tokens, cudaStream_t stream) {
+  static std::atomic<bool> configured[64];
+  const int ready = opt_in_shared_memory(paged_prefill_tc_kernel<D>, Geo<D>::kSmemBytes, configured);
+  if (ready != GK_OK) return ready;
+  {
+    // Never launch if the register pool of this build cannot satisfy the budgets (the kernel would hang).
+    static std::atomic<int> launch_regs{-1};
+    int regs = launch_regs.load(std::memory_order_acquire);
+    if (regs < 0) {
+      cudaFuncAttributes attr;
+      if (cudaFuncGetAttributes(&attr, paged_prefill_tc_kernel<D>) != cudaSuccess) return check_launch();
+      regs = attr.numRegs;
+      launch_regs.store(regs, std::memory_order_release);
+    }
+    if (regs * kThreads < kSoftmaxThreads * kSoftmaxRegs + 128 * kLoaderRegs + 128 * kIssueRegs) return GK_ERR_UNSUPPORTED;
+  }
+  // TMA boxes need slot-contiguous pages of at least 8 tokens and 32-bit row coordinates; a box is at most
+  // the rows one loader warp stages.
+  alignas(64) CUtensorMap map_k, map_v;
+  memset(&map_k, 0, sizeof(map_k));
+  memset(&map_v, 0, sizeof(map_v));
+  constexpr int kWarpRows = Geo<D>::kKv / 2;
+  const int box_rows = page_tokens < kWarpRows ? page_tokens : kWarpRows;
+  const int64_t pool_rows = (int64_t)p.kv_heads * p.slots;
+  if (page_tokens >= 8 && pool_rows < 0x7fffffffLL && make_pool_map(&map_k, p.pool_k, pool_rows, box_rows, D) &&
+      make_pool_map(&map_v, p.pool_v, pool_rows, box_rows, D))
+    p.tma_rows = box_rows;
+  const int64_t ctas = n_work * p.kv_heads * (Geo<D>::kTiles == 2 ? 1 : 2);
+  if (ctas > 0x7fffffffLL) return GK_ERR_UNSUPPORTED;
+  paged_prefill_tc_kernel<D><<<(unsigned)ctas, kThreads, Geo<D>::kSmemBytes, stream>>>(p, map_k, map_v);
+  return check_launch();
+}
 
 }  // namespace
 }  // namespace gk
@@ -524,7 +593,7 @@ extern "C" int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_strid
       table_entry_stride <= 0 || page_tokens <= 0 || (page_tokens & (page_tokens - 1)) || q_heads <= 0 || kv_heads <= 0 ||
       !(scale > 0.f) || !(softcap >= 0.f) || (window != -1 && window <= 0))
     return GK_ERR_INVALID_ARGUMENT;
-  if (head_dim != 128 || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS ||
+  if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || q_heads % kv_heads != 0 || q_heads / kv_heads > GK_PREFILL_TILE_ROWS ||
       n_work * kv_heads > 0x7fffffffLL)
     return GK_ERR_UNSUPPORTED;
   if (((reinterpret_cast<uintptr_t>(pool_k) | reinterpret_cast<uintptr_t>(pool_v) | reinterpret_cast<uintptr_t>(work)) & 15) ||
@@ -552,34 +621,10 @@ extern "C" int gk_paged_prefill_tc_multi_bf16(const void* q, int64_t q_row_strid
   p.q_heads = q_heads;
   p.kv_heads = kv_heads;
   p.group = q_heads / kv_heads;
-  static std::atomic<bool> configured[64];
-  const int ready = gk::opt_in_shared_memory(gk::paged_prefill_tc_kernel, gk::kSmemBytes, configured);
-  if (ready != GK_OK) return ready;
-  {
-    // Never launch if the register pool of this build cannot satisfy the budgets (the kernel would hang).
-    static std::atomic<int> launch_regs{-1};
-    int regs = launch_regs.load(std::memory_order_acquire);
-    if (regs < 0) {
-      cudaFuncAttributes attr;
-      if (cudaFuncGetAttributes(&attr, gk::paged_prefill_tc_kernel) != cudaSuccess) return gk::check_launch();
-      regs = attr.numRegs;
-      launch_regs.store(regs, std::memory_order_release);
-    }
-    if (regs * gk::kThreads < gk::kSoftmaxThreads * gk::kSoftmaxRegs + 128 * gk::kLoaderRegs + 128 * gk::kIssueRegs)
-      return GK_ERR_UNSUPPORTED;
-  }
-  // TMA boxes need slot-contiguous pages of at least 8 tokens and 32-bit row coordinates.
-  alignas(64) CUtensorMap map_k, map_v;
-  memset(&map_k, 0, sizeof(map_k));
-  memset(&map_v, 0, sizeof(map_v));
-  const int box_rows = page_tokens < 64 ? page_tokens : 64;
-  const int64_t pool_rows = (int64_t)kv_heads * slots;
-  if (page_tokens >= 8 && pool_rows < 0x7fffffffLL && gk::make_pool_map(&map_k, pool_k, pool_rows, box_rows) &&
-      gk::make_pool_map(&map_v, pool_v, pool_rows, box_rows))
-    p.tma_rows = box_rows;
-  gk::paged_prefill_tc_kernel<<<(unsigned)(n_work * kv_heads), gk::kThreads, gk::kSmemBytes,
-                                reinterpret_cast<cudaStream_t>(stream)>>>(p, map_k, map_v);
-  return gk::check_launch();
+  cudaStream_t at = reinterpret_cast<cudaStream_t>(stream);
+  if (head_dim == 64) return gk::launch_prefill<64>(p, n_work, page_tokens, at);
+  if (head_dim == 256) return gk::launch_prefill<256>(p, n_work, page_tokens, at);
+  return gk::launch_prefill<128>(p, n_work, page_tokens, at);
 }
 
 extern "C" int gk_paged_prefill_tc_bf16(const void* q, int64_t q_row_stride, const void* pool_k, const void* pool_v,

@@ -424,11 +424,11 @@ class PagedMetadata : public torch::CustomClassHolder {
     const int sm_count = at::cuda::getDeviceProperties(device.index())->multiProcessorCount;
     const int64_t n_seq = static_cast<int64_t>(sequences_.size() / 4);
     const int window = static_cast<int>(sliding_window);
-    // Multi-row sequences go to the tensor-core prefill kernel (head_dim 128 only), the rest --
-    // decode rows and very short chunks -- to the split-KV decode kernel.
+    // Multi-row sequences go to the tensor-core prefill kernel, the rest -- decode rows and very
+    // short chunks -- to the split-KV decode kernel.
     int64_t n_prefill = 0, n_rest = n_seq;
     std::vector<int32_t> rest(sequences_);
-    const bool tensor_core = head_dim == 128 && prefill_min_rows_ >= 0;
+    const bool tensor_core = prefill_min_rows_ >= 0;
     if (tensor_core)
       check_status(gk_prefill_plan_build(sequences_.data(), n_seq, (int)query_heads, (int)kv_heads, window,
                                          prefill_min_rows_, nullptr, 0, &n_prefill, rest.data(), &n_rest),

@@ -166,7 +166,9 @@ GK_API int gk_paged_attn_combine_bf16(const float* part_ml, const float* part_o,
  * record; Q K^T and P V as tcgen05 UMMA contractions with fp32 accumulators in tensor memory (P is
  * the A operand straight from tensor memory), online softmax between them, causal inside the
  * chunk.  Same arithmetic contract as gk_paged_attn_bf16 (P rounded to bf16 before P V, fp32
- * accumulation, out = bf16(O / l)).  head_dim must be 128.
+ * accumulation, out = bf16(O / l)).  head_dim in {64, 128, 256}, the geometries of
+ * tests/paged_attention_generalized_smoke.py:59-65; at 256 the two query tiles of a record run in
+ * two CTAs against 64-key tiles (the accumulators of two tiles would not fit in tensor memory).
  *
  * gk_prefill_plan_build splits a step's sequences: those with at least min_rows rows
  * (0 = default, ceil(32 / (q_heads/kv_heads)) but at least 2) become tensor-core work records

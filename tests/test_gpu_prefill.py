@@ -65,7 +65,8 @@ def run_case(seqs, q_heads, kv_heads, page, seed, softcap=0.0, window=-1, min_ro
     ref32 = oracle.attend_fp32_softmax(*args, softcap=softcap, window=window)
     oracle.fp32_softmax_gate(got, ref32)
     oracle.isolated_errors(got, oracle.attend_fp64_rounded(*args, softcap=softcap, window=window),
-                           oracle.tiled_bf16_pv(*args, kv_tile=oracle.KV_TILE, softcap=softcap, window=window))
+                           oracle.tiled_bf16_pv(*args, kv_tile=64 if d == 256 else oracle.KV_TILE, softcap=softcap,
+                                                window=window))
     return len(work), len(rest)
 
 
@@ -99,6 +100,20 @@ def test_ragged_tile_boundaries():
 def test_softcap_and_sliding_window():
     run_case([(0, 200), (500, 64)], 8, 2, 128, seed=5, softcap=30.0, window=96)
     run_case([(37, 150)], 4, 1, 8, seed=6, window=64)
+
+
+@pytest.mark.parametrize("d", [64, 256])
+def test_other_head_dims(d):
+    """head_dim 64 (two query tiles per CTA, 64-column accumulators) and 256 (one query tile per CTA, KV tiles
+    of 64 tokens): whole pages by TMA and token-granular tables, grouped heads, records of one and two query
+    tiles, ragged ends, softcap and window."""
+    seqs = [(0, 70), (300, 129), (1000, 33), (127, 1), (640, 2), (64, 64)]
+    for page in (128, 16, 1):
+        n_tc, n_rest = run_case(seqs, 8, 2, page, seed=d + page, d=d)
+        assert n_tc > 0 and n_rest >= 1
+    run_case([(0, 257), (129, 130)], 4, 4, 32, seed=d + 7, min_rows=1, d=d)
+    run_case([(0, 200), (500, 64)], 16, 2, 128, seed=d + 9, softcap=30.0, window=96, d=d)
+    run_case([(37, 150)], 4, 1, 8, seed=d + 11, window=64, d=d)
 
 
 def test_config4_shape_scaled_down():
