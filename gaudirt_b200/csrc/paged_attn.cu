@@ -5,11 +5,19 @@
 // All query heads of the KV head's GQA group -- times the rows of the block -- are packed into
 // the 16 rows of an m16n8k16 tile, so every K/V byte is read from HBM once per work item.
 // The KV range is cut into 16-token groups dealt round-robin to the warps; each warp owns a
-// private cp.async ring (16-byte copies, L1 bypass) and never meets a block-wide barrier until
-// the final cross-warp merge.  Slots are looked up in the kernel from the slot table, so there
-// is no gather-index buffer and no gathered K/V copy as in the reference
-// (src/bridge/attention_plan.cpp:246-255, src/bridge/paged_attention.cpp:89-100).
-#include "gk_common.cuh"
+// private ring of staged groups, each stage with its own mbarrier, and never meets a block-wide
+// barrier until the final cross-warp merge.  A group that is 16 slot-contiguous tokens of one page
+// (any page of at least 16 tokens) is fetched by one lane as ONE 4-D TMA box (cp.async.bulk.tensor:
+// K and V, every 64-column panel, 16 rows, 128-byte swizzle, no multicast); any other group -- token-granular tables, ragged
+// ends, ranges that do not start on a 16-token boundary -- row by row with 16-byte cp.async into the
+// same layout (rows past the range zero-filled).  The slot of a group is looked up one iteration
+// before its copies are issued, so the table read is never waited for.  Slots come from the slot
+// table in the kernel, so there is no gather-index buffer and no gathered K/V copy as in the
+// reference (src/bridge/attention_plan.cpp:246-255, src/bridge/paged_attention.cpp:89-100).
+#include "tc_common.cuh"
+
+#include <stdlib.h>
+#include <string.h>
 
 #include <math_constants.h>
 
@@ -43,25 +51,36 @@ struct AttnParams {
   int64_t part_capacity;                 // entries part_ml / part_o hold; a record that points past it is skipped
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group, n_out;
+  int tma;                               // whole groups may be fetched through the tensor maps
 };
 
 template <int D, int WARPS, int STAGES>
 struct AttnConfig {
   static constexpr int kRowBytes = D * 2;
   static constexpr int kChunks = D / 8;                         // 16-byte chunks per row
-  static constexpr int kTileBytes = kGroupTokens * kRowBytes;   // K (or V) of one group
+  static constexpr int kTileBytes = kGroupTokens * kRowBytes;   // K (or V) of one group: D/64 panels
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kWarpBytes = STAGES * kStageBytes;
-  static constexpr int kSmemBytes = WARPS * kWarpBytes;
+  static constexpr int kRingBytes = WARPS * kWarpBytes;
+  static constexpr int kSmemBytes = kRingBytes + 128;           // + one mbarrier per warp and stage, the abort flag
+  static_assert(WARPS * STAGES * 8 + 4 <= 128, "barrier area");
   static constexpr int kMergeStride = D + 8;                    // floats per merged row
   static_assert(STAGES >= 3, "the merge buffers reuse the ring and need three stages of room");
   static_assert(kWarpBytes >= (GK_MAX_PACKED_ROWS * kMergeStride + 2 * GK_MAX_PACKED_ROWS) * 4, "merge area");
 };
 
-template <int D, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnParams p) {
+// Byte offset of 16-byte chunk `chunk` of token `row` in a staged K or V tile: panels of 64 columns,
+// rows 128 bytes apart, chunks exchanged by the 128-byte swizzle (what a TMA box writes; conflict-free
+// for ldmatrix).
+__device__ __forceinline__ uint32_t group_off(int row, int chunk) {
+  return (chunk >> 3) * (kGroupTokens * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+template <int D, int WARPS, int STAGES, bool TMA>
+__global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnParams p,
+                                                                   const __grid_constant__ CUtensorMap map_kv) {
   using C = AttnConfig<D, WARPS, STAGES>;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];     // swizzle atoms of the TMA boxes are 1 KiB
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
@@ -136,6 +155,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
           atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
         }
       }
+      asm volatile("fence.proxy.async;\n" ::: "memory");   // the rows may come back through a TMA box
       __threadfence_block();
       __syncthreads();                                  // uniform per CTA: the range is the CTA's
     }
@@ -144,20 +164,60 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       p.table + (int64_t)(p.table_rows ? __ldg(p.table_rows + table_row) : table_row) * p.table_stride;
   const int page_mask = (1 << p.page_shift) - 1;
 
-  // Asynchronously stage the K and V rows of 16-token group `gi` into ring stage `stage`.
-  // Lanes 0..15 resolve one token each; rows past the range are zero-filled so that a masked
-  // probability of 0 never multiplies stale shared memory.
-  auto stage_group = [&](int gi, int stage) {
-    const int tok = kv_begin + gi * kGroupTokens + (lane & 15);
-    int slot = -1;
-    if (tok < kv_end) {
-      slot = __ldg(trow + (int64_t)(tok >> p.page_shift) * p.entry_stride) + (tok & page_mask);
-      if ((unsigned)slot >= (unsigned)p.slots) {
-        if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
-        slot = -1;
-      }
+  // TMA form: one mbarrier per ring stage, private to the warp, one arrival per fill.
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kRingBytes) + warp * STAGES;
+  int* abort_flag = reinterpret_cast<int*>(smem + C::kRingBytes + WARPS * STAGES * 8);
+  if (TMA) {
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) bar_init(&bars[s], 1);
+      if (warp == 0) *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+  }
+  const int head_row = head * (int)p.slots;
+  const bool swizzle_ok = (smem_u32(smem) & 1023) == 0;     // a box lands where group_off expects it
+
+  // Table entry of this lane's token (lanes 0..15 and 16..31 alike) of the warp's local group `local`.
+  // The loaded value is not touched here -- not even by an add, which would wait for the load: it is
+  // issued one iteration before stage_group turns it into a slot.
+  auto lookup = [&](int local) -> int {
+    const int tok = kv_begin + (warp + local * WARPS) * kGroupTokens + (lane & 15);
+    const int32_t* entry = trow + (int64_t)(tok >> p.page_shift) * p.entry_stride;
+    int raw;
+    asm volatile("{\n.reg .pred p;\nsetp.ne.s32 p, %2, 0;\nmov.s32 %0, 0;\n@p ld.global.nc.s32 %0, [%1];\n}\n"
+                 : "=&r"(raw)
+                 : "l"(entry), "r"((int)(local < my_groups && tok < kv_end)));
+    return raw;
+  };
+  // Asynchronously stage the K and V rows of the warp's local group `local` into ring stage `stage`;
+  // `raw` is lookup(local).  Rows past the range are zero-filled so that a masked probability of 0 never
+  // multiplies stale shared memory.  TMA form: a whole group inside one page is ONE box issued by lane 0
+  // (completion by transaction bytes); the rare other group (a ragged end, a range that does not start on
+  // a 16-token boundary) is copied row by row and waited for on the spot.  Plain form: row by row, one
+  // cp.async group per call (committed by the caller).
+  auto stage_group = [&](int local, int stage, int raw) {
+    const int tok0 = kv_begin + (warp + local * WARPS) * kGroupTokens;
+    const int tok = tok0 + (lane & 15);
+    int slot = tok < kv_end ? raw + (tok & page_mask) : -1;
+    if (slot != -1 && (unsigned)slot >= (unsigned)p.slots) {         // a table entry outside the pool
+      if (p.status) atomicOr(p.status, (int)GK_DEV_BAD_TABLE);
+      slot = -1;
     }
     const uint32_t dst_k = ring + stage * C::kStageBytes, dst_v = dst_k + C::kTileBytes;
+    if (TMA) {
+      const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
+      const bool boxed = swizzle_ok && (tok0 & (kGroupTokens - 1)) == 0 && tok0 + kGroupTokens <= kv_end && slot0 >= 0 &&
+                         (int64_t)slot0 + kGroupTokens <= p.slots;
+      if (boxed) {
+        if (lane == 0) {                              // K and V, all panels: one box (see make_kv_group_map)
+          bar_arrive_expect_tx(&bars[stage], 2 * C::kTileBytes);
+          tma_load_kv_group(dst_k, &map_kv, head_row + slot0, &bars[stage]);
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < kGroupTokens * C::kChunks / 32; ++j) {
       const int c = j * 32 + lane;
@@ -165,9 +225,14 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       const int s = __shfl_sync(0xffffffffu, slot, row);
       const int64_t src = (int64_t)(s < 0 ? 0 : s) * D + col * 8;
       const int bytes = s < 0 ? 0 : 16;
-      const uint32_t off = row * C::kRowBytes + (((col & ~7) | ((col ^ row) & 7)) << 4);
+      const uint32_t off = group_off(row, col);
       cp_async_16(dst_k + off, kbase + src, bytes);
       cp_async_16(dst_v + off, vbase + src, bytes);
+    }
+    if (TMA) {
+      asm volatile("cp.async.wait_all;\n" ::: "memory");   // these copies belong to no committed group
+      __syncwarp();
+      if (lane == 0) bar_arrive(&bars[stage]);
     }
   };
 
@@ -180,21 +245,43 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
   const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
   const bool upper = mv > 8;
 
+  int raw_next;
+  {
+    int first[STAGES - 1];
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < my_groups) stage_group(warp + s * WARPS, s);
-    cp_async_commit();
+    for (int s = 0; s < STAGES - 1; ++s) first[s] = lookup(s);
+    raw_next = lookup(STAGES - 1);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < my_groups) stage_group(s, s, first[s]);
+      if (!TMA) cp_async_commit();
+    }
   }
 
+  bool alive = true;
+  int stage = 0, fill = STAGES - 1;                    // ring positions of group i and of group i + STAGES - 1
+  uint32_t parity = 0;
   for (int i = 0; i < my_groups; ++i) {
-    cp_async_wait<STAGES - 2>();
+    if (!TMA) cp_async_wait<STAGES - 2>();
+    // the stage about to be refilled is the one group i - 1 was read from: those reads are complete
+    // (their consumers have been issued) once every lane is here
     __syncwarp();
-    {
-      const int nxt = i + STAGES - 1;
-      if (nxt < my_groups) stage_group(warp + nxt * WARPS, nxt % STAGES);
-      cp_async_commit();
+    if (i + STAGES - 1 < my_groups) stage_group(i + STAGES - 1, fill, raw_next);
+    if (!TMA) cp_async_commit();
+    raw_next = lookup(i + STAGES);
+    if (++fill == STAGES) fill = 0;
+    if (TMA) {
+      // usually the box has landed: one try, one vote; the bounded wait only otherwise
+      uint32_t landed;
+      asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
+                   : "=r"(landed)
+                   : "r"(smem_u32(&bars[stage])), "r"(parity)
+                   : "memory");
+      if (!__all_sync(0xffffffffu, landed)) {
+        alive = __all_sync(0xffffffffu, bar_wait(&bars[stage], parity, abort_flag));
+        if (!alive) break;
+      }
     }
-    const int stage = i % STAGES;
     const uint32_t ks_base = ring + stage * C::kStageBytes, vs_base = ks_base + C::kTileBytes;
 
     // ---- S = Q K^T for 16 keys: two n-tiles of 8 keys -----------------------------------
@@ -207,7 +294,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       for (int nt = 0; nt < 2; ++nt) {
         const int row = nt * 8 + (lane & 7), chunk = kp * 4 + (lane >> 3);
         uint32_t b[4];
-        ldmatrix_x4(b, ks_base + row * C::kRowBytes + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+        ldmatrix_x4(b, ks_base + group_off(row, chunk));
         mma_bf16_16816(sc[nt], qf[2 * kp], b[0], b[1]);
         mma_bf16_16816(sc[nt], qf[2 * kp + 1], b[2], b[3]);
       }
@@ -270,12 +357,14 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
       pr[1][3] = fast_exp2(sc[1][3] - mu1);
       l1 = l1 * a1 + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
     }
+    if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {       // the running maxima seldom move: skip the no-op
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      o[n][0] *= a0;
-      o[n][1] *= a0;
-      o[n][2] *= a1;
-      o[n][3] *= a1;
+      for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= a0;
+        o[n][1] *= a0;
+        o[n][2] *= a1;
+        o[n][3] *= a1;
+      }
     }
 
     // ---- O += P V, P rounded to bf16 (the reference's boundary before the second product) --
@@ -288,12 +377,17 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
     for (int np = 0; np < D / 16; ++np) {
       const int row = ((lane >> 3) & 1) * 8 + (lane & 7), chunk = np * 2 + (lane >> 4);
       uint32_t b[4];
-      ldmatrix_x4_trans(b, vs_base + row * C::kRowBytes + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+      ldmatrix_x4_trans(b, vs_base + group_off(row, chunk));
       mma_bf16_16816(o[2 * np], pa, b[0], b[1]);
       mma_bf16_16816(o[2 * np + 1], pa, b[2], b[3]);
     }
+    if (++stage == STAGES) {
+      stage = 0;
+      parity ^= 1u;
+    }
   }
-  cp_async_wait<0>();
+  asm volatile("cp.async.wait_all;\n" ::: "memory");
+  if (!alive && lane == 0 && p.status) atomicOr(p.status, (int)GK_DEV_WAIT_EXPIRED);
 
   // ---- merge the warps' partial states through the (now idle) rings ----------------------
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -501,16 +595,44 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
 constexpr int kWarps = 4;
 constexpr int kStages = 3;
 
-template <int D>
-int launch_attn(const AttnParams& p, int64_t n_work, cudaStream_t stream) {
+template <int D, bool TMA>
+int launch_attn_form(const AttnParams& p, const CUtensorMap& map_kv, int64_t n_work, cudaStream_t stream) {
   using C = AttnConfig<D, kWarps, kStages>;
-  auto kernel = paged_attn_kernel<D, kWarps, kStages>;
+  auto kernel = paged_attn_kernel<D, kWarps, kStages, TMA>;
   static std::atomic<bool> configured[64];
   const int ready = opt_in_shared_memory(kernel, C::kSmemBytes, configured);
   if (ready != GK_OK) return ready;
   const int64_t blocks = n_work * p.kv_heads;
-  kernel<<<(unsigned)blocks, kWarps * 32, C::kSmemBytes, stream>>>(p);
+  kernel<<<(unsigned)blocks, kWarps * 32, C::kSmemBytes, stream>>>(p, map_kv);
   return check_launch();
+}
+
+inline int sm_count_of_current_device() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+template <int D>
+int launch_attn(AttnParams& p, int64_t n_work, int page_tokens, cudaStream_t stream) {
+  // One box per 16-token group needs pages of at least 16 slot-contiguous tokens, 32-bit row coordinates and
+  // the V half at a positive 16-byte-aligned distance after the K half; without them (or without the driver's
+  // encoder) the plain form copies every group row by row.
+  alignas(64) CUtensorMap map_kv;
+  memset(&map_kv, 0, sizeof(map_kv));
+  const int64_t pool_rows = (int64_t)p.kv_heads * p.slots;
+  const int64_t v_minus_k = reinterpret_cast<const char*>(p.pool_v) - reinterpret_cast<const char*>(p.pool_k);
+  const char* form = getenv("GK_DEBUG_ATTN_FORM");
+  const bool small = n_work * p.kv_heads <= 2 * sm_count_of_current_device();
+  p.tma = page_tokens >= kGroupTokens && pool_rows < 0x7fffffffLL && (form ? form[0] == 't' : small) &&
+          make_kv_group_map(&map_kv, p.pool_k, v_minus_k, pool_rows, kGroupTokens, D);
+  return p.tma ? launch_attn_form<D, true>(p, map_kv, n_work, stream) : launch_attn_form<D, false>(p, map_kv, n_work, stream);
 }
 
 // Argument checks + launch of the attention kernel.  `part_capacity` is the number of entries the
@@ -582,9 +704,9 @@ int attn_entry(const void* q, int64_t q_row_stride, const void* pool_k, const vo
   p.group = q_heads / kv_heads;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (head_dim) {
-    case 64: return launch_attn<64>(p, n_work, s);
-    case 128: return launch_attn<128>(p, n_work, s);
-    default: return launch_attn<256>(p, n_work, s);
+    case 64: return launch_attn<64>(p, n_work, page_tokens, s);
+    case 128: return launch_attn<128>(p, n_work, page_tokens, s);
+    default: return launch_attn<256>(p, n_work, page_tokens, s);
   }
 }
 

@@ -528,19 +528,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
 }
 
-// 2-D view [kv_heads*slots rows, head_dim bf16] of one pool half; boxes of 64 columns x box_rows rows.
-bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_rows, int head_dim) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D>
 int launch_prefill(PrefillParams& p, int64_t n_work, int page_tokens, cudaStream_t stream) {
   static std::atomic<bool> configured[64];

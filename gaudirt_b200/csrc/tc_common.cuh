@@ -6,6 +6,7 @@
 #include "gk_common.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace gk {
 
@@ -141,5 +142,48 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// 2-D view [kv_heads*slots rows, head_dim bf16] of one half of a head-major KV pool; boxes of 64 columns (one
+// 128-byte swizzled panel) x box_rows rows.
+inline bool make_pool_map(CUtensorMap* map, const void* pool, int64_t rows, int box_rows, int head_dim) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// One 4-D TMA box into shared memory; only the row coordinate moves (see make_kv_group_map).
+__device__ __forceinline__ void tma_load_kv_group(uint32_t dst, const CUtensorMap* map, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %3, %3}], [%2];\n" ::"r"(dst),
+      "l"(map), "r"(smem_u32(bar)), "r"(0), "r"(row)
+      : "memory");
+}
+
+// 4-D view of a head-major KV pool whose K and V halves are `v_minus_k` bytes apart, for fetching K AND V
+// of `box_rows` consecutive slots of one head with a single box: dimensions (64 columns of a panel, rows =
+// kv_heads*slots, head_dim/64 panels, K|V), so the box lands as [K|V][panel][row][128 bytes], each panel
+// swizzled by 128 bytes.
+inline bool make_kv_group_map(CUtensorMap* map, const void* pool_k, int64_t v_minus_k, int64_t rows, int box_rows,
+                              int head_dim) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || v_minus_k <= 0 || (v_minus_k & 15) || v_minus_k >= ((int64_t)1 << 40)) return false;
+  const cuuint64_t dims[4] = {64, (cuuint64_t)rows, (cuuint64_t)(head_dim / 64), 2};
+  const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)v_minus_k};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(head_dim / 64), 2};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const char* promo_env = getenv("GK_DEBUG_PROMO");
+  const CUtensorMapL2promotion promo = !promo_env ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                       : promo_env[0] == '0' ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                       : promo_env[0] == '1' ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                             : CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool_k), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 }  // namespace gk
