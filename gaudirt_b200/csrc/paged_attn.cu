@@ -16,7 +16,6 @@
 // reference (src/bridge/attention_plan.cpp:246-255, src/bridge/paged_attention.cpp:89-100).
 #include "tc_common.cuh"
 
-#include <stdlib.h>
 #include <string.h>
 
 #include <math_constants.h>
@@ -607,6 +606,8 @@ int launch_attn_form(const AttnParams& p, const CUtensorMap& map_kv, int64_t n_w
   return check_launch();
 }
 
+std::atomic<int> attention_form{GK_ATTENTION_FORM_AUTO};
+
 inline int sm_count_of_current_device() {
   static std::atomic<int> cached[64];
   int dev = 0;
@@ -628,9 +629,12 @@ int launch_attn(AttnParams& p, int64_t n_work, int page_tokens, cudaStream_t str
   memset(&map_kv, 0, sizeof(map_kv));
   const int64_t pool_rows = (int64_t)p.kv_heads * p.slots;
   const int64_t v_minus_k = reinterpret_cast<const char*>(p.pool_v) - reinterpret_cast<const char*>(p.pool_k);
-  const char* form = getenv("GK_DEBUG_ATTN_FORM");
-  const bool small = n_work * p.kv_heads <= 2 * sm_count_of_current_device();
-  p.tma = page_tokens >= kGroupTokens && pool_rows < 0x7fffffffLL && (form ? form[0] == 't' : small) &&
+  // Measured: the box form is 4 % faster per CTA while the grid leaves resident slots idle (the copies cost
+  // one instruction instead of sixteen), the row form 1 % faster once the grid saturates the memory system.
+  const int form = attention_form.load(std::memory_order_relaxed);
+  const bool boxes = form == GK_ATTENTION_FORM_AUTO ? n_work * p.kv_heads <= 2 * sm_count_of_current_device()
+                                                    : form == GK_ATTENTION_FORM_BOXES;
+  p.tma = boxes && page_tokens >= kGroupTokens && pool_rows < 0x7fffffffLL &&
           make_kv_group_map(&map_kv, p.pool_k, v_minus_k, pool_rows, kGroupTokens, D);
   return p.tma ? launch_attn_form<D, true>(p, map_kv, n_work, stream) : launch_attn_form<D, false>(p, map_kv, n_work, stream);
 }
@@ -879,4 +883,11 @@ extern "C" int gk_paged_attn_static_scratch_bf16(const void* q, int64_t q_row_st
   if (rc != GK_OK) return rc;
   return gk::combine_entry(part_ml, part_o, partial_entries, combine, n_combine, outs, 1, out_row_stride, q_heads,
                            head_dim, status, stream);
+}
+
+extern "C" int gk_set_attention_form(int form) {
+  if (form != GK_ATTENTION_FORM_AUTO && form != GK_ATTENTION_FORM_ROWS && form != GK_ATTENTION_FORM_BOXES)
+    return GK_ERR_INVALID_ARGUMENT;
+  gk::attention_form.store(form, std::memory_order_relaxed);
+  return GK_OK;
 }

@@ -6,7 +6,6 @@
 #include "gk_common.cuh"
 
 #include <cuda.h>
-#include <stdlib.h>
 
 namespace gk {
 
@@ -176,13 +175,8 @@ inline bool make_kv_group_map(CUtensorMap* map, const void* pool_k, int64_t v_mi
   const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)v_minus_k};
   const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(head_dim / 64), 2};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
-  const char* promo_env = getenv("GK_DEBUG_PROMO");
-  const CUtensorMapL2promotion promo = !promo_env ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-                                       : promo_env[0] == '0' ? CU_TENSOR_MAP_L2_PROMOTION_NONE
-                                       : promo_env[0] == '1' ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                                                             : CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool_k), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -151,6 +151,18 @@ GK_API int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* p
                        float* part_o, float scale, float softcap, int window, int q_heads,
                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream);
 
+/* How the attention kernel brings a 16-token group of K and V into shared memory.  BOXES: one
+ * cp.async.bulk.tensor box per group (K and V, all columns; needs pages of at least 16 tokens, groups
+ * that do not qualify -- ragged ends, ranges starting off a 16-token boundary -- are copied row by row).
+ * ROWS: 16-byte cp.async copies for every group (the only form for token-granular tables).  AUTO (the
+ * default) takes BOXES for launches of at most two CTAs per SM and ROWS otherwise, which is where each
+ * measured faster.  Both forms produce the same bits.  Process-wide; not part of the reference, which has
+ * no such choice (its gather runs in a separate index kernel, src/bridge/attention_plan.cpp:246-255). */
+#define GK_ATTENTION_FORM_AUTO 0
+#define GK_ATTENTION_FORM_ROWS 1
+#define GK_ATTENTION_FORM_BOXES 2
+GK_API int gk_set_attention_form(int form);
+
 /* Replaces gk_attn_online_merge_f32_v1 + gk_attn_online_finalize_bf16_v1
  * (src/bridge/paged_attention_tiles.cpp:173-188): merges the n_splits partial states of every
  * combine record in split order (deterministic) and writes bf16(O / l); l == 0 gives 0. */

@@ -145,6 +145,36 @@ def test_decode_edge_lengths(q_heads, kv_heads, d):
         oracle_gates(out, args, tile=64)
 
 
+@pytest.fixture
+def attention_form():
+    from gaudirt_b200 import abi
+    lib = abi.lib()
+    yield lambda form: abi.check(lib.gk_set_attention_form(form), "gk_set_attention_form")
+    lib.gk_set_attention_form(0)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,d", [(8, 2, 64), (32, 8, 128), (8, 1, 256)])
+def test_box_and_row_forms_give_the_same_bits(attention_form, q_heads, kv_heads, d):
+    """The two ways of staging a 16-token group (one TMA box / 16-byte row copies) feed the same arithmetic:
+    same bits, whatever the launch size.  Covers whole groups, ragged ends, ranges of fewer groups than
+    warps, split ranges that leave warps without a group, a window that starts ranges off a 16-token
+    boundary (row copies inside the box form) and pages of exactly one group."""
+    ctx = [1, 7, 16, 17, 49, 64, 113, 287, 519, 1167, 2048]
+    case = cases.decode_case(len(ctx), q_heads, kv_heads, d, 128, 64, ctx, seed=d + q_heads)
+    _, args = oracle_args(case)
+    for page, split, window in ((128, 0, -1), (128, 64, -1), (16, 256, -1), (128, 0, 100), (16, 64, 333)):
+        outs = []
+        for form in (1, 2):            # GK_ATTENTION_FORM_ROWS, GK_ATTENTION_FORM_BOXES
+            attention_form(form)
+            out, _, _ = run_decode(case, page_tokens=page, split_tokens=split, window=window)
+            outs.append(out.cpu())
+        assert torch.equal(bits(outs[0]), bits(outs[1])), (page, split, window)
+        if window < 0:
+            oracle_gates(outs[1], args)
+    with pytest.raises(Exception):
+        attention_form(7)
+
+
 def test_skewed_lengths_with_automatic_split():
     ctx = cases.lognormal_contexts(24, 20261103, median=512, sigma=1.0, lo=16, hi=6000)
     blocks = int(((ctx + 127) // 128).sum()) + 3
