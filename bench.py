@@ -146,6 +146,9 @@ def parse():
                     help="experiments only: on ONE GPU run rank 0's share of an N-way tensor-parallel split (no gather)")
     ap.add_argument("--split-tokens", type=int, default=0,
                     help="experiments only: longest KV range of one work item (0 = chosen by the schedule search)")
+    ap.add_argument("--programmatic-launch", type=int, default=-1, choices=(-1, 0, 1),
+                    help="experiments only: 0 / 1 switch programmatic dependent launch of the kernels off / on "
+                         "(-1 = the library's default)")
     ap.add_argument("--no-tp-configs", action="store_true",
                     help="with N > 1: measure the chosen configuration only, not configs 3 and 5 after it")
     return ap.parse_args()
@@ -852,6 +855,9 @@ def run_b200(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.programmatic_launch >= 0:
+        from gaudirt_b200 import abi
+        abi.check(abi.lib().gk_set_programmatic_launch(args.programmatic_launch), "gk_set_programmatic_launch")
     line = measure(args, args.config, world, rank, dev, headline=True)
     # The tensor-parallel configurations ride along with the default multi-GPU run, so that one scaling
     # sweep of the headline benchmark also carries their curves.

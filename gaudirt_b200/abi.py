@@ -27,6 +27,7 @@ PROTOTYPES = {
                                  i32, i32, i32, vp, vp]),
     "gk_paged_attn_combine_bf16": (i32, [vp, vp, vp, i64, vp, i64, i32, i32, vp]),
     "gk_set_attention_form": (i32, [i32]),
+    "gk_set_programmatic_launch": (i32, [i32]),
     "gk_prefill_plan_build": (i32, [vp, i64, i32, i32, i32, i32, vp, i64, i64p, vp, i64p]),
     "gk_paged_prefill_tc_bf16": (i32, [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, i64, vp, i64, f32, f32, i32,
                                        i32, i32, i32, vp, vp]),

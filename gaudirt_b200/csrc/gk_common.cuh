@@ -40,6 +40,35 @@ inline int opt_in_shared_memory(Kernel kernel, int bytes, std::atomic<bool> (&do
   return GK_OK;
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_after_predecessor may be set up on
+// the GPU while the kernel before it in the stream is still running; its first statement is
+// wait_for_predecessor(), which lets the kernel AFTER it start its own set-up and then blocks until the
+// kernel before it has completed and its writes are visible, so every access of the kernel body is
+// ordered exactly as by plain stream order.  What overlaps is the launch latency and the scheduling of
+// the CTAs, which is most of a decode layer's gap between kernels.  Launched the ordinary way (or with
+// the switch off) both instructions do nothing.
+extern std::atomic<int> g_programmatic_launch;
+
+__device__ __forceinline__ void wait_for_predecessor() {
+  asm volatile("griddepcontrol.launch_dependents;\ngriddepcontrol.wait;\n" ::: "memory");
+}
+
+template <typename... Params, typename... Args>
+inline void launch_after_predecessor(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes,
+                                     cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = g_programmatic_launch.load(std::memory_order_relaxed) ? 1 : 0;
+  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads the error with check_launch()
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

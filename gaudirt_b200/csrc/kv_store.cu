@@ -6,6 +6,10 @@
 
 namespace gk {
 thread_local int g_last_cuda_error = 0;
+#ifndef GK_PROGRAMMATIC_LAUNCH_DEFAULT
+#define GK_PROGRAMMATIC_LAUNCH_DEFAULT 0
+#endif
+std::atomic<int> g_programmatic_launch{GK_PROGRAMMATIC_LAUNCH_DEFAULT};
 
 namespace {
 
@@ -44,6 +48,11 @@ __global__ void __launch_bounds__(256) kv_store_kernel(const unsigned short* __r
 
 }  // namespace
 }  // namespace gk
+
+extern "C" int gk_set_programmatic_launch(int on) {
+  gk::g_programmatic_launch.store(on ? 1 : 0, std::memory_order_relaxed);
+  return GK_OK;
+}
 
 extern "C" int gk_kv_store_head_major_bf16(const void* k, const void* v, int64_t k_row_stride, int64_t v_row_stride,
                                            const int32_t* locations, int64_t rows, void* pool_k, void* pool_v,

@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const unsigned short* __r
                                                        double weight_offset, const PartList parts = PartList{}) {
   static_assert(!PARTS || (VEC == 8 && FUSED), "the rank-sum front exists for the vectorised fused form only");
   __shared__ double partial[8];
+  wait_for_predecessor();
   const int64_t row = blockIdx.x;
   const unsigned short* xr = PARTS ? nullptr : x + row * x_stride;
   const unsigned short* rr = FUSED ? residual + row * r_stride : nullptr;
@@ -310,6 +311,7 @@ __device__ __forceinline__ unsigned short rotate_element(const unsigned short* h
 // One thread per element of q, k (and v when the store is fused).
 template <bool STORE>
 __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
+  wait_for_predecessor();
   const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
   const int64_t per_row = (int64_t)heads * p.head_dim;
   const int64_t total = p.rows * per_row;
@@ -359,6 +361,7 @@ __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
 // (rotary_dim % 16 == 0 for neox pairs, % 8 == 0 for interleaved pairs).
 template <bool STORE>
 __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
+  wait_for_predecessor();
   const int chunks = p.head_dim >> 3;
   const int heads = p.q_heads + p.k_heads + (STORE ? p.k_heads : 0);
   const int per_row = heads * chunks;
@@ -446,9 +449,9 @@ int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
     const int64_t want = (total + 255) / 256;
     const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
     if (store)
-      rotary_vec_kernel<true><<<blocks, 256, 0, stream>>>(p);
+      launch_after_predecessor(rotary_vec_kernel<true>, dim3(blocks), dim3(256), 0, stream, p);
     else
-      rotary_vec_kernel<false><<<blocks, 256, 0, stream>>>(p);
+      launch_after_predecessor(rotary_vec_kernel<false>, dim3(blocks), dim3(256), 0, stream, p);
     return check_launch();
   }
   const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
@@ -456,9 +459,9 @@ int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
   const int64_t want = (total + 255) / 256;
   const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
   if (store)
-    rotary_kernel<true><<<blocks, 256, 0, stream>>>(p);
+    launch_after_predecessor(rotary_kernel<true>, dim3(blocks), dim3(256), 0, stream, p);
   else
-    rotary_kernel<false><<<blocks, 256, 0, stream>>>(p);
+    launch_after_predecessor(rotary_kernel<false>, dim3(blocks), dim3(256), 0, stream, p);
   return check_launch();
 }
 
@@ -494,11 +497,11 @@ static int norm_common(const void* x, const void* residual, const void* weight, 
   const unsigned grid = (unsigned)rows;
   const int h = (int)hidden;
   if (fused) {
-    if (vec) gk::rms_norm_kernel<8, true><<<grid, 256, 0, s>>>(xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset);
-    else gk::rms_norm_kernel<1, true><<<grid, 256, 0, s>>>(xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset);
+    if (vec) gk::launch_after_predecessor(gk::rms_norm_kernel<8, true, false>, dim3(grid), dim3(256), 0, s, xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset, gk::PartList{});
+    else gk::launch_after_predecessor(gk::rms_norm_kernel<1, true, false>, dim3(grid), dim3(256), 0, s, xs, rs, ws, ys, us, x_row_stride, residual_row_stride, h, epsilon, weight_offset, gk::PartList{});
   } else {
-    if (vec) gk::rms_norm_kernel<8, false><<<grid, 256, 0, s>>>(xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset);
-    else gk::rms_norm_kernel<1, false><<<grid, 256, 0, s>>>(xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset);
+    if (vec) gk::launch_after_predecessor(gk::rms_norm_kernel<8, false, false>, dim3(grid), dim3(256), 0, s, xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset, gk::PartList{});
+    else gk::launch_after_predecessor(gk::rms_norm_kernel<1, false, false>, dim3(grid), dim3(256), 0, s, xs, nullptr, ws, ys, nullptr, x_row_stride, 0, h, epsilon, weight_offset, gk::PartList{});
   }
   return gk::check_launch();
 }
@@ -555,7 +558,7 @@ extern "C" int gk_rank_sum_add_rms_norm_bf16(const void* const* parts, int world
   if ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y) |
        reinterpret_cast<uintptr_t>(u)) & 15)
     return GK_ERR_INVALID_ARGUMENT;
-  gk::rms_norm_kernel<8, true, true><<<(unsigned)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  gk::launch_after_predecessor(gk::rms_norm_kernel<8, true, true>, dim3((unsigned)rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       nullptr, static_cast<const unsigned short*>(residual), static_cast<const unsigned short*>(weight),
       static_cast<unsigned short*>(y), static_cast<unsigned short*>(u), part_row_stride, residual_row_stride, (int)hidden,
       (double)epsilon, (double)weight_offset, list);

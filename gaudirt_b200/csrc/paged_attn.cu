@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) paged_attn_kernel(const AttnPar
                                                                    const __grid_constant__ CUtensorMap map_kv) {
   using C = AttnConfig<D, WARPS, STAGES>;
   extern __shared__ __align__(1024) uint8_t smem[];     // swizzle atoms of the TMA boxes are 1 KiB
+  wait_for_predecessor();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int item = blockIdx.x / p.kv_heads, head = blockIdx.x - item * p.kv_heads;
@@ -522,6 +523,7 @@ __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __
                                                                 const int32_t* __restrict__ combine,
                                                                 const OutputList outs, int64_t out_stride,
                                                                 int q_heads, int64_t capacity, int32_t* status) {
+  wait_for_predecessor();
   const int4 rec = __ldg(reinterpret_cast<const int4*>(combine) + blockIdx.x);
   const int first_row = rec.x, n_rows = rec.y, base = rec.z, n_splits = rec.w;
   const int entries = n_rows * q_heads;
@@ -602,7 +604,7 @@ int launch_attn_form(const AttnParams& p, const CUtensorMap& map_kv, int64_t n_w
   const int ready = opt_in_shared_memory(kernel, C::kSmemBytes, configured);
   if (ready != GK_OK) return ready;
   const int64_t blocks = n_work * p.kv_heads;
-  kernel<<<(unsigned)blocks, kWarps * 32, C::kSmemBytes, stream>>>(p, map_kv);
+  launch_after_predecessor(kernel, dim3((unsigned)blocks), dim3(kWarps * 32), C::kSmemBytes, stream, p, map_kv);
   return check_launch();
 }
 
@@ -789,9 +791,9 @@ int combine_entry(const float* part_ml, const float* part_o, int64_t capacity, c
   // rows loop over them.
   const dim3 grid((unsigned)n_combine, (unsigned)((q_heads + 3) / 4));
   switch (head_dim) {
-    case 64: paged_attn_combine_kernel<64><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
-    case 128: paged_attn_combine_kernel<128><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
-    default: paged_attn_combine_kernel<256><<<grid, 128, 0, s>>>(part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
+    case 64: launch_after_predecessor(paged_attn_combine_kernel<64>, grid, dim3(128), 0, s, part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
+    case 128: launch_after_predecessor(paged_attn_combine_kernel<128>, grid, dim3(128), 0, s, part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
+    default: launch_after_predecessor(paged_attn_combine_kernel<256>, grid, dim3(128), 0, s, part_ml, part_o, combine, o, out_row_stride, q_heads, capacity, status); break;
   }
   return check_launch();
 }

@@ -8,7 +8,8 @@
 // accumulators in tensor memory.  The description below is head_dim 128 (KV tiles of T = 128 tokens);
 // head_dim 64 is the same with 64-column accumulators, and head_dim 256, whose two 256-column accumulators
 // would not fit beside the scores, runs ONE query tile per CTA (the record's two tiles go to two CTAs)
-// against KV tiles of 64 tokens, so that two K and three V stages still fit in shared memory:
+// against KV tiles of 64 tokens, so that two K and three V stages still fit in shared memory; there the two
+// score buffers alternate between consecutive KV tiles and Q.K^T runs two tiles ahead of P.V:
 //
 //   TMEM (512 columns)   S0 | S1 | O0 | O1, 128 columns each; P_t (bf16, 64 columns) overwrites the lower
 //                        half of S_t and is the A operand of P_t.V straight from tensor memory
@@ -247,8 +248,6 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const int tile_first_pos = first_pos + t * tile_rows;
     const int lim = pr < mv ? tile_first_pos + pr / G : 0x7fffffff;   // last visible key of this row
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem + t * 128 + lane_base;          // S_t; P_t overwrites its lower half
-    const uint32_t p_addr = s_addr;
     const uint32_t o_addr = tmem + 256 + t * D + lane_base;
     const bool capped = p.softcap > 0.f;
     const float to_log2 = capped ? kLog2e : p.scale * kLog2e;
@@ -256,7 +255,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     float m = -CUDART_INF_F, l = 0.f;                            // m: exponent reference of this row
     bool alive = true;
     for (int j = 0; j < my_tiles && alive; ++j) {
-      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[t], j & 1, &sh->abort));
+      // Two query tiles: tile t owns score buffer t.  One query tile: the two buffers alternate between
+      // consecutive KV tiles, so Q.K^T of the next tile is already there when this softmax ends.
+      const int buf = kTiles == 2 ? t : (j & 1);
+      const uint32_t use = kTiles == 2 ? j : (j >> 1);            // how often this buffer was filled before
+      const uint32_t s_addr = tmem + buf * 128 + lane_base;       // S; P overwrites its lower half
+      const uint32_t p_addr = s_addr;
+      alive = __all_sync(0xffffffffu, bar_wait(&sh->s_full[buf], use & 1, &sh->abort));
       if (!alive) break;
       tc_fence_after();
       const int tok0 = kv_begin + j * kKv;
@@ -349,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();                                      // every lane's P is in tensor memory: one arrival per warp
-      if (lane == 0) bar_arrive(&sh->p_full[t]);
+      if (lane == 0) bar_arrive(&sh->p_full[buf]);
     }
     // epilogue: O / l -> bf16 rows of the output
     if (alive && my_tiles > 0) {
@@ -462,32 +467,68 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
     const uint32_t q_lo = (uint32_t)q_desc, k_lo = (uint32_t)k_desc, v_lo = (uint32_t)v_desc;
     const uint32_t qk_hi = (uint32_t)(q_desc >> 32), v_hi = (uint32_t)(v_desc >> 32);      // K's upper half equals Q's
     constexpr uint32_t kStageStep = kKvTileBytes >> 4;
-    auto issue_qk = [&](int t, int stage) {
+    // S[buf] = Q[t] . K[stage]^T ; O[t] += P[buf] . V[stage]
+    auto issue_qk = [&](int t, int buf, int stage) {
       const uint32_t a = q_lo + t * (kQTileBytes >> 4), b = k_lo + stage * kStageStep;
 #pragma unroll
       for (int k = 0; k < D / 16; ++k) {               // 16 elements of head_dim per step
         const uint32_t a_step = ((k >> 2) * kQPanelBytes + (k & 3) * 32) >> 4;
         const uint32_t b_step = ((k >> 2) * kKvPanelBytes + (k & 3) * 32) >> 4;
-        umma_bf16_ss_split(tmem + t * 128, a + a_step, qk_hi, b + b_step, qk_hi, G_::kIdescQK, k > 0 ? 1u : 0u);
+        umma_bf16_ss_split(tmem + buf * 128, a + a_step, qk_hi, b + b_step, qk_hi, G_::kIdescQK, k > 0 ? 1u : 0u);
       }
-      umma_commit(&sh->s_full[t]);
+      umma_commit(&sh->s_full[buf]);
     };
-    auto issue_pv = [&](int t, int j, int stage) {
+    auto issue_pv = [&](int t, int buf, int j, int stage) {
       const uint32_t b = v_lo + stage * kStageStep;
 #pragma unroll
       for (int k = 0; k < kKv / 16; ++k) {             // 16 tokens per step: 8 columns of P, 16 rows of V
-        umma_bf16_ts_split(tmem + 256 + t * D, tmem + t * 128 + k * 8, b + k * (2048 >> 4), v_hi, G_::kIdescPV,
+        umma_bf16_ts_split(tmem + 256 + t * D, tmem + buf * 128 + k * 8, b + k * (2048 >> 4), v_hi, G_::kIdescPV,
                            (j > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(&sh->pv_done[t]);
     };
+    if (kTiles == 1) {
+      // One query tile, two score buffers: Q.K^T runs two KV tiles ahead of P.V, so the tensor pipe has the next
+      // tile's scores ready while this tile's softmax runs.  Order: QK(0), QK(1), then PV(j), QK(j+2) per tile.
+      for (int a = 0; a < 2 && a < n_tiles && alive; ++a) {
+        alive = bar_wait(&sh->k_full[a % kKStages], (a / kKStages) & 1, &sh->abort);
+        if (!alive) break;
+        fence_async_smem();
+        tc_fence_after();
+        issue_qk(0, a, a % kKStages);
+        umma_commit(&sh->k_free[a % kKStages]);
+      }
+      int vs = 0, vround = 0;
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        alive = bar_wait(&sh->v_full[vs], vround & 1, &sh->abort) &&
+                bar_wait(&sh->p_full[j & 1], (j >> 1) & 1, &sh->abort);
+        if (!alive) break;
+        fence_async_smem();
+        tc_fence_after();
+        issue_pv(0, j & 1, j, vs);
+        umma_commit(&sh->v_free[vs]);
+        if (j + 2 < n_tiles) {                 // the buffer P.V(j) reads is free once that product has run: in order
+          const int ks = (j + 2) % kKStages;
+          alive = bar_wait(&sh->k_full[ks], ((j + 2) / kKStages) & 1, &sh->abort);
+          if (!alive) break;
+          fence_async_smem();
+          tc_fence_after();
+          issue_qk(0, j & 1, ks);
+          umma_commit(&sh->k_free[ks]);
+        }
+        if (++vs == kVStages) {
+          vs = 0;
+          ++vround;
+        }
+      }
+    } else {
     if (n_tiles > 0) {
       alive = bar_wait(&sh->k_full[0], 0, &sh->abort);
       if (alive) {
         fence_async_smem();
         tc_fence_after();
         for (int t = 0; t < 2; ++t)
-          if (nt[t] > 0) issue_qk(t, 0);
+          if (nt[t] > 0) issue_qk(t, t, 0);
         umma_commit(&sh->k_free[0]);
       }
     }
@@ -504,9 +545,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
           alive = bar_wait(&sh->p_full[t], j & 1, &sh->abort);
           if (!alive) break;
           tc_fence_after();
-          issue_pv(t, j, vs);
+          issue_pv(t, t, j, vs);
         }
-        if (j + 1 < nt[t]) issue_qk(t, ks);
+        if (j + 1 < nt[t]) issue_qk(t, t, ks);
       }
       if (!alive) break;
       umma_commit(&sh->v_free[vs]);
@@ -519,6 +560,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const Pre
         ks = 0;
         ++kround;
       }
+    }
     }
   }
 

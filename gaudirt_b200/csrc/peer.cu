@@ -20,6 +20,7 @@ struct PeerFlags {
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerFlags flags, int rank, int world, int epoch,
                                                           int32_t* counter, long long max_cycles, int32_t* status) {
   const int lane = threadIdx.x;
+  wait_for_predecessor();               // the kernels that wrote the peers' buffers have completed
   if (counter) {
     if (lane == 0) {
       epoch = *counter + 1;
@@ -59,8 +60,8 @@ extern "C" int gk_peer_barrier(int32_t* const* flags, int rank, int world, int32
     if (!flags[p] || (reinterpret_cast<uintptr_t>(flags[p]) & 3)) return GK_ERR_INVALID_ARGUMENT;
     f.ptr[p] = flags[p];
   }
-  gk::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, rank, world, epoch, nullptr,
-                                                                                (long long)max_cycles, status);
+  gk::launch_after_predecessor(gk::peer_barrier_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), f, rank,
+                               world, epoch, static_cast<int32_t*>(nullptr), (long long)max_cycles, status);
   return gk::check_launch();
 }
 
@@ -73,7 +74,7 @@ extern "C" int gk_peer_barrier_counted(int32_t* const* flags, int rank, int worl
     if (!flags[p] || (reinterpret_cast<uintptr_t>(flags[p]) & 3)) return GK_ERR_INVALID_ARGUMENT;
     f.ptr[p] = flags[p];
   }
-  gk::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(f, rank, world, 0, epoch_counter,
-                                                                                (long long)max_cycles, status);
+  gk::launch_after_predecessor(gk::peer_barrier_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), f, rank,
+                               world, 0, epoch_counter, (long long)max_cycles, status);
   return gk::check_launch();
 }

@@ -151,6 +151,13 @@ GK_API int gk_paged_attn_bf16(const void* q, int64_t q_row_stride, const void* p
                        float* part_o, float scale, float softcap, int window, int q_heads,
                        int kv_heads, int head_dim, int32_t* status, gk_stream_t stream);
 
+/* Programmatic dependent launch (on by default): the attention, combine, norm, rotary and barrier kernels
+ * are launched so that the GPU may set them up while the kernel before them in the stream is still
+ * running; their first statement waits until that kernel has completed and its writes are visible, so
+ * every access keeps plain stream order and only launch latency overlaps.  0 switches back to ordinary
+ * launches.  Process-wide; the reference has no such switch. */
+GK_API int gk_set_programmatic_launch(int on);
+
 /* How the attention kernel brings a 16-token group of K and V into shared memory.  BOXES: one
  * cp.async.bulk.tensor box per group (K and V, all columns; needs pages of at least 16 tokens, groups
  * that do not qualify -- ragged ends, ranges starting off a 16-token boundary -- are copied row by row).
