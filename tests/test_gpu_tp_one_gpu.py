@@ -84,9 +84,9 @@ def test_sharded_decode_lands_in_every_ranks_gathered_buffer(rt, world, combine)
 
 
 @pytest.mark.parametrize("world", [2, 8])
-def test_sharded_mixed_prefill_and_decode_step_is_gathered_by_the_kernels(rt, world):
+@pytest.mark.parametrize("q_heads,kv_heads,d", [(32, 8, 128), (16, 8, 256), (16, 8, 64)])
+def test_sharded_mixed_prefill_and_decode_step_is_gathered_by_the_kernels(rt, world, q_heads, kv_heads, d):
     """A step with extend chunks (tensor-core kernel), short chunks and decode rows (decode kernel) in one call."""
-    q_heads, kv_heads, d = 32, 8, 128
     prefixes, lengths = [0, 700, 130, 2000, 64, 5, 300], [200, 1, 70, 1, 3, 140, 1]
     case = cases.ragged_case(prefixes, lengths, q_heads, kv_heads, d, 128, seed=77 + world, std=0.5)
     md = rt.PagedMetadata(case.locations, case.requests, case.positions, case.mapping, case.slots)
@@ -102,7 +102,8 @@ def test_sharded_mixed_prefill_and_decode_step_is_gathered_by_the_kernels(rt, wo
     args = (case.q, kp, vp, case.requests, case.positions, case.mapping, q_heads, kv_heads, d, case.scale)
     got = buffers[-1].cpu().double()
     oracle.fp32_softmax_gate(got, oracle.attend_fp32_softmax(*args))
-    oracle.isolated_errors(got, oracle.attend_fp64_rounded(*args), oracle.tiled_bf16_pv(*args, kv_tile=oracle.KV_TILE))
+    oracle.isolated_errors(got, oracle.attend_fp64_rounded(*args),
+                           oracle.tiled_bf16_pv(*args, kv_tile=64 if d == 256 else oracle.KV_TILE))
     assert rt._C._take_device_status() == 0
 
 
