@@ -6,14 +6,17 @@
 // slot of every tensor-parallel peer's receive buffer -- so the exchange rides on the epilogue's
 // stores and no separate collective moves the partials.
 //
-// One CTA owns a [128 * MT] x BN block of the output (MT = 1 or 2 accumulators of BN = 128 or 64
-// TMEM columns each) and walks its K range in steps of 64:
+// One CTA owns a [128 * MT] x BN block of the output (MT = 1 or 2 accumulators of BN = 256, 128 or 64
+// TMEM columns each; the 256 x 256 block uses all 512 columns) and walks its K range in steps of 64:
 //   warp 0     one thread issues the TMA loads of a stage: MT boxes [128 x 64] of A and one box
 //              [BN x 64] of W, 128-byte swizzle, no multicast; rows past M are zero-filled by TMA
 //   warp 1     one thread issues tcgen05.mma.kind::f16 (M 128, N BN, K 16) four times per box and
 //              commits the stage back to the loader, finally the accumulators to the epilogue
 //   warps 2-5  epilogue: tcgen05.ld of the thread's row, rounding to bf16, the block staged in
 //              shared memory and stored to every destination as whole contiguous row segments
+// Wide blocks are for large problems: a 256 x 256 block needs 64 KB of operands per 64 of K where two
+// 256 x 128 blocks need 96 KB, and a 128 x 256 x 16 MMA reads 96 bytes of shared-memory operands per cycle
+// where the 128 x 128 x 16 one reads the SM's whole 128.
 // A kernel of this shape is bound by how fast one SM takes in operand boxes, so small problems are
 // cut along K over a thread-block cluster (2 or 4 CTAs per output block) until the grid fills the
 // GPU; the cluster adds its fp32 accumulators through distributed shared memory in a fixed order.
@@ -41,7 +44,8 @@ struct LinearTile {
   static constexpr int kTmemCols = MT * BN < 32 ? 32 : MT * BN;
   static constexpr int kReduceBytes = MT * BN * kBM * 4;         // fp32 accumulators parked for the split-K sum
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-  static_assert(kReduceBytes <= kStages * kStageBytes, "the reduce buffer reuses the pipeline stages");
+  // the split-K reduce buffer reuses the pipeline stages: tiles too large for that are never cut along K
+  static constexpr bool kCanSplit = kReduceBytes <= kStages * kStageBytes;
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns: a power of two");
 };
 
@@ -295,6 +299,7 @@ bool make_matrix_map(CUtensorMap* map, const void* data, int64_t rows, int64_t c
 template <int MT, int BN>
 int launch_linear(const LinearParams& p, const CUtensorMap& map_a, const CUtensorMap& map_w, int split, cudaStream_t stream) {
   using T = LinearTile<MT, BN>;
+  if (split > 1 && !T::kCanSplit) return GK_ERR_UNSUPPORTED;
   static std::atomic<bool> configured[64];
   const int ready = opt_in_shared_memory(linear_tc_kernel<MT, BN>, T::kSmemBytes, configured);
   if (ready != GK_OK) return ready;
@@ -325,10 +330,10 @@ LinearChoice choose_linear(int64_t m, int64_t n, int64_t k, int mt, int sms) {
   const int64_t m_blocks = (m + kBM * mt - 1) / (kBM * mt), k_steps = k / kBK;
   LinearChoice best{64, 1};
   double best_us = 1e30;
-  for (int bn = 128; bn >= 64; bn /= 2) {
+  for (int bn = 256; bn >= 64; bn /= 2) {
     if (n % bn) continue;
     for (int split = 1; split <= kMaxSplit; split *= 2) {
-      if (split > 1 && (bn / split < 32 || k_steps / split < 4)) break;
+      if (split > 1 && (bn / split < 32 || k_steps / split < 4 || mt * bn > 256)) break;
       const int64_t ctas = (n / bn) * m_blocks * split, waves = (ctas + sms - 1) / sms;
       const double stage_kb = mt * 16.0 + bn / 8.0;
       const double us = (double)waves * (double)((k_steps + split - 1) / split) * stage_kb * (1.0 / 76.0) +
@@ -382,6 +387,7 @@ extern "C" int gk_oproj_bf16(const void* a, int64_t a_row_stride, const void* we
   if (!make_matrix_map(&map_a, a, m, k, a_row_stride, kBM) || !make_matrix_map(&map_w, weight, n, k, weight_row_stride, bn))
     return GK_ERR_UNSUPPORTED;
   auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) return mt == 2 ? launch_linear<2, 256>(p, map_a, map_w, split, s) : launch_linear<1, 256>(p, map_a, map_w, split, s);
   if (bn == 128) return mt == 2 ? launch_linear<2, 128>(p, map_a, map_w, split, s) : launch_linear<1, 128>(p, map_a, map_w, split, s);
   return mt == 2 ? launch_linear<2, 64>(p, map_a, map_w, split, s) : launch_linear<1, 64>(p, map_a, map_w, split, s);
 }

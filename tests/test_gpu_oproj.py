@@ -33,11 +33,13 @@ def gemm_gate(got, x, w):
     assert same > 0.98, float(same)
 
 
-# shapes chosen to reach every kernel variant: 128- and 64-wide blocks, one or two accumulators, and
-# K cut over clusters of 1, 2 and 4 CTAs (few output blocks and many k-steps give the larger clusters)
+# shapes chosen to reach every kernel variant: 256-, 128- and 64-wide blocks (the widest needs more output
+# blocks than SMs: the last two shapes), one or two accumulators, and K cut over clusters of 1, 2 and 4 CTAs
+# (few output blocks and many k-steps give the larger clusters)
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (64, 8192, 1024), (137, 256, 192), (256, 4096, 4096), (129, 128, 128),
                                    (300, 192, 320), (1000, 64, 704), (64, 128, 2048), (200, 256, 1024), (10, 512, 1024),
-                                   (256, 8192, 1024), (77, 192, 4096), (256, 8192, 8192)])
+                                   (256, 8192, 1024), (77, 192, 4096), (256, 8192, 8192), (4001, 2048, 256),
+                                   (100, 65536, 64)])
 def test_oproj_against_binary64(rt, m, n, k):
     gen = torch.Generator().manual_seed(m * 7 + n + k)
     x = torch.randn(m, k, generator=gen).bfloat16()
