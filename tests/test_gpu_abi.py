@@ -175,6 +175,25 @@ def test_box_and_row_forms_give_the_same_bits(attention_form, q_heads, kv_heads,
         attention_form(7)
 
 
+def test_programmatic_launch_changes_no_bits():
+    """With programmatic dependent launch every kernel still waits for its predecessor before its first
+    access: a store -> attention -> combine chain gives the same bits with the switch on and off."""
+    from gaudirt_b200 import abi
+    lib = abi.lib()
+    case = cases.config1()
+    outs = []
+    try:
+        for on in (0, 1, 1):
+            abi.check(lib.gk_set_programmatic_launch(on), "gk_set_programmatic_launch")
+            out, pool, n_combine = run_decode(case, page_tokens=128, split_tokens=256)
+            assert n_combine > 0
+            outs.append((out.cpu(), pool.cpu()))
+    finally:
+        lib.gk_set_programmatic_launch(0)
+    for out, pool in outs[1:]:
+        assert torch.equal(bits(out), bits(outs[0][0])) and torch.equal(bits(pool), bits(outs[0][1]))
+
+
 def test_skewed_lengths_with_automatic_split():
     ctx = cases.lognormal_contexts(24, 20261103, median=512, sigma=1.0, lo=16, hi=6000)
     blocks = int(((ctx + 127) // 128).sum()) + 3
