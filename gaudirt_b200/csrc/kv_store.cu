@@ -25,48 +25,23 @@ __global__ void __launch_bounds__(256) kv_store_kernel(const unsigned short* __r
   const int pieces = head_dim / VEC;                           // per (row, head, K|V)
   const int64_t per_row = 2LL * kv_heads * pieces;
   const int64_t total = rows * per_row;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  // Four pieces per thread and pass: the four slot lookups, then the four loads, then the four stores, so
-  // that the latencies of one piece's chain (slot -> source -> store) overlap with the others'.
-  constexpr int kBatch = 4;
-  for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < total; i0 += stride * kBatch) {
-    const unsigned short* src[kBatch];
-    unsigned short* dst[kBatch];
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const int64_t i = i0 + b * stride;
-      src[b] = nullptr;
-      dst[b] = nullptr;
-      if (i >= total) continue;
-      const int64_t row = i / per_row;
-      int rem = (int)(i - row * per_row);
-      const int kind = rem / (kv_heads * pieces);
-      rem -= kind * kv_heads * pieces;
-      const int head = rem / pieces, piece = rem - head * pieces;
-      const int slot = __ldg(locations + row);
-      if ((unsigned)slot >= (unsigned)slots) {
-        if (status && piece == 0 && head == 0 && kind == 0) atomicOr(status, (int)GK_DEV_BAD_SLOT);
-        continue;
-      }
-      src[b] = (kind ? v + row * v_stride : k + row * k_stride) + head * head_dim + piece * VEC;
-      dst[b] = (kind ? pool_v : pool_k) + ((int64_t)head * slots + slot) * head_dim + piece * VEC;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / per_row;
+    int rem = (int)(i - row * per_row);
+    const int kind = rem / (kv_heads * pieces);
+    rem -= kind * kv_heads * pieces;
+    const int head = rem / pieces, piece = rem - head * pieces;
+    const int slot = __ldg(locations + row);
+    if ((unsigned)slot >= (unsigned)slots) {
+      if (status && piece == 0 && head == 0 && kind == 0) atomicOr(status, (int)GK_DEV_BAD_SLOT);
+      continue;
     }
+    const unsigned short* src = (kind ? v + row * v_stride : k + row * k_stride) + head * head_dim + piece * VEC;
+    unsigned short* dst = (kind ? pool_v : pool_k) + ((int64_t)head * slots + slot) * head_dim + piece * VEC;
     if (VEC == 8) {
-      uint4 data[kBatch];
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-        if (src[b]) data[b] = __ldg(reinterpret_cast<const uint4*>(src[b]));
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-        if (dst[b]) *reinterpret_cast<uint4*>(dst[b]) = data[b];
+      *reinterpret_cast<uint4*>(dst) = __ldg(reinterpret_cast<const uint4*>(src));
     } else {
-      unsigned short data[kBatch];
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-        if (src[b]) data[b] = __ldg(src[b]);
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-        if (dst[b]) *dst[b] = data[b];
+      *dst = __ldg(src);
     }
   }
 }
