@@ -12,6 +12,7 @@
 //     fp32 and are added in binary64;
 //   * a rotation a*cos - b*sin: an exact fp32 product plus one fused multiply-add evaluated toward -inf
 //     and toward +inf, with a sticky bit when the two differ (round-to-odd), then one rounding to bf16.
+//     The vector kernel does this two elements per packed instruction and without a branch (rotate_word).
 //     (A round-to-nearest evaluation with the exact one only for results on a bf16 midpoint was measured
 //     slower, 72 against 54 us: sums of two 16-bit products land on a midpoint about once in 500 elements,
 //     so four warps in ten took the exact path for some lane.)
@@ -93,6 +94,21 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
 __device__ __forceinline__ uint32_t pack2(float2 v) {
   const __nv_bfloat162 b = __float22bfloat162_rn(v);
   return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+// rotate_pair for the two elements of a word, without a branch: bf16(x*c + y*s) rounded once from the exact
+// value.  The packed multiply-add is taken toward -inf and toward +inf.  If the two agree the value is exact.
+// If not, they are neighbouring floats, exactly one of them has an odd bit pattern, and that one IS the
+// truncation of the exact value with a sticky bit (truncation | 1 either keeps an odd truncation or steps
+// an even one to its neighbour away from zero): so "the odd one of the two, else either" is round-to-odd.
+// An exact zero comes out as -0 | +0, and the even-patterned -0 yields to +0.
+__device__ __forceinline__ uint32_t rotate_word(float2 x, float2 c, float2 y, float2 s) {
+  const float2 a = __fmul2_rn(x, c);                                   // exact
+  const float2 down = __ffma2_rd(y, s, a), up = __ffma2_ru(y, s, a);
+  float2 r;
+  r.x = (__float_as_uint(down.x) & 1u) ? down.x : up.x;
+  r.y = (__float_as_uint(down.y) & 1u) ? down.y : up.y;
+  return pack2(r);
 }
 
 // u = bf16(a + b) for the 4 words of a chunk (see add_bf16_exact for why one fp32 rounding is enough)
@@ -370,10 +386,22 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
   const int per_row = heads * chunks;
   const int64_t total = p.rows * (int64_t)per_row;
   const int half = p.rotary_dim >> 1;
+  // Index arithmetic in 32 bits whenever the launch allows it (a 64-bit division is a long subroutine, and
+  // this kernel is bound by instruction issue), and a shift for the usual power-of-two chunks per head.
+  const bool narrow = total <= 0x7fffffffLL;
+  const int chunk_shift = (chunks & (chunks - 1)) == 0 ? __ffs(chunks) - 1 : -1;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = idx / per_row;
-    const int rem = (int)(idx - row * per_row);
-    const int head = rem / chunks, ch = rem - head * chunks;
+    int64_t row;
+    int rem;
+    if (narrow) {
+      const unsigned i = (unsigned)idx, r = i / (unsigned)per_row;
+      row = r;
+      rem = (int)(i - r * (unsigned)per_row);
+    } else {
+      row = idx / per_row;
+      rem = (int)(idx - row * per_row);
+    }
+    const int head = chunk_shift >= 0 ? rem >> chunk_shift : rem / chunks, ch = rem - head * chunks;
     const int kh = head - p.q_heads;
     if (STORE && kh >= p.k_heads) {                              // V: straight to its slot
       const int vh = kh - p.k_heads;
@@ -395,32 +423,38 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
     const unsigned short* src = is_q ? p.q + row * p.q_stride + (int64_t)head * p.head_dim
                                      : p.k + row * p.k_stride + (int64_t)kh * p.head_dim;
     uint4 self4 = __ldg(reinterpret_cast<const uint4*>(src + ch * 8));
-    const unsigned short* self = reinterpret_cast<const unsigned short*>(&self4);
-    unsigned short out[8];
+    uint32_t outw[4];
     if (ch * 8 >= rotary_dim) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) out[e] = self[e];
+      outw[0] = self4.x;
+      outw[1] = self4.y;
+      outw[2] = self4.z;
+      outw[3] = self4.w;
     } else if (p.is_neox) {
       const bool first = ch * 8 < half;
       const int i0 = first ? ch * 8 : ch * 8 - half;
       uint4 other4 = __ldg(reinterpret_cast<const uint4*>(src + (first ? ch * 8 + half : ch * 8 - half)));
       uint4 cos4 = __ldg(reinterpret_cast<const uint4*>(table + i0)), sin4 = __ldg(reinterpret_cast<const uint4*>(table + half + i0));
-      const unsigned short* other = reinterpret_cast<const unsigned short*>(&other4);
-      const unsigned short* c = reinterpret_cast<const unsigned short*>(&cos4);
-      const unsigned short* sn = reinterpret_cast<const unsigned short*>(&sin4);
+      // first half: x*cos - y*sin, second half: x*cos + y*sin (x = this element, y = its partner), two per word
+      const uint32_t sw[4] = {self4.x, self4.y, self4.z, self4.w}, ow[4] = {other4.x, other4.y, other4.z, other4.w};
+      const uint32_t cw[4] = {cos4.x, cos4.y, cos4.z, cos4.w}, nw[4] = {sin4.x, sin4.y, sin4.z, sin4.w};
+      const uint32_t flip = first ? 0x80008000u : 0u;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) out[e] = rotate_pair(self[e], c[e], other[e], sn[e], first);
+      for (int k = 0; k < 4; ++k)
+        outw[k] = rotate_word(unpack2(sw[k]), unpack2(cw[k]), unpack2(ow[k]), unpack2(nw[k] ^ flip));
     } else {
       uint2 cos2 = __ldg(reinterpret_cast<const uint2*>(table + ch * 4)), sin2 = __ldg(reinterpret_cast<const uint2*>(table + half + ch * 4));
-      const unsigned short* c = reinterpret_cast<const unsigned short*>(&cos2);
-      const unsigned short* sn = reinterpret_cast<const unsigned short*>(&sin2);
+      // a word holds the pair (a, b): a*cos - b*sin | b*cos + a*sin
+      const uint32_t sw[4] = {self4.x, self4.y, self4.z, self4.w};
+      const uint32_t cpair[2] = {cos2.x, cos2.y}, spair[2] = {sin2.x, sin2.y};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        out[2 * k] = rotate_pair(self[2 * k], c[k], self[2 * k + 1], sn[k], true);
-        out[2 * k + 1] = rotate_pair(self[2 * k + 1], c[k], self[2 * k], sn[k], false);
+        const float2 v = unpack2(sw[k]);
+        const float cf = __uint_as_float((cpair[k >> 1] >> ((k & 1) * 16)) << 16);
+        const float sf = __uint_as_float((spair[k >> 1] >> ((k & 1) * 16)) << 16);
+        outw[k] = rotate_word(v, make_float2(cf, cf), make_float2(v.y, v.x), make_float2(-sf, sf));
       }
     }
-    const uint4 packed = *reinterpret_cast<const uint4*>(out);
+    const uint4 packed = make_uint4(outw[0], outw[1], outw[2], outw[3]);
     if (is_q) {
       *reinterpret_cast<uint4*>(p.q_out + row * (int64_t)p.q_heads * p.head_dim + (int64_t)head * p.head_dim + ch * 8) = packed;
     } else {
