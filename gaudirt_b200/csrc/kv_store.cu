@@ -25,12 +25,25 @@ __global__ void __launch_bounds__(256) kv_store_kernel(const unsigned short* __r
   const int pieces = head_dim / VEC;                           // per (row, head, K|V)
   const int64_t per_row = 2LL * kv_heads * pieces;
   const int64_t total = rows * per_row;
+  // 32-bit index arithmetic whenever the launch allows it (a 64-bit division is a long subroutine) and a
+  // shift for the usual power-of-two pieces per head
+  const bool narrow = total <= 0x7fffffffLL;
+  const int piece_shift = (pieces & (pieces - 1)) == 0 ? __ffs(pieces) - 1 : -1;
+  const int per_kind = kv_heads * pieces;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / per_row;
-    int rem = (int)(i - row * per_row);
-    const int kind = rem / (kv_heads * pieces);
-    rem -= kind * kv_heads * pieces;
-    const int head = rem / pieces, piece = rem - head * pieces;
+    int64_t row;
+    int rem;
+    if (narrow) {
+      const unsigned r = (unsigned)i / (unsigned)per_row;
+      row = r;
+      rem = (int)((unsigned)i - r * (unsigned)per_row);
+    } else {
+      row = i / per_row;
+      rem = (int)(i - row * per_row);
+    }
+    const int kind = rem >= per_kind;
+    rem -= kind * per_kind;
+    const int head = piece_shift >= 0 ? rem >> piece_shift : rem / pieces, piece = rem - head * pieces;
     const int slot = __ldg(locations + row);
     if ((unsigned)slot >= (unsigned)slots) {
       if (status && piece == 0 && head == 0 && kind == 0) atomicOr(status, (int)GK_DEV_BAD_SLOT);
