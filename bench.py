@@ -791,8 +791,7 @@ def measure(args, config, world, rank, dev, headline):
                     "frac_of_8TBs_nominal": achieved / 8000.0}
         # the launch sequence layer() issues; the KV store rides in the attention launch on decode steps
         # (in the rotary launch when the layer has a front)
-        fused_combine = combine_mode == 1 or (combine_mode == -1 and len(combine) > 0 and
-                                              (len(combine) * 4 <= 148 or int(combine[:, 3].max()) <= 2))
+        fused_combine = bool(md._last_plan_fuses_combine())      # what the operator layer decided for this step's plan
         per_layer = {"paged_attn_kernel": 1}
         if len(combine) and not fused_combine:
             per_layer["paged_attn_combine_kernel"] = 1

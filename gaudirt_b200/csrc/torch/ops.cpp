@@ -421,7 +421,8 @@ TORCH_LIBRARY(gaudirt, m) {
       .def("vocabulary", &PagedMetadata::vocabulary)
       .def("_set_split_tokens", &PagedMetadata::set_split_tokens)
       .def("_set_prefill_min_rows", &PagedMetadata::set_prefill_min_rows)
-      .def("_set_fused_combine", &PagedMetadata::set_fused_combine);
+      .def("_set_fused_combine", &PagedMetadata::set_fused_combine)
+      .def("_last_plan_fuses_combine", &PagedMetadata::last_plan_fuses_combine);
   m.def("paged_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) key_pool, Tensor(b!) value_pool, "
         "__torch__.torch.classes.gaudirt.PagedMetadata metadata, int head_dim, float scale, "
         "float softcap=0.0, int sliding_window=-1) -> Tensor");

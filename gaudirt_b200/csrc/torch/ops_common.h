@@ -459,14 +459,15 @@ class PagedMetadata : public torch::CustomClassHolder {
     plan->part_ml = at::empty({std::max<int64_t>(entries, 1) * 2}, f32);
     plan->part_o = at::empty({std::max<int64_t>(entries, 1) * head_dim}, f32);
     // Fused combine (the last split of a block to finish merges it inside the attention kernel) pays
-    // when only a few blocks are split: it saves a launch whose grid would be tiny.  With many split
+    // when few blocks are split: it saves a launch whose grid would be small.  With many split
     // blocks the merges are better spread over the whole GPU by the separate combine kernel
-    // (measured: 2-5 % faster fused at 4-23 split blocks, 2-9 % slower at 64-256).
+    // (measured: 2-10 % faster fused at 4-59 split blocks, even at 61, 2-9 % slower at 64-256).
     // Blocks cut in two (the uneven cut that fills a tensor-parallel shard's single wave) merge so little state
     // that the fused form costs nothing even with hundreds of them, and it saves the launch.
     int32_t most_splits = 0;
     for (int64_t i = 0; i < n_combine; ++i) most_splits = std::max(most_splits, host[combine_offset + i * GK_COMBINE_WORDS + 3]);
-    const bool fuse = fused_combine_ > 0 || (fused_combine_ < 0 && (n_combine * 4 <= sm_count || most_splits <= 2));
+    const bool fuse = fused_combine_ > 0 || (fused_combine_ < 0 && (n_combine * 5 <= sm_count * 2 || most_splits <= 2));
+    last_plan_fused_ = n_combine > 0 && fuse;
     if (n_combine > 0 && fuse)
       plan->counters = at::zeros({rows_ * kv_heads}, at::TensorOptions().dtype(at::kInt).device(device));
     plan->table = mapping_;
@@ -520,11 +521,13 @@ class PagedMetadata : public torch::CustomClassHolder {
 
   int64_t rows_ = 0, slots_ = 0, request_count_ = 0, context_ = 0, vocabulary_ = 0, page_tokens_ = 1;
   // -1: decide from the schedule, 0: separate combine kernel, 1: combine fused into attention.
+  bool last_plan_fuses_combine() const { return last_plan_fused_; }
   void set_fused_combine(int64_t mode) {
     TORCH_CHECK(mode >= -1 && mode <= 1, "GaudiRT attention: invalid combine mode");
     fused_combine_ = static_cast<int>(mode);
   }
   int split_tokens_ = 0, prefill_min_rows_ = 0, fused_combine_ = -1;
+  bool last_plan_fused_ = false;       // whether the plan built last merges its splits inside the attention kernel
   bool rows_independent_ = false;   // no sequence of the step reads a row that another sequence writes
   at::Tensor locations_, requests_, positions_, mapping_, header_, batch_requests_, token_ids_, last_token_indices_;
   at::Tensor dev_seq_, dev_workspace_, dev_verdict_, dev_row_status_;   // device-validated forms only (revalidate_)
