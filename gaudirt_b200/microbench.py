@@ -1,6 +1,6 @@
 """Kernel-level timings of the small kernels of the path against the HBM roofline.
 
-    python -m gaudirt_b200.microbench [rows|oproj|steps|vocab ...]      (no argument: all sections)
+    python -m gaudirt_b200.microbench [rows|oproj|prefill|steps|vocab ...]      (no argument: all sections)
 
 Times `kv_store`, `fused_add_rms_norm`, `rotary_embedding` and the split-KV combine alone with CUDA
 events (inputs larger than L2 are cycled so no launch re-reads cached data) and prints algorithmic
@@ -41,6 +41,8 @@ def main(sections=()):
         _row_kernels(rows, H, dev, peak)
     if want("oproj"):
         _oproj(dev, peak, path)
+    if want("prefill"):
+        _prefill(H, dev, path)
     if want("steps"):
         _steps(rt, dev)
     if want("vocab"):
@@ -87,6 +89,56 @@ def _row_kernels(rows, H, dev, peak):
         gbs = nbytes / ms / 1e6
         print(f"{name:58s} {ms:8.4f} {gbs:9.1f} {gbs / peak:22.3f}")
 
+
+
+def _prefill(H, dev, path):
+    """The tensor-core prefill kernel at head_dim 64, 128 and 256 on the chunked-prefill shape (16 sequences x
+    512 new rows on paged prefixes of up to 8192 tokens, 32 query / 8 KV heads, pages of 128): CUDA events around
+    each launch, four pools cycled, against the measured bf16 tensor throughput."""
+    import math
+    import numpy as np
+    from gaudirt_b200 import abi
+    tpeak = 1590.0
+    if os.path.exists(path):
+        tpeak = float(json.load(open(path)).get("bf16_tflops", tpeak))
+    batch, chunk, hq, hkv, page, pools_n = 16, 512, 32, 8, 128, 4
+    gen = torch.Generator().manual_seed(20261104)
+    prefix = torch.randint(0, 8193, (batch,), generator=gen)
+    need = (prefix + chunk + page - 1) // page
+    n_pages = int(int(need.sum()) * 1.1) + 1
+    slots = n_pages * page
+    perm = torch.randperm(n_pages, generator=gen).to(torch.int32)
+    tables = torch.zeros(batch, int(need.max()), dtype=torch.int32)
+    cursor = 0
+    for b in range(batch):
+        tables[b, :int(need[b])] = perm[cursor:cursor + int(need[b])]
+        cursor += int(need[b])
+    table = (tables * page).to(dev)                         # first slot of every page of 128 slot-contiguous tokens
+    seq = np.array([[b * chunk, chunk, int(prefix[b]), b] for b in range(batch)], dtype=np.int32)
+    work, _ = H.prefill_plan(seq, hq, hkv)
+    work_d = torch.from_numpy(work).to(dev)
+    visible = int((prefix * chunk).sum()) + batch * chunk * (chunk + 1) // 2
+    lib, stream = abi.lib(), H.stream_ptr()
+    print()
+    print(f"{'paged_prefill_tc_kernel  16 x 512 rows, 32q/8kv':52s} {'ms':>8s} {'TFLOP/s':>9s} {'of measured bf16 peak':>22s}")
+    for d in (64, 128, 256):
+        pools = [(torch.randn(2, hkv, slots, d, device=dev) * 0.5).bfloat16() for _ in range(pools_n)]
+        q = (torch.randn(batch * chunk, hq * d, device=dev) * 0.5).bfloat16()
+        out = torch.empty_like(q)
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(pools_n)]
+        for _ in range(3):
+            for pool, (a, b) in zip(pools, events):
+                a.record()
+                abi.check(lib.gk_paged_prefill_tc_bf16(q.data_ptr(), q.stride(0), pool[0].data_ptr(), pool[1].data_ptr(), slots,
+                                                       table.data_ptr(), table.stride(0), 1, page, None, work_d.data_ptr(),
+                                                       len(work), out.data_ptr(), out.stride(0), 1 / math.sqrt(d), 0.0, -1, hq,
+                                                       hkv, d, None, stream), "gk_paged_prefill_tc_bf16")
+                b.record()
+            torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in events) / pools_n
+        tflops = 4.0 * d * hq * visible / ms / 1e9
+        print(f"{f'head_dim {d}':52s} {ms:8.4f} {tflops:9.0f} {tflops / tpeak:22.3f}")
+        del pools, q, out
 
 
 def _oproj(dev, peak, path):
