@@ -231,9 +231,9 @@ def test_slot_layout_random_batches_agree_with_the_oracle():
 
 
 def test_plan_cuts_partition_every_range_including_uneven_cuts():
-    """Whatever cut the schedule search picks (even pieces, or pieces of the limit with the remainder last, which
-    it may pick when the grid is a few waves), the pieces of a block tile its KV range exactly, in split order,
-    and the split state is sized for them."""
+    """Whatever cut the schedule search picks (none, even pieces, or pieces of the limit with the remainder last,
+    which it may pick when the grid is a few waves), the pieces of a block tile its KV range exactly, in split
+    order, and the split state is sized for them."""
     shapes = [
         (np.array([[i, 1, 4095, i] for i in range(256)], dtype=np.int32), 4, 1),      # one KV head of config 2: one wave
         (np.array([[i, 1, 4095, i] for i in range(256)], dtype=np.int32), 8, 2),
@@ -263,4 +263,8 @@ def test_plan_cuts_partition_every_range_including_uneven_cuts():
             else:
                 assert int(pieces[0][6]) == -1
         assert total == entries and len(combine) == sum(1 for r in by_row.values() if len(r) > 1)
-    assert saw_uneven, "the one-wave shard of equal ranges is where the uneven cut is chosen"
+    assert saw_uneven, "the skewed single-head batch is where the uneven cut is chosen"
+    # equal ranges that fit the resident CTA slots in one wave are left whole: the launch is HBM-bound either
+    # way, and a CTA next to an idle slot streams faster, so a cut would only add prologues and merges
+    work, combine, _ = H.plan(shapes[0][0], 4, 1, 128, sm_count=148)
+    assert len(work) == 256 and len(combine) == 0
