@@ -476,6 +476,8 @@ def measure(args, config, world, rank, dev, headline):
             for _ in range(DEPTH - 2):
                 layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))
         if row_parallel is not None:
+            while row_parallel.mode == "push" and row_parallel._turn % row_parallel.depth:
+                layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))     # the ring back at a whole number of rounds
             return record
         rows = sampled_rows(w.ctx, w.chunk)
         q0 = split(resident_qkv[0])[0]

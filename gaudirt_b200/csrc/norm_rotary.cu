@@ -471,6 +471,100 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
   }
 }
 
+// Neox layout, vector form: one thread per PAIR of 16-byte chunks (chunk c of the first half of the rotated
+// part and its partner c + rotary_dim/16), so every input chunk, cosine and sine is loaded and unpacked once
+// for the two chunks it feeds; chunks past the rotated part and (with the store) the V rows are plain copies.
+// A head is `units` work units: rotary_dim/16 pairs, then (head_dim - rotary_dim)/8 single chunks.
+template <bool STORE>
+__global__ void __launch_bounds__(256) rotary_neox_pair_kernel(const RotaryParams p) {
+  wait_for_predecessor();
+  const int chunks = p.head_dim >> 3, pairs = p.rotary_dim >> 4, units = pairs + chunks - 2 * pairs;
+  const int rotated = (p.q_heads + p.k_heads) * units;                      // units of a row that are q or k
+  const int per_row = rotated + (STORE ? p.k_heads * chunks : 0);
+  const int64_t total = p.rows * (int64_t)per_row;
+  const int half = p.rotary_dim >> 1;
+  const bool narrow = total <= 0x7fffffffLL;
+  const int unit_shift = (units & (units - 1)) == 0 ? __ffs(units) - 1 : -1;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row;
+    int rem;
+    if (narrow) {
+      const unsigned i = (unsigned)idx, r = i / (unsigned)per_row;
+      row = r;
+      rem = (int)(i - r * (unsigned)per_row);
+    } else {
+      row = idx / per_row;
+      rem = (int)(idx - row * per_row);
+    }
+    if (STORE && rem >= rotated) {                                 // V: straight to its slot
+      const int at = rem - rotated, vh = at / chunks, ch = at - vh * chunks;
+      const int slot = __ldg(p.locations + row);
+      if ((unsigned)slot < (unsigned)p.slots)
+        *reinterpret_cast<uint4*>(p.pool_v + ((int64_t)vh * p.slots + slot) * p.head_dim + ch * 8) =
+            __ldg(reinterpret_cast<const uint4*>(p.v + row * p.v_stride + (int64_t)vh * p.head_dim + ch * 8));
+      continue;
+    }
+    const int head = unit_shift >= 0 ? rem >> unit_shift : rem / units, unit = rem - head * units;
+    const int kh = head - p.q_heads;
+    const bool is_q = kh < 0;
+    int pos = __ldg(p.positions + row);
+    bool rotate = unit < pairs;
+    if ((unsigned)pos >= (unsigned)p.cache_rows) {                // position outside the table: pass through, report
+      if (p.status && rem == 0) atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+      pos = 0;
+      rotate = false;
+    }
+    const unsigned short* src = is_q ? p.q + row * p.q_stride + (int64_t)head * p.head_dim
+                                     : p.k + row * p.k_stride + (int64_t)kh * p.head_dim;
+    unsigned short* dst = is_q ? p.q_out + (row * p.q_heads + head) * (int64_t)p.head_dim
+                               : (p.k_out ? p.k_out + (row * p.k_heads + kh) * (int64_t)p.head_dim : nullptr);
+    unsigned short* pooled = nullptr;
+    if (STORE && !is_q) {
+      const int slot = __ldg(p.locations + row);
+      if ((unsigned)slot < (unsigned)p.slots) {
+        pooled = p.pool_k + ((int64_t)kh * p.slots + slot) * p.head_dim;
+      } else if (p.status && unit == 0 && kh == 0) {
+        atomicOr(p.status, (int)GK_DEV_BAD_SLOT);
+      }
+    }
+    // a unit below `pairs` covers chunks `unit` and `unit + pairs`; the others are one chunk each
+    const int ch_a = unit < pairs ? unit : 2 * pairs + (unit - pairs);
+    const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(src + ch_a * 8));
+    if (unit >= pairs) {                                          // past the rotated part: a copy
+      if (dst) *reinterpret_cast<uint4*>(dst + ch_a * 8) = a4;
+      if (pooled) *reinterpret_cast<uint4*>(pooled + ch_a * 8) = a4;
+      continue;
+    }
+    const int ch_b = unit + pairs;
+    const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(src + ch_b * 8));
+    uint4 out_a = a4, out_b = b4;
+    if (rotate) {
+      const unsigned short* table = p.cache + (int64_t)pos * p.rotary_dim;
+      const uint4 cos4 = __ldg(reinterpret_cast<const uint4*>(table + unit * 8));
+      const uint4 sin4 = __ldg(reinterpret_cast<const uint4*>(table + half + unit * 8));
+      const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w}, bw[4] = {b4.x, b4.y, b4.z, b4.w};
+      const uint32_t cw[4] = {cos4.x, cos4.y, cos4.z, cos4.w}, sw[4] = {sin4.x, sin4.y, sin4.z, sin4.w};
+      uint32_t oa[4], ob[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack2(aw[k]), b = unpack2(bw[k]), c = unpack2(cw[k]), sn = unpack2(sw[k]);
+        oa[k] = rotate_word(a, c, b, make_float2(-sn.x, -sn.y));      // a*cos - b*sin
+        ob[k] = rotate_word(b, c, a, sn);                             // b*cos + a*sin
+      }
+      out_a = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+      out_b = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    }
+    if (dst) {
+      *reinterpret_cast<uint4*>(dst + ch_a * 8) = out_a;
+      *reinterpret_cast<uint4*>(dst + ch_b * 8) = out_b;
+    }
+    if (pooled) {
+      *reinterpret_cast<uint4*>(pooled + ch_a * 8) = out_a;
+      *reinterpret_cast<uint4*>(pooled + ch_b * 8) = out_b;
+    }
+  }
+}
+
 bool rotary_vectorisable(const RotaryParams& p, bool store) {
   uintptr_t bits = reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.cache) |
                    reinterpret_cast<uintptr_t>(p.q_out) | reinterpret_cast<uintptr_t>(p.k_out);
@@ -480,6 +574,17 @@ bool rotary_vectorisable(const RotaryParams& p, bool store) {
 }
 
 int launch_rotary(const RotaryParams& p, bool store, cudaStream_t stream) {
+  if (p.is_neox && rotary_vectorisable(p, store)) {
+    const int chunks = p.head_dim / 8, pairs = p.rotary_dim / 16, units = chunks - pairs;
+    const int64_t total = p.rows * ((int64_t)(p.q_heads + p.k_heads) * units + (store ? p.k_heads * chunks : 0));
+    const int64_t want = (total + 255) / 256;
+    const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    if (store)
+      launch_after_predecessor(rotary_neox_pair_kernel<true>, dim3(blocks), dim3(256), 0, stream, p);
+    else
+      launch_after_predecessor(rotary_neox_pair_kernel<false>, dim3(blocks), dim3(256), 0, stream, p);
+    return check_launch();
+  }
   if (rotary_vectorisable(p, store)) {
     const int heads = p.q_heads + p.k_heads + (store ? p.k_heads : 0);
     const int64_t total = p.rows * heads * (p.head_dim / 8);
