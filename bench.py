@@ -800,9 +800,9 @@ def measure(args, config, world, rank, dev, headline):
         if pushed:
             per_layer["peer_barrier_kernel"] = 1
         if w.front:
-            per_layer.update(rms_norm_kernel=1, rotary_vec_kernel=1)
+            per_layer.update(rms_norm_kernel=1, rotary_neox_pair_kernel=1)
         if row_parallel is not None:
-            per_layer = {"rotary_vec_kernel": 1, "paged_attn_kernel": 1, "linear_tc_kernel": 1, "rms_norm_kernel": 1}
+            per_layer = {"rotary_neox_pair_kernel": 1, "paged_attn_kernel": 1, "linear_tc_kernel": 1, "rms_norm_kernel": 1}
             if len(combine) and not fused_combine:
                 per_layer["paged_attn_combine_kernel"] = 1
             if row_parallel.mode == "push":
