@@ -436,7 +436,8 @@ def measure(args, config, world, rank, dev, headline):
             # rotary + store -> attention on this rank's heads -> o_proj, rank-ordered sum, add + norm
             q = torch.ops.gaudirt._rotary_kv_store(q, k, v, cache, md, kp, vp, d, d, True)
             attn = torch.ops.gaudirt._paged_attn_stored(q, kp, vp, md, d, scale)
-            return row_parallel.forward(attn, o_weight[l], xr[1], gamma, 1e-5, 1.0)[0]
+            sums = exchange if isinstance(exchange, tp.RowParallelOutput) else row_parallel
+            return sums.forward(attn, o_weight[l], xr[1], gamma, 1e-5, 1.0)[0]
         if w.front:
             torch.ops.gaudirt.fused_add_rms_norm(xr[0], xr[1], gamma, 1e-5, 1.0)
             q = torch.ops.gaudirt._rotary_kv_store(q, k, v, cache, md, kp, vp, d, d, True)
@@ -476,6 +477,15 @@ def measure(args, config, world, rank, dev, headline):
             for _ in range(DEPTH - 2):
                 layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))
         if row_parallel is not None:
+            if row_parallel.mode == "push":
+                # the fused exchange against the NCCL all-gather of the partials: same bits on every rank
+                baseline = tp.RowParallelOutput(R, w.hidden, dev, mode="nccl")
+                again = layer(0, md, resident_qkv[0], xr_of(resident_xr, 0), exchange=baseline).clone()
+                same = torch.tensor([int(torch.equal(bits(out), bits(again)))], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                record["push_eq_nccl"] = bool(same.item())
+                if not record["push_eq_nccl"]:
+                    raise SystemExit("parity: the fused o_proj exchange differs from the NCCL exchange")
             while row_parallel.mode == "push" and row_parallel._turn % row_parallel.depth:
                 layer(0, md, resident_qkv[0], xr_of(resident_xr, 0))     # the ring back at a whole number of rounds
             return record
