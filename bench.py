@@ -149,8 +149,6 @@ def parse():
     ap.add_argument("--programmatic-launch", type=int, default=-1, choices=(-1, 0, 1),
                     help="experiments only: 0 / 1 switch programmatic dependent launch of the kernels off / on "
                          "(-1 = the library's default)")
-    ap.add_argument("--e2e-copy-groups", type=int, default=1, choices=(0, 1),
-                    help="experiments only: 0 copies every layer's rows in with a copy and an event of its own")
     ap.add_argument("--no-tp-configs", action="store_true",
                     help="with N > 1: measure the chosen configuration only, not configs 3 and 5 after it")
     return ap.parse_args()
@@ -684,24 +682,18 @@ def measure(args, config, world, rank, dev, headline):
                         t.copy_(h, non_blocking=True)
                     got_index = torch.cuda.Event()
                     got_index.record(copy_in)
-                    # Layers come in as groups of 1, 2, 4, ... (one copy and one event per group): the first layer
-                    # waits for one layer's rows only, and a kernel that depends on a copy is a cross-engine edge
-                    # of the graph, which costs microseconds even when the copy finished long ago.
-                    arrived, first = {}, 0
-                    while first < L:
-                        last = min(L, first + max(1, first + 1 if args.e2e_copy_groups else 1))
-                        dev_qkv[first:last].copy_(host_qkv[first:last], non_blocking=True)
+                    arrived = []
+                    for l in range(L):
+                        dev_qkv[l].copy_(host_qkv[l], non_blocking=True)
                         if w.front:
-                            dev_xr[first:last].copy_(host_xr[first:last], non_blocking=True)
-                        arrived[first] = torch.cuda.Event()
-                        arrived[first].record(copy_in)
-                        first = last
+                            dev_xr[l].copy_(host_xr[l], non_blocking=True)
+                        arrived.append(torch.cuda.Event())
+                        arrived[-1].record(copy_in)
                 main.wait_event(got_index)
                 md_e2e._revalidate_(*index_dev)
                 done = []
                 for l in range(L):
-                    if l in arrived:
-                        main.wait_event(arrived[l])
+                    main.wait_event(arrived[l])
                     if gather is not None and l >= DEPTH - 1:
                         main.wait_event(done[l - (DEPTH - 1)])
                     out = layer(l, md_e2e, dev_qkv[l], xr_of(dev_xr, l))
