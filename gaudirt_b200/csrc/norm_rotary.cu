@@ -480,8 +480,11 @@ __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
 // part and its partner c + rotary_dim/16), so every input chunk, cosine and sine is loaded and unpacked once
 // for the two chunks it feeds; chunks past the rotated part and (with the store) the V rows are plain copies.
 // A head is `units` work units: rotary_dim/16 pairs, then (head_dim - rotary_dim)/8 single chunks.
+#ifndef GK_ROTARY_MIN_BLOCKS
+#define GK_ROTARY_MIN_BLOCKS 5   // 48 registers: 35.4 us at 8192 rows; 37.5 us with no target (62 registers), 39.4 us at eight CTAs (spills)
+#endif
 template <bool STORE>
-__global__ void __launch_bounds__(256) rotary_neox_pair_kernel(const RotaryParams p) {
+__global__ void __launch_bounds__(256, GK_ROTARY_MIN_BLOCKS) rotary_neox_pair_kernel(const RotaryParams p) {
   wait_for_predecessor();
   const int chunks = p.head_dim >> 3, pairs = p.rotary_dim >> 4, units = pairs + chunks - 2 * pairs;
   const int rotated = (p.q_heads + p.k_heads) * units;                      // units of a row that are q or k
