@@ -5,14 +5,20 @@
 // All query heads of the KV head's GQA group -- times the rows of the block -- are packed into
 // the 16 rows of an m16n8k16 tile, so every K/V byte is read from HBM once per work item.
 // The KV range is cut into 16-token groups dealt round-robin to the warps; each warp owns a
-// private ring of staged groups, each stage with its own mbarrier, and never meets a block-wide
-// barrier until the final cross-warp merge.  A group that is 16 slot-contiguous tokens of one page
-// (any page of at least 16 tokens) is fetched by one lane as ONE 4-D TMA box (cp.async.bulk.tensor:
-// K and V, every 64-column panel, 16 rows, 128-byte swizzle, no multicast); any other group -- token-granular tables, ragged
-// ends, ranges that do not start on a 16-token boundary -- row by row with 16-byte cp.async into the
-// same layout (rows past the range zero-filled).  The slot of a group is looked up one iteration
-// before its copies are issued, so the table read is never waited for.  Slots come from the slot
-// table in the kernel, so there is no gather-index buffer and no gathered K/V copy as in the
+// private ring of staged groups and never meets a block-wide barrier until the final cross-warp
+// merge.  The kernel exists in two forms that stage a group differently and are otherwise the same
+// code (same bits):
+//   boxes  a group that is 16 slot-contiguous tokens of one page (any page of at least 16 tokens) is
+//          fetched by one lane as ONE 4-D TMA box (cp.async.bulk.tensor: K and V, every 64-column
+//          panel, 16 rows, 128-byte swizzle, no multicast), completion by transaction bytes on the
+//          stage's own mbarrier (bounded wait); the rare other group -- a ragged end, a range that does
+//          not start on a 16-token boundary -- is copied row by row and waited for on the spot;
+//   rows   every group row by row with 16-byte cp.async into the same layout (rows past the range
+//          zero-filled), one cp.async group per stage; the only form for token-granular tables.
+// The launcher takes boxes for launches that leave resident CTA slots idle and rows otherwise, which
+// is where each measured faster.  The table entry of a group is loaded one iteration before its copies
+// are issued and not touched until then, so the table read is never waited for.  Slots come from the
+// slot table in the kernel, so there is no gather-index buffer and no gathered K/V copy as in the
 // reference (src/bridge/attention_plan.cpp:246-255, src/bridge/paged_attention.cpp:89-100).
 #include "tc_common.cuh"
 
@@ -50,7 +56,6 @@ struct AttnParams {
   int64_t part_capacity;                 // entries part_ml / part_o hold; a record that points past it is skipped
   float scale, softcap;
   int window, page_shift, q_heads, kv_heads, group, n_out;
-  int tma;                               // whole groups may be fetched through the tensor maps
 };
 
 template <int D, int WARPS, int STAGES>
@@ -623,7 +628,7 @@ inline int sm_count_of_current_device() {
 }
 
 template <int D>
-int launch_attn(AttnParams& p, int64_t n_work, int page_tokens, cudaStream_t stream) {
+int launch_attn(const AttnParams& p, int64_t n_work, int page_tokens, cudaStream_t stream) {
   // One box per 16-token group needs pages of at least 16 slot-contiguous tokens, 32-bit row coordinates and
   // the V half at a positive 16-byte-aligned distance after the K half; without them (or without the driver's
   // encoder) the plain form copies every group row by row.
@@ -636,9 +641,9 @@ int launch_attn(AttnParams& p, int64_t n_work, int page_tokens, cudaStream_t str
   const int form = attention_form.load(std::memory_order_relaxed);
   const bool boxes = form == GK_ATTENTION_FORM_AUTO ? n_work * p.kv_heads <= 2 * sm_count_of_current_device()
                                                     : form == GK_ATTENTION_FORM_BOXES;
-  p.tma = boxes && page_tokens >= kGroupTokens && pool_rows < 0x7fffffffLL &&
-          make_kv_group_map(&map_kv, p.pool_k, v_minus_k, pool_rows, kGroupTokens, D);
-  return p.tma ? launch_attn_form<D, true>(p, map_kv, n_work, stream) : launch_attn_form<D, false>(p, map_kv, n_work, stream);
+  const bool boxed = boxes && page_tokens >= kGroupTokens && pool_rows < 0x7fffffffLL &&
+                     make_kv_group_map(&map_kv, p.pool_k, v_minus_k, pool_rows, kGroupTokens, D);
+  return boxed ? launch_attn_form<D, true>(p, map_kv, n_work, stream) : launch_attn_form<D, false>(p, map_kv, n_work, stream);
 }
 
 // Argument checks + launch of the attention kernel.  `part_capacity` is the number of entries the
