@@ -268,3 +268,18 @@ def test_plan_cuts_partition_every_range_including_uneven_cuts():
     # way, and a CTA next to an idle slot streams faster, so a cut would only add prologues and merges
     work, combine, _ = H.plan(shapes[0][0], 4, 1, 128, sm_count=148)
     assert len(work) == 256 and len(combine) == 0
+
+
+def test_process_wide_switches_take_only_their_values():
+    """The two host-side switches (how the decode kernel stages a group, programmatic dependent launch) need no
+    GPU: valid values are accepted, anything else is GK_ERR_INVALID_ARGUMENT and changes nothing."""
+    lib = abi.lib()
+    try:
+        for form in (0, 1, 2):
+            assert lib.gk_set_attention_form(form) == 0
+        for bad in (-1, 3, 99):
+            assert lib.gk_set_attention_form(bad) != 0
+        assert lib.gk_set_programmatic_launch(1) == 0 and lib.gk_set_programmatic_launch(0) == 0
+    finally:
+        lib.gk_set_attention_form(0)
+        lib.gk_set_programmatic_launch(0)
