@@ -149,6 +149,8 @@ def parse():
     ap.add_argument("--programmatic-launch", type=int, default=-1, choices=(-1, 0, 1),
                     help="experiments only: 0 / 1 switch programmatic dependent launch of the kernels off / on "
                          "(-1 = the library's default)")
+    ap.add_argument("--ring-depth", type=int, default=4, choices=(2, 4, 8),
+                    help="experiments only: gathered buffers in the tensor-parallel ring")
     ap.add_argument("--no-tp-configs", action="store_true",
                     help="with N > 1: measure the chosen configuration only, not configs 3 and 5 after it")
     return ap.parse_args()
@@ -415,7 +417,7 @@ def measure(args, config, world, rank, dev, headline):
     lo_row, hi_row = rank * R // world, (rank + 1) * R // world       # the rows this rank reads back
     host_out = torch.empty(L, hi_row - lo_row, hq * d * world, dtype=torch.bfloat16).pin_memory()
 
-    DEPTH = 4         # ring of gathered buffers (divides every layer count): the read-back of layer l has until layer l + 3
+    DEPTH = args.ring_depth   # ring of gathered buffers (divides every layer count): the read-back of layer l has until layer l + DEPTH - 1
     gather = tp.OutputGather(R, hq * d, dev, mode=args.gather, depth=DEPTH) if world > 1 and not args.oproj else None
     lib = abi.lib()
     row_parallel = o_weight = None
